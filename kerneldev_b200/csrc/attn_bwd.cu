@@ -1,0 +1,644 @@
+// Backward kernels for sm_100a: dQ (query-tile major) and dK/dV (key-tile major).
+//
+// Both kernels recompute P = exp2(S*scale*log2e - LSE) from Q, K and the saved base-2 LSE and
+// form dS = P * (dP - delta), as the reference's two backward workers do
+// (_flash_attn_bwd_dq, original_kernel.py:1173-1336; _flash_attn_bwd_dkdv, :1339-1525), but
+// walk only the non-empty tiles of the plan and apply the rule only on PARTIAL tiles.
+// delta = rowsum(O * dO) (the reference's _flash_attn_bwd_precompute, :629-710) is produced
+// by the dQ kernel's prologue and consumed by the dK/dV kernel, which therefore runs second.
+//
+// Shared structure (384 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warps 4-7 and
+// 8-11 = two compute warpgroups. The backward needs no row reductions, so the 128 columns of a
+// score tile are split into two independent 64-column streams, one per warpgroup; the MMA
+// issuer alternates between the streams so that one stream's element-wise work overlaps the
+// other stream's MMAs:
+//   M1(i): S_i, dP_i  (smem x smem -> TMEM, N = 64)      compute(i): P_i / dS_i -> TMEM (16 bit)
+//   M2(i): accumulators += (P_i | dS_i) x smem operand   (A from TMEM)
+#include "common.cuh"
+#include "mask_rule.cuh"
+#include "sm100_prims.cuh"
+
+namespace kd {
+
+struct BwdArgs {
+  int B, H, T, NT, NP, Tpad;
+  float scale_log2;  // sm_scale * log2(e)
+  float sm_scale;
+  const uint32_t* desc;
+  const int32_t* fwd_cnt;
+  const uint16_t* fwd_list;
+  const int32_t* bwd_cnt;
+  const uint16_t* bwd_list;
+  uint32_t* status;
+  const void* o;
+  int64_t o_sb, o_sh, o_st;
+  const void* d_o;
+  int64_t do_sb, do_sh, do_st;
+  const float* lse;
+  float* delta;
+  void* dq;
+  int64_t dq_sb, dq_sh, dq_st;
+  void* dk;
+  int64_t dk_sb, dk_sh, dk_st;
+  void* dv;
+  int64_t dv_sb, dv_sh, dv_st;
+};
+
+template <int HD>
+struct BwdCfg {
+  static constexpr int KBLK = HD / 64;
+  static constexpr int TILE_BYTES = KD_TILE * HD * 2;
+  static constexpr int STAGES = (HD == 64) ? 3 : 2;   // ring of (tile, tile) pairs
+  static constexpr int SMEM_FIX = 0;                               // two resident tiles
+  static constexpr int SMEM_RING = SMEM_FIX + 2 * TILE_BYTES;      // STAGES x two streamed tiles
+  static constexpr int SMEM_STAGE = SMEM_RING + STAGES * 2 * TILE_BYTES;  // per-warp staging
+  static constexpr int STAGE_WORDS = 3 * 64;                       // 64 x {-lse, delta, descriptor}
+  static constexpr int SMEM_ACT = SMEM_STAGE + 8 * STAGE_WORDS * 4;  // compacted entry list
+  static constexpr int SMEM_TOTAL = SMEM_ACT + 128 * 2;
+  static constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;
+  // TMEM columns
+  static constexpr uint32_t TM_S0 = 0, TM_S1 = 64, TM_P0 = 128, TM_P1 = 192;  // scores / dP streams
+  static constexpr uint32_t TM_ACC0 = 256;        // dQ, or dK
+  static constexpr uint32_t TM_ACC1 = 256 + HD;   // dV
+};
+
+enum : uint32_t {
+  W_Q_FIXFULL = 0x201, W_Q_RINGEMPTY = 0x202, W_Q_RINGFULL = 0x203, W_Q_PFULL = 0x204, W_Q_SFULL = 0x205,
+  W_Q_ACCFULL = 0x206,
+  W_K_FIXFULL = 0x301, W_K_RINGEMPTY = 0x302, W_K_RINGFULL = 0x303, W_K_PFULL = 0x304, W_K_SFULL = 0x305,
+  W_K_ACCFULL = 0x306,
+};
+
+// stores 32 fp32 accumulator values (scaled) as 16-bit elements to a row in global memory
+template <bool kBf16>
+__device__ __forceinline__ void store_row32(uint16_t* dst, const uint32_t (&r)[32], float f) {
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    uint4 v;
+    v.x = pack2<kBf16>(__uint_as_float(r[j + 0]) * f, __uint_as_float(r[j + 1]) * f);
+    v.y = pack2<kBf16>(__uint_as_float(r[j + 2]) * f, __uint_as_float(r[j + 3]) * f);
+    v.z = pack2<kBf16>(__uint_as_float(r[j + 4]) * f, __uint_as_float(r[j + 5]) * f);
+    v.w = pack2<kBf16>(__uint_as_float(r[j + 6]) * f, __uint_as_float(r[j + 7]) * f);
+    *reinterpret_cast<uint4*>(dst + j) = v;
+  }
+}
+
+// =========================================================================================
+// dQ kernel: one CTA per (b, h, query tile); streams = key halves of the current key tile.
+//   M1(i): S_i = Q K_i^T, dP_i = dO V_i^T      M2(i): dQ += dS_i K_i
+// =========================================================================================
+template <int HD, bool kBf16>
+__global__ void __launch_bounds__(384, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                   const BwdArgs a) {
+  using C = BwdCfg<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sQ = smem_u32(smem + C::SMEM_FIX);
+  const uint32_t sDO = sQ + C::TILE_BYTES;
+  const uint32_t sRing = smem_u32(smem + C::SMEM_RING);  // stage s: K at +0, V at +TILE_BYTES
+  uint32_t* sStage = reinterpret_cast<uint32_t*>(smem + C::SMEM_STAGE);
+  uint16_t* sAct = reinterpret_cast<uint16_t*>(smem + C::SMEM_ACT);
+
+  __shared__ __align__(8) uint64_t bar_fix_full, bar_ring_full[C::STAGES], bar_ring_empty[C::STAGES],
+      bar_s_full[2], bar_p_full[2], bar_acc_full;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int n_act_s;
+  __shared__ AbortFlag abortf;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int pair = qt >> 1, ip = qt & 1;
+
+  if (tid == 0) {
+    abortf.v = 0;
+    mbar_init(smem_u32(&bar_fix_full), 1);
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(smem_u32(&bar_ring_full[s]), 1);
+      mbar_init(smem_u32(&bar_ring_empty[s]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&bar_s_full[i]), 1);
+      mbar_init(smem_u32(&bar_p_full[i]), 128);
+    }
+    mbar_init(smem_u32(&bar_acc_full), 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_s), 512);
+    tmem_relinquish();
+  }
+  if (warp == 2) {
+    // compact the pair's list down to the entries that are non-empty for this query tile
+    const int n = a.fwd_cnt[b * a.NP + pair];
+    const uint16_t* list = a.fwd_list + ((size_t)b * a.NP + pair) * a.NT;
+    int na = 0;
+    for (int base = 0; base < n; base += 32) {
+      const int e = base + lane;
+      const uint32_t ent = e < n ? list[e] : 0u;
+      const uint32_t cls = (ent >> (8 + 2 * ip)) & 3u;
+      const uint32_t bal = __ballot_sync(0xffffffffu, cls != 0u);
+      if (cls != 0u) sAct[na + __popc(bal & ((1u << lane) - 1u))] = static_cast<uint16_t>((ent & 0xFFu) | (cls << 8));
+      na += __popc(bal);
+    }
+    if (lane == 0) n_act_s = na;
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = tmem_base_s;
+  const int na = n_act_s;
+
+  if (warp < 4) {
+    reg_dealloc<56>();
+    if (warp == 0 && lane == 0 && na > 0) {
+      // ------------------------------ TMA producer ------------------------------
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      tma_prefetch_desc(&tmDO);
+      mbar_arrive_expect_tx(smem_u32(&bar_fix_full), 2 * C::TILE_BYTES);
+      for (int kb = 0; kb < C::KBLK; ++kb) {
+        tma_load_4d(sQ + kb * 16384, &tmQ, smem_u32(&bar_fix_full), kb * 64, qt * KD_TILE, h, b);
+        tma_load_4d(sDO + kb * 16384, &tmDO, smem_u32(&bar_fix_full), kb * 64, qt * KD_TILE, h, b);
+      }
+      int issued = 0;
+      for (int e = 0; e < na; ++e) {
+        const int s = e % C::STAGES;
+        const uint32_t ph = (e / C::STAGES) & 1;
+        const int kt = sAct[e] & 0xFF;
+        if (!mbar_wait(smem_u32(&bar_ring_empty[s]), ph ^ 1, &abortf, a.status, W_Q_RINGEMPTY)) break;
+        mbar_arrive_expect_tx(smem_u32(&bar_ring_full[s]), 2 * C::TILE_BYTES);
+        const uint32_t dst = sRing + s * 2 * C::TILE_BYTES;
+        for (int kb = 0; kb < C::KBLK; ++kb) {
+          tma_load_4d(dst + kb * 16384, &tmK, smem_u32(&bar_ring_full[s]), kb * 64, kt * KD_TILE, h, b);
+          tma_load_4d(dst + C::TILE_BYTES + kb * 16384, &tmV, smem_u32(&bar_ring_full[s]), kb * 64, kt * KD_TILE, h, b);
+        }
+        issued = e + 1;
+      }
+      if (abortf.v != 0) {
+        for (int e = max(0, issued - C::STAGES); e < issued; ++e)
+          for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_ring_full[e % C::STAGES]), (e / C::STAGES) & 1); ++spin) {}
+        for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_fix_full), 0); ++spin) {}
+      }
+    } else if (warp == 1 && lane == 0 && na > 0) {
+      // ------------------------------ MMA issuer ------------------------------
+      const uint32_t idesc_m1 = make_idesc_f16(kBf16, 0, 0, KD_TILE, 64);   // S_i, dP_i: N = 64 keys
+      const uint32_t idesc_m2 = make_idesc_f16(kBf16, 0, 1, KD_TILE, HD);   // dQ: B = K rows, MN-major
+      const uint32_t tS[2] = {tbase + C::TM_S0, tbase + C::TM_S1};
+      const uint32_t tP[2] = {tbase + C::TM_P0, tbase + C::TM_P1};
+      const uint32_t tAcc = tbase + C::TM_ACC0;
+      auto issue_m1 = [&](int i, int e) {
+        const uint32_t kb_base = sRing + (e % C::STAGES) * 2 * C::TILE_BYTES + i * 64 * 128;  // key rows 64i..
+        const uint32_t vb_base = kb_base + C::TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+          mma_ss(tS[i], desc_kmajor_sw128(sQ + (kk / 4) * 16384, kk % 4),
+                 desc_kmajor_sw128(kb_base + (kk / 4) * 16384, kk % 4), idesc_m1, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+          mma_ss(tP[i], desc_kmajor_sw128(sDO + (kk / 4) * 16384, kk % 4),
+                 desc_kmajor_sw128(vb_base + (kk / 4) * 16384, kk % 4), idesc_m1, kk > 0);
+        mma_commit(smem_u32(&bar_s_full[i]));
+      };
+      auto issue_m2 = [&](int i, int e, bool acc) {
+        const uint32_t kb_base = sRing + (e % C::STAGES) * 2 * C::TILE_BYTES + i * 64 * 128;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)  // 64 keys of this stream, 16 per MMA; dS_i sits on top of S_i
+          mma_ts(tAcc, tS[i] + kk * 8, desc_mnmajor_sw128(kb_base, kk, 16384), idesc_m2, (acc || kk > 0) ? 1u : 0u);
+      };
+      bool ok = mbar_wait(smem_u32(&bar_fix_full), 0, &abortf, a.status, W_Q_FIXFULL);
+      if (ok) ok = mbar_wait(smem_u32(&bar_ring_full[0]), 0, &abortf, a.status, W_Q_RINGFULL);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_m1(0, 0);
+        issue_m1(1, 0);
+      }
+      uint32_t pphase = 0;
+      for (int e = 0; e < na && ok; ++e) {
+        bool ring_waited = false;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          ok = mbar_wait(smem_u32(&bar_p_full[i]), pphase, &abortf, a.status, W_Q_PFULL);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_m2(i, e, e > 0 || i > 0);
+          if (e + 1 < na) {
+            if (!ring_waited) {
+              ok = mbar_wait(smem_u32(&bar_ring_full[(e + 1) % C::STAGES]), ((e + 1) / C::STAGES) & 1, &abortf,
+                             a.status, W_Q_RINGFULL);
+              if (!ok) break;
+              ring_waited = true;
+              tc_fence_after_sync();
+            }
+            issue_m1(i, e + 1);
+          }
+        }
+        if (!ok) break;
+        pphase ^= 1;
+        mma_commit(smem_u32(&bar_ring_empty[e % C::STAGES]));
+      }
+      if (ok) mma_commit(smem_u32(&bar_acc_full));
+    }
+  } else {
+    reg_alloc<224>();
+    // ------------------------------ compute warpgroups ------------------------------
+    const int i = (warp - 4) >> 2;   // stream: key half of each key tile
+    const int wq = warp & 3;
+    const int row = wq * 32 + lane;
+    const int qi = qt * KD_TILE + row;
+    const bool q_valid = qi < a.T;
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    const uint32_t tS = tbase + lane_base + (i == 0 ? C::TM_S0 : C::TM_S1);
+    const uint32_t tP = tbase + lane_base + (i == 0 ? C::TM_P0 : C::TM_P1);
+    uint32_t* kd_buf = sStage + (size_t)(warp - 4) * C::STAGE_WORDS;
+    const float c = a.scale_log2;
+    const size_t bh = (size_t)b * a.H + h;
+
+    // delta = rowsum(O * dO) for this thread's query row
+    float delta = 0.f;
+    if (q_valid) {
+      const uint4* orow = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(a.o) + (size_t)b * a.o_sb + (size_t)h * a.o_sh + (size_t)qi * a.o_st);
+      const uint4* drow = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(a.d_o) + (size_t)b * a.do_sb + (size_t)h * a.do_sh + (size_t)qi * a.do_st);
+#pragma unroll
+      for (int j = 0; j < HD / 8; ++j) {
+        const uint4 ov = orow[j], dv = drow[j];
+        const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w}, dw[4] = {dv.x, dv.y, dv.z, dv.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 x = unpack2<kBf16>(ow[k]), y = unpack2<kBf16>(dw[k]);
+          delta = fmaf(x.x, y.x, delta);
+          delta = fmaf(x.y, y.y, delta);
+        }
+      }
+      if (i == 0) a.delta[bh * a.T + qi] = delta;
+    }
+    const float neg_lse = q_valid ? -a.lse[bh * a.T + qi] : 0.f;
+    const uint32_t qd = a.desc[(size_t)b * a.Tpad + qi];
+    uint32_t sphase = 0;
+    bool ok = true;
+
+    for (int e = 0; e < na; ++e) {
+      const uint32_t ent = sAct[e];
+      const uint32_t cls = ent >> 8;
+      const int kt = ent & 0xFF;
+      const int j0 = kt * KD_TILE + i * 64;  // first key of this stream
+      if (cls == KD_TILE_PARTIAL) {
+        __syncwarp();
+        const uint32_t* src = a.desc + (size_t)b * a.Tpad + j0;
+        kd_buf[lane] = src[lane];
+        kd_buf[32 + lane] = src[32 + lane];
+        __syncwarp();
+      }
+      ok = mbar_wait(smem_u32(&bar_s_full[i]), sphase, &abortf, a.status, W_Q_SFULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      sphase ^= 1;
+      tc_fence_after_sync();
+
+      uint32_t pk[32];
+#pragma unroll
+      for (int cb = 0; cb < 2; ++cb) {
+        uint32_t rs[32], rp[32];
+        tmem_ld32(tS + cb * 32, rs);
+        tmem_ld32(tP + cb * 32, rp);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float p0 = fast_exp2(fmaf(__uint_as_float(rs[j]), c, neg_lse));
+          float p1 = fast_exp2(fmaf(__uint_as_float(rs[j + 1]), c, neg_lse));
+          if (cls == KD_TILE_PARTIAL) {
+            if (!rule_allowed(qd, qi, kd_buf[cb * 32 + j], j0 + cb * 32 + j)) p0 = 0.f;
+            if (!rule_allowed(qd, qi, kd_buf[cb * 32 + j + 1], j0 + cb * 32 + j + 1)) p1 = 0.f;
+          }
+          const float ds0 = p0 * (__uint_as_float(rp[j]) - delta);
+          const float ds1 = p1 * (__uint_as_float(rp[j + 1]) - delta);
+          pk[cb * 16 + j / 2] = pack2<kBf16>(ds0, ds1);
+        }
+      }
+      tmem_st32(tS, pk);   // dS_i as 16-bit A operand on top of S_i (this thread's own row)
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&bar_p_full[i]));
+    }
+
+    // epilogue: this warpgroup stores columns [i*HD/2, (i+1)*HD/2) of dQ
+    if (ok && na > 0) {
+      ok = mbar_wait(smem_u32(&bar_acc_full), 0, &abortf, a.status, W_Q_ACCFULL);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after_sync();
+      uint16_t* drow = reinterpret_cast<uint16_t*>(a.dq) + (size_t)b * a.dq_sb + (size_t)h * a.dq_sh + (size_t)qi * a.dq_st + i * (HD / 2);
+#pragma unroll
+      for (int cb = 0; cb < HD / 64; ++cb) {
+        uint32_t r[32];
+        if (na > 0) {
+          tmem_ld32(tbase + lane_base + C::TM_ACC0 + i * (HD / 2) + cb * 32, r);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        if (q_valid) store_row32<kBf16>(drow + cb * 32, r, a.sm_scale);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tbase, 512);
+}
+
+// =========================================================================================
+// dK/dV kernel: one CTA per (b, h, key tile); streams = query halves of the current query tile.
+//   M1(i): S^T_i = K Q_i^T, dP^T_i = V dO_i^T     M2(i): dV += P^T_i dO_i,  dK += dS^T_i Q_i
+// =========================================================================================
+template <int HD, bool kBf16>
+__global__ void __launch_bounds__(384, 1)
+attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                     const BwdArgs a) {
+  using C = BwdCfg<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sK = smem_u32(smem + C::SMEM_FIX);
+  const uint32_t sV = sK + C::TILE_BYTES;
+  const uint32_t sRing = smem_u32(smem + C::SMEM_RING);  // stage s: Q at +0, dO at +TILE_BYTES
+  uint32_t* sStage = reinterpret_cast<uint32_t*>(smem + C::SMEM_STAGE);
+
+  __shared__ __align__(8) uint64_t bar_fix_full, bar_ring_full[C::STAGES], bar_ring_empty[C::STAGES],
+      bar_s_full[2], bar_p_full[2], bar_acc_full;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ AbortFlag abortf;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int n = a.bwd_cnt[b * a.NT + kt];
+  const uint16_t* list = a.bwd_list + ((size_t)b * a.NT + kt) * a.NT;
+
+  if (tid == 0) {
+    abortf.v = 0;
+    mbar_init(smem_u32(&bar_fix_full), 1);
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(smem_u32(&bar_ring_full[s]), 1);
+      mbar_init(smem_u32(&bar_ring_empty[s]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&bar_s_full[i]), 1);
+      mbar_init(smem_u32(&bar_p_full[i]), 128);
+    }
+    mbar_init(smem_u32(&bar_acc_full), 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_s), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = tmem_base_s;
+
+  if (warp < 4) {
+    reg_dealloc<56>();
+    if (warp == 0 && lane == 0 && n > 0) {
+      // ------------------------------ TMA producer ------------------------------
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      tma_prefetch_desc(&tmDO);
+      mbar_arrive_expect_tx(smem_u32(&bar_fix_full), 2 * C::TILE_BYTES);
+      for (int kb = 0; kb < C::KBLK; ++kb) {
+        tma_load_4d(sK + kb * 16384, &tmK, smem_u32(&bar_fix_full), kb * 64, kt * KD_TILE, h, b);
+        tma_load_4d(sV + kb * 16384, &tmV, smem_u32(&bar_fix_full), kb * 64, kt * KD_TILE, h, b);
+      }
+      int issued = 0;
+      for (int e = 0; e < n; ++e) {
+        const int s = e % C::STAGES;
+        const uint32_t ph = (e / C::STAGES) & 1;
+        const int qt = list[e] & 0xFF;
+        if (!mbar_wait(smem_u32(&bar_ring_empty[s]), ph ^ 1, &abortf, a.status, W_K_RINGEMPTY)) break;
+        mbar_arrive_expect_tx(smem_u32(&bar_ring_full[s]), 2 * C::TILE_BYTES);
+        const uint32_t dst = sRing + s * 2 * C::TILE_BYTES;
+        for (int kb = 0; kb < C::KBLK; ++kb) {
+          tma_load_4d(dst + kb * 16384, &tmQ, smem_u32(&bar_ring_full[s]), kb * 64, qt * KD_TILE, h, b);
+          tma_load_4d(dst + C::TILE_BYTES + kb * 16384, &tmDO, smem_u32(&bar_ring_full[s]), kb * 64, qt * KD_TILE, h, b);
+        }
+        issued = e + 1;
+      }
+      if (abortf.v != 0) {
+        for (int e = max(0, issued - C::STAGES); e < issued; ++e)
+          for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_ring_full[e % C::STAGES]), (e / C::STAGES) & 1); ++spin) {}
+        for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_fix_full), 0); ++spin) {}
+      }
+    } else if (warp == 1 && lane == 0 && n > 0) {
+      // ------------------------------ MMA issuer ------------------------------
+      const uint32_t idesc_m1 = make_idesc_f16(kBf16, 0, 0, KD_TILE, 64);   // S^T_i, dP^T_i: N = 64 queries
+      const uint32_t idesc_m2 = make_idesc_f16(kBf16, 0, 1, KD_TILE, HD);   // dV, dK: B = dO / Q rows, MN-major
+      const uint32_t tS[2] = {tbase + C::TM_S0, tbase + C::TM_S1};
+      const uint32_t tP[2] = {tbase + C::TM_P0, tbase + C::TM_P1};
+      const uint32_t tDK = tbase + C::TM_ACC0, tDV = tbase + C::TM_ACC1;
+      auto issue_m1 = [&](int i, int e) {
+        const uint32_t qb = sRing + (e % C::STAGES) * 2 * C::TILE_BYTES + i * 64 * 128;  // query rows 64i..
+        const uint32_t dob = qb + C::TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+          mma_ss(tS[i], desc_kmajor_sw128(sK + (kk / 4) * 16384, kk % 4),
+                 desc_kmajor_sw128(qb + (kk / 4) * 16384, kk % 4), idesc_m1, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+          mma_ss(tP[i], desc_kmajor_sw128(sV + (kk / 4) * 16384, kk % 4),
+                 desc_kmajor_sw128(dob + (kk / 4) * 16384, kk % 4), idesc_m1, kk > 0);
+        mma_commit(smem_u32(&bar_s_full[i]));
+      };
+      auto issue_m2 = [&](int i, int e, bool acc) {
+        const uint32_t qb = sRing + (e % C::STAGES) * 2 * C::TILE_BYTES + i * 64 * 128;
+        const uint32_t dob = qb + C::TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)  // dV += P^T_i dO_i   (P^T_i on top of S^T_i)
+          mma_ts(tDV, tS[i] + kk * 8, desc_mnmajor_sw128(dob, kk, 16384), idesc_m2, (acc || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)  // dK += dS^T_i Q_i   (dS^T_i on top of dP^T_i)
+          mma_ts(tDK, tP[i] + kk * 8, desc_mnmajor_sw128(qb, kk, 16384), idesc_m2, (acc || kk > 0) ? 1u : 0u);
+      };
+      bool ok = mbar_wait(smem_u32(&bar_fix_full), 0, &abortf, a.status, W_K_FIXFULL);
+      if (ok) ok = mbar_wait(smem_u32(&bar_ring_full[0]), 0, &abortf, a.status, W_K_RINGFULL);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_m1(0, 0);
+        issue_m1(1, 0);
+      }
+      uint32_t pphase = 0;
+      for (int e = 0; e < n && ok; ++e) {
+        bool ring_waited = false;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          ok = mbar_wait(smem_u32(&bar_p_full[i]), pphase, &abortf, a.status, W_K_PFULL);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_m2(i, e, e > 0 || i > 0);
+          if (e + 1 < n) {
+            if (!ring_waited) {
+              ok = mbar_wait(smem_u32(&bar_ring_full[(e + 1) % C::STAGES]), ((e + 1) / C::STAGES) & 1, &abortf,
+                             a.status, W_K_RINGFULL);
+              if (!ok) break;
+              ring_waited = true;
+              tc_fence_after_sync();
+            }
+            issue_m1(i, e + 1);
+          }
+        }
+        if (!ok) break;
+        pphase ^= 1;
+        mma_commit(smem_u32(&bar_ring_empty[e % C::STAGES]));
+      }
+      if (ok) mma_commit(smem_u32(&bar_acc_full));
+    }
+  } else {
+    reg_alloc<224>();
+    // ------------------------------ compute warpgroups ------------------------------
+    const int i = (warp - 4) >> 2;   // stream: query half of each query tile
+    const int wq = warp & 3;
+    const int row = wq * 32 + lane;
+    const int kj = kt * KD_TILE + row;   // this thread's key
+    const bool k_valid = kj < a.T;
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    const uint32_t tS = tbase + lane_base + (i == 0 ? C::TM_S0 : C::TM_S1);
+    const uint32_t tP = tbase + lane_base + (i == 0 ? C::TM_P0 : C::TM_P1);
+    uint32_t* st_buf = sStage + (size_t)(warp - 4) * C::STAGE_WORDS;  // [64 -lse][64 delta][64 desc]
+    const float c = a.scale_log2;
+    const size_t bh = (size_t)b * a.H + h;
+    const uint32_t kdesc = a.desc[(size_t)b * a.Tpad + kj];
+    uint32_t sphase = 0;
+    bool ok = true;
+
+    for (int e = 0; e < n; ++e) {
+      const uint32_t ent = list[e];
+      const uint32_t cls = ent >> 8;
+      const int qt = ent & 0xFF;
+      const int i0 = qt * KD_TILE + i * 64;  // first query of this stream
+      __syncwarp();
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int q = i0 + r * 32 + lane;
+        const bool v = q < a.T;
+        st_buf[r * 32 + lane] = __float_as_uint(v ? -a.lse[bh * a.T + q] : 0.f);
+        st_buf[64 + r * 32 + lane] = __float_as_uint(v ? a.delta[bh * a.T + q] : 0.f);
+        st_buf[128 + r * 32 + lane] = a.desc[(size_t)b * a.Tpad + q];
+      }
+      __syncwarp();
+      ok = mbar_wait(smem_u32(&bar_s_full[i]), sphase, &abortf, a.status, W_K_SFULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      sphase ^= 1;
+      tc_fence_after_sync();
+
+      uint32_t pk_p[32], pk_ds[32];
+#pragma unroll
+      for (int cb = 0; cb < 2; ++cb) {
+        uint32_t rs[32], rp[32];
+        tmem_ld32(tS + cb * 32, rs);
+        tmem_ld32(tP + cb * 32, rp);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const int jj = cb * 32 + j;
+          float p0 = fast_exp2(fmaf(__uint_as_float(rs[j]), c, __uint_as_float(st_buf[jj])));
+          float p1 = fast_exp2(fmaf(__uint_as_float(rs[j + 1]), c, __uint_as_float(st_buf[jj + 1])));
+          if (cls == KD_TILE_PARTIAL) {
+            if (!rule_allowed(st_buf[128 + jj], i0 + jj, kdesc, kj)) p0 = 0.f;
+            if (!rule_allowed(st_buf[128 + jj + 1], i0 + jj + 1, kdesc, kj)) p1 = 0.f;
+          }
+          const float ds0 = p0 * (__uint_as_float(rp[j]) - __uint_as_float(st_buf[64 + jj]));
+          const float ds1 = p1 * (__uint_as_float(rp[j + 1]) - __uint_as_float(st_buf[64 + jj + 1]));
+          pk_p[cb * 16 + j / 2] = pack2<kBf16>(p0, p1);
+          pk_ds[cb * 16 + j / 2] = pack2<kBf16>(ds0, ds1);
+        }
+      }
+      tmem_st32(tS, pk_p);    // P^T_i on top of S^T_i
+      tmem_st32(tP, pk_ds);   // dS^T_i on top of dP^T_i
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&bar_p_full[i]));
+    }
+
+    // epilogue: this warpgroup stores columns [i*HD/2, (i+1)*HD/2) of dK and dV
+    if (ok && n > 0) {
+      ok = mbar_wait(smem_u32(&bar_acc_full), 0, &abortf, a.status, W_K_ACCFULL);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after_sync();
+      uint16_t* krow = reinterpret_cast<uint16_t*>(a.dk) + (size_t)b * a.dk_sb + (size_t)h * a.dk_sh + (size_t)kj * a.dk_st + i * (HD / 2);
+      uint16_t* vrow = reinterpret_cast<uint16_t*>(a.dv) + (size_t)b * a.dv_sb + (size_t)h * a.dv_sh + (size_t)kj * a.dv_st + i * (HD / 2);
+#pragma unroll
+      for (int cb = 0; cb < HD / 64; ++cb) {
+        uint32_t rk[32], rv[32];
+        if (n > 0) {
+          tmem_ld32(tbase + lane_base + C::TM_ACC0 + i * (HD / 2) + cb * 32, rk);
+          tmem_ld32(tbase + lane_base + C::TM_ACC1 + i * (HD / 2) + cb * 32, rv);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) { rk[j] = 0u; rv[j] = 0u; }
+        }
+        if (k_valid) {
+          store_row32<kBf16>(krow + cb * 32, rk, a.sm_scale);
+          store_row32<kBf16>(vrow + cb * 32, rv, 1.0f);
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tbase, 512);
+}
+
+template <int HD, bool kBf16>
+static int launch_bwd_t(const kd_attn_params& p, const kd_plan_layout& L, const PlanView& pv, cudaStream_t stream) {
+  using C = BwdCfg<HD>;
+  CUtensorMap tmQ, tmK, tmV, tmDO;
+  int rc;
+  if ((rc = encode_tensor_map(&tmQ, p.q, p.B, p.H, p.T, p.D, p.dtype, KD_TILE, "q")) != 0) return rc;
+  if ((rc = encode_tensor_map(&tmK, p.k, p.B, p.H, p.T, p.D, p.dtype, KD_TILE, "k")) != 0) return rc;
+  if ((rc = encode_tensor_map(&tmV, p.v, p.B, p.H, p.T, p.D, p.dtype, KD_TILE, "v")) != 0) return rc;
+  if ((rc = encode_tensor_map(&tmDO, p.d_o, p.B, p.H, p.T, p.D, p.dtype, KD_TILE, "do")) != 0) return rc;
+  BwdArgs a;
+  a.B = p.B; a.H = p.H; a.T = p.T; a.NT = L.NT; a.NP = L.NP; a.Tpad = L.NT * KD_TILE;
+  a.scale_log2 = p.sm_scale * 1.4426950408889634f;
+  a.sm_scale = p.sm_scale;
+  a.desc = pv.desc; a.fwd_cnt = pv.fwd_cnt; a.fwd_list = pv.fwd_list;
+  a.bwd_cnt = pv.bwd_cnt; a.bwd_list = pv.bwd_list; a.status = pv.status;
+  a.o = p.o.ptr; a.o_sb = p.o.stride_b; a.o_sh = p.o.stride_h; a.o_st = p.o.stride_t;
+  a.d_o = p.d_o.ptr; a.do_sb = p.d_o.stride_b; a.do_sh = p.d_o.stride_h; a.do_st = p.d_o.stride_t;
+  a.lse = p.lse; a.delta = p.delta;
+  a.dq = p.dq.ptr; a.dq_sb = p.dq.stride_b; a.dq_sh = p.dq.stride_h; a.dq_st = p.dq.stride_t;
+  a.dk = p.dk.ptr; a.dk_sb = p.dk.stride_b; a.dk_sh = p.dk.stride_h; a.dk_st = p.dk.stride_t;
+  a.dv = p.dv.ptr; a.dv_sb = p.dv.stride_b; a.dv_sh = p.dv.stride_h; a.dv_st = p.dv.stride_t;
+  auto kq = attn_bwd_dq_kernel<HD, kBf16>;
+  auto kk = attn_bwd_dkdv_kernel<HD, kBf16>;
+  cudaError_t e = cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_ALLOC);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(kk, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_ALLOC);
+  if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "bwd smem attribute: %s", cudaGetErrorString(e));
+  dim3 grid(L.NT, p.H, p.B);
+  kq<<<grid, 384, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
+  kk<<<grid, 384, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "attn_bwd kernels launch: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+int launch_attn_bwd(const kd_attn_params& p, cudaStream_t stream) {
+  kd_plan_layout L;
+  if (kd_plan_layout_get(p.B, p.T, &L) != 0) return KD_ERR_ARG;
+  PlanView pv = make_plan_view(const_cast<void*>(p.plan), L);
+  if (!p.d_o.ptr) return set_error(KD_ERR_ARG, "d_o is null");
+  if (p.D == 64) return p.dtype == KD_BF16 ? launch_bwd_t<64, true>(p, L, pv, stream) : launch_bwd_t<64, false>(p, L, pv, stream);
+  if (p.D == 128) return p.dtype == KD_BF16 ? launch_bwd_t<128, true>(p, L, pv, stream) : launch_bwd_t<128, false>(p, L, pv, stream);
+  return set_error(KD_ERR_ARG, "head dim %d not supported (64 or 128)", p.D);
+}
+
+}  // namespace kd

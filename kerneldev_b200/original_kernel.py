@@ -1,0 +1,230 @@
+"""Host side of the attention operator: the call signature of the reference's
+``original_kernel.flash_attention`` (original_kernel.py:2096-2168) in front of the hand-written
+sm_100a kernels in libkd_attention.so.
+
+``flash_attention`` is a drop-in for ``model.MultiHeadAttention`` (model.py:83-93): same
+arguments, same return structure, O contiguous in the dtype of q, LSE in base-2 units
+(original_kernel.py:603-604), gradients for q, k and v only (the gradient of LSE is ignored,
+as at original_kernel.py:1965-1992).
+
+Differences from the reference, all deliberate:
+  * the mask is the rule of original_kernel.py:480-517 for the forward AND the backward; the
+    reference's backward loop bounds ignore the bidirectional sections when ``causal=True`` and
+    metadata is given (original_kernel.py:1202-1204, :1368-1371);
+  * a query row that sees no key gets O = 0, LSE = -inf and no gradient (the reference's default
+    path produces NaN there, original_kernel.py:554-561);
+  * CUDA sm_100 only, fp16 / bf16, head_dim 64 or 128. There is no Triton, no autotuning and no
+    CPU path: unsupported inputs raise.
+``autotune``, ``prescale_qk`` and ``precision`` are accepted and ignored.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+
+import torch
+
+from . import _capi
+from .plan import AttentionPlan, get_plan
+
+__all__ = ["flash_attention", "generate_hadamard_signs", "hadamard_transform"]
+
+_DTYPES = {torch.float16: _capi.KD_F16, torch.bfloat16: _capi.KD_BF16}
+
+
+def _kd_tensor(t: torch.Tensor) -> _capi.KdTensor:
+    return _capi.KdTensor(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
+
+
+def _usable(t: torch.Tensor) -> torch.Tensor:
+    """Returns t itself when TMA can describe it (unit stride along D, 16-byte aligned rows),
+    else one contiguous copy."""
+    es = t.element_size()
+    ok = (t.stride(3) == 1 and t.data_ptr() % 16 == 0
+          and all((t.stride(i) * es) % 16 == 0 and t.stride(i) > 0 for i in range(3)))
+    return t if ok else t.contiguous()
+
+
+def _check_inputs(q, k, v):
+    if q.dim() != 4:
+        raise ValueError("q, k, v must be (batch, heads, time, head_dim)")
+    if not (q.shape == k.shape == v.shape):
+        raise ValueError(f"q, k, v must have the same shape, got {tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
+    if not q.is_cuda:
+        raise RuntimeError("flash_attention runs on CUDA sm_100 devices only; there is no CPU path")
+    if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError("q, k, v must share dtype float16 or bfloat16")
+    if q.shape[-1] not in (64, 128):
+        raise ValueError(f"head_dim {q.shape[-1]} is not supported (64 or 128)")
+    if not (k.device == q.device and v.device == q.device):
+        raise ValueError("q, k, v must be on the same device")
+
+
+def _params(q, k, v, o, lse, plan, sm_scale):
+    B, H, T, D = q.shape
+    p = _capi.KdAttnParams()
+    p.B, p.H, p.T, p.D = B, H, T, D
+    p.dtype = _DTYPES[q.dtype]
+    p.sm_scale = sm_scale
+    p.q, p.k, p.v, p.o = _kd_tensor(q), _kd_tensor(k), _kd_tensor(v), _kd_tensor(o)
+    p.lse = lse.data_ptr()
+    p.plan = plan.ptr
+    return p
+
+
+def _forward(q, k, v, plan: AttentionPlan, sm_scale: float):
+    q, k, v = _usable(q), _usable(k), _usable(v)
+    B, H, T, D = q.shape
+    o = torch.empty((B, H, T, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
+    p = _params(q, k, v, o, lse, plan, sm_scale)
+    stream = torch.cuda.current_stream(q.device).cuda_stream
+    with torch.cuda.device(q.device):
+        _capi.check(_capi.load().kd_attn_fwd(ctypes.byref(p), stream))
+    if os.environ.get("KD_CHECK_STATUS") == "1":
+        plan.check_status()
+    return o, lse
+
+
+def _backward(q, k, v, o, lse, d_o, plan: AttentionPlan, sm_scale: float):
+    q, k, v, d_o = _usable(q), _usable(k), _usable(v), _usable(d_o)
+    B, H, T, D = q.shape
+    dq = torch.empty((B, H, T, D), dtype=q.dtype, device=q.device)
+    dk = torch.empty_like(dq)
+    dv = torch.empty_like(dq)
+    delta = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
+    p = _params(q, k, v, o, lse, plan, sm_scale)
+    p.d_o = _kd_tensor(d_o)
+    p.dq, p.dk, p.dv = _kd_tensor(dq), _kd_tensor(dk), _kd_tensor(dv)
+    p.delta = delta.data_ptr()
+    stream = torch.cuda.current_stream(q.device).cuda_stream
+    with torch.cuda.device(q.device):
+        _capi.check(_capi.load().kd_attn_bwd(ctypes.byref(p), stream))
+    if os.environ.get("KD_CHECK_STATUS") == "1":
+        plan.check_status()
+    return dq, dk, dv
+
+
+class _FlashAttentionFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, plan, sm_scale):
+        o, lse = _forward(q, k, v, plan, sm_scale)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.plan = plan
+        ctx.sm_scale = sm_scale
+        ctx.mark_non_differentiable(lse)
+        return o, lse
+
+    @staticmethod
+    def backward(ctx, d_o, _d_lse):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = _backward(q, k, v, o, lse, d_o, ctx.plan, ctx.sm_scale)
+        return dq, dk, dv, None, None
+
+
+def _hadamard_call(x: torch.Tensor, signs, inverse: bool) -> torch.Tensor:
+    x = _usable(x)
+    B, H, T, D = x.shape
+    y = torch.empty((B, H, T, D), dtype=x.dtype, device=x.device)
+    xs, ys = _kd_tensor(x), _kd_tensor(y)
+    stream = torch.cuda.current_stream(x.device).cuda_stream
+    with torch.cuda.device(x.device):
+        _capi.check(_capi.load().kd_hadamard(ctypes.byref(xs), ctypes.byref(ys), B, H, T, D, _DTYPES[x.dtype],
+                                             signs.data_ptr() if signs is not None else None,
+                                             1 if inverse else 0, stream))
+    return y
+
+
+class _HadamardFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, signs):
+        ctx.signs = signs
+        return _hadamard_call(x, signs, inverse=False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        # y = x diag(s) W / sqrt(D) with W symmetric, so dx = dy W / sqrt(D) diag(s)
+        return _hadamard_call(dy, ctx.signs, inverse=True), None
+
+
+def generate_hadamard_signs(n_heads: int, head_dim: int, seed: int = 0, device="cuda") -> torch.Tensor:
+    """(n_heads, head_dim) float32 tensor of +-1 drawn from a seeded CPU generator.
+
+    The reference only names this utility (README.md:68-77); the recipe here is this package's own:
+    ``torch.randint(0, 2, (n_heads, head_dim), generator=torch.Generator().manual_seed(seed)) * 2 - 1``.
+    """
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    s = torch.randint(0, 2, (n_heads, head_dim), generator=g, dtype=torch.int64) * 2 - 1
+    return s.to(torch.float32).to(device)
+
+
+def hadamard_transform(x: torch.Tensor, signs: torch.Tensor | None = None) -> torch.Tensor:
+    """``WHT(x * signs[h]) / sqrt(D)`` over the last dimension of a (B, H, T, D) tensor, with the
+    Walsh-Hadamard matrix in natural (Sylvester) order; differentiable."""
+    if x.dim() != 4 or x.shape[-1] not in (64, 128) or x.dtype not in _DTYPES or not x.is_cuda:
+        raise ValueError("hadamard_transform expects a CUDA (B, H, T, D) fp16/bf16 tensor with D in {64, 128}")
+    if signs is not None:
+        if signs.shape != (x.shape[1], x.shape[3]):
+            raise ValueError("signs must have shape (heads, head_dim)")
+        signs = signs.to(device=x.device, dtype=torch.float32).contiguous()
+    return _HadamardFn.apply(x, signs)
+
+
+def flash_attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    lens: torch.Tensor | None = None,
+    sm_scale: float | None = None,
+    causal: bool = True,
+    autotune=False,
+    return_lse=False,
+    prescale_qk=False,
+    precision="tf32",
+    attention_mask: torch.Tensor | None = None,
+    in_span: torch.Tensor | None = None,
+    span_id: torch.Tensor | None = None,
+    is_prefix: torch.Tensor | None = None,
+    return_attention_mask: bool = False,
+    hadamard_signs: torch.Tensor | None = None,
+):
+    """Self-attention with the 4-section hierarchical mask; arguments and return value as the
+    reference's ``flash_attention`` (original_kernel.py:2096-2168).
+
+    q, k, v: (batch, heads, time, head_dim), any strides. lens: int32 (batch,) or None.
+    in_span / is_prefix: bool (batch, time); span_id: int64 (batch, time) (1-based span ids, -1 at
+    [MASKQ]). When any of attention_mask / in_span / span_id / is_prefix is given the mask is the
+    rule of original_kernel.py:480-517 and ``causal`` is not part of it; otherwise the mask is
+    ``i >= j`` (causal) or all-ones. ``attention_mask`` itself is never read (as in the reference).
+
+    hadamard_signs (extension, default None): (heads, head_dim) +-1; Q and K are replaced by
+    ``hadamard_transform(., signs)`` before the attention, which leaves Q K^T unchanged in exact
+    arithmetic and spreads outliers over the head dimension.
+
+    Returns O, or (O, LSE) with return_lse, or (that, mask[B,H,T,T] bool) with return_attention_mask.
+    """
+    _check_inputs(q, k, v)
+    B, H, T, D = q.shape
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    sm_scale = float(sm_scale)
+    if not (sm_scale > 0.0 and math.isfinite(sm_scale)):
+        raise ValueError("sm_scale must be positive and finite")
+    rules = any(t is not None for t in (attention_mask, in_span, span_id, is_prefix))
+    plan = get_plan(B, T, q.device, in_span, span_id, is_prefix, lens, causal, rules)
+
+    if hadamard_signs is not None:
+        q = hadamard_transform(q, hadamard_signs)
+        k = hadamard_transform(k, hadamard_signs)
+
+    o, lse = _FlashAttentionFn.apply(q, k, v, plan, sm_scale)
+
+    if return_attention_mask:
+        mask = plan.dense_mask().unsqueeze(1).expand(B, H, T, T)
+        if return_lse:
+            return (o, lse), mask
+        return o, mask
+    if return_lse:
+        return o, lse
+    return o
