@@ -96,6 +96,9 @@ typedef struct kd_attn_params {
   float* delta;      /* (B,H,T) contiguous fp32 scratch of the backward: rowsum(O * dO)
                         (kd_workspace_bytes gives its size) */
   const void* plan;  /* filled by kd_classify for the same (B,T) */
+  int32_t bwd_phases; /* kd_attn_bwd only. 0 or 3: both kernels; 1: the dQ kernel alone (it also
+                         writes delta); 2: the dK/dV kernel alone (reads delta of an earlier dQ
+                         pass). Lets a caller time the two kernels separately. */
 } kd_attn_params;
 
 /* Size and layout of a plan for B sequences of T tokens. */

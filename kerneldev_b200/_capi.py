@@ -53,7 +53,7 @@ class KdAttnParams(Structure):
         ("dtype", c_int32), ("sm_scale", c_float),
         ("q", KdTensor), ("k", KdTensor), ("v", KdTensor), ("o", KdTensor), ("d_o", KdTensor),
         ("dq", KdTensor), ("dk", KdTensor), ("dv", KdTensor),
-        ("lse", c_void_p), ("delta", c_void_p), ("plan", c_void_p),
+        ("lse", c_void_p), ("delta", c_void_p), ("plan", c_void_p), ("bwd_phases", c_int32),
     ]
 
 

@@ -624,8 +624,9 @@ static int launch_bwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
   if (e == cudaSuccess) e = cudaFuncSetAttribute(kk, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_ALLOC);
   if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "bwd smem attribute: %s", cudaGetErrorString(e));
   dim3 grid(L.NT, p.H, p.B);
-  kq<<<grid, 384, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
-  kk<<<grid, 384, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
+  const int phases = (p.bwd_phases & 3) ? (p.bwd_phases & 3) : 3;
+  if (phases & 1) kq<<<grid, 384, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
+  if (phases & 2) kk<<<grid, 384, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "attn_bwd kernels launch: %s", cudaGetErrorString(e));
   return 0;

@@ -28,6 +28,8 @@ import torch
 from . import _capi
 from .plan import AttentionPlan, get_plan
 
+_capi.load()  # fail at import time, loudly, when the CUDA library has not been built
+
 __all__ = ["flash_attention", "generate_hadamard_signs", "hadamard_transform"]
 
 _DTYPES = {torch.float16: _capi.KD_F16, torch.bfloat16: _capi.KD_BF16}
@@ -74,6 +76,7 @@ def _params(q, k, v, o, lse, plan, sm_scale):
 
 
 def _forward(q, k, v, plan: AttentionPlan, sm_scale: float):
+    """One kd_attn_fwd call: returns (O, LSE) for inputs that passed _check_inputs."""
     q, k, v = _usable(q), _usable(k), _usable(v)
     B, H, T, D = q.shape
     o = torch.empty((B, H, T, D), dtype=q.dtype, device=q.device)
@@ -87,17 +90,23 @@ def _forward(q, k, v, plan: AttentionPlan, sm_scale: float):
     return o, lse
 
 
-def _backward(q, k, v, o, lse, d_o, plan: AttentionPlan, sm_scale: float):
+def _backward(q, k, v, o, lse, d_o, plan: AttentionPlan, sm_scale: float, phases: int = 0, bufs=None):
+    """One kd_attn_bwd call: returns (dQ, dK, dV). ``phases`` selects one of the two backward
+    kernels (see kd_attn_params.bwd_phases); ``bufs`` = (dq, dk, dv, delta) reuses buffers."""
     q, k, v, d_o = _usable(q), _usable(k), _usable(v), _usable(d_o)
     B, H, T, D = q.shape
-    dq = torch.empty((B, H, T, D), dtype=q.dtype, device=q.device)
-    dk = torch.empty_like(dq)
-    dv = torch.empty_like(dq)
-    delta = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
+    if bufs is None:
+        dq = torch.empty((B, H, T, D), dtype=q.dtype, device=q.device)
+        dk = torch.empty_like(dq)
+        dv = torch.empty_like(dq)
+        delta = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
+    else:
+        dq, dk, dv, delta = bufs
     p = _params(q, k, v, o, lse, plan, sm_scale)
     p.d_o = _kd_tensor(d_o)
     p.dq, p.dk, p.dv = _kd_tensor(dq), _kd_tensor(dk), _kd_tensor(dv)
     p.delta = delta.data_ptr()
+    p.bwd_phases = phases
     stream = torch.cuda.current_stream(q.device).cuda_stream
     with torch.cuda.device(q.device):
         _capi.check(_capi.load().kd_attn_bwd(ctypes.byref(p), stream))

@@ -116,3 +116,12 @@ def test_hadamard_is_orthogonal_and_preserves_scores():
     hx, hy = ao.hadamard_transform(x, s), ao.hadamard_transform(y, s)
     assert torch.allclose(hx @ hy.transpose(-1, -2), x @ y.transpose(-1, -2), atol=1e-4)
     assert torch.allclose(ao.hadamard_matrix(4), torch.tensor([[1., 1, 1, 1], [1, -1, 1, -1], [1, 1, -1, -1], [1, -1, -1, 1]]))
+
+
+def test_package_generator_equals_oracle_generator():
+    from kerneldev_b200 import synthetic
+    for cfg, (B, T) in {2: (3, 4096), 3: (2, 8192), 4: (3, 2048)}.items():
+        a = ao.batch_metadata(9, B, T, **ao.CONFIG_RANGES[cfg])
+        b = synthetic.batch_metadata(9, B, T, **synthetic.CONFIG_RANGES[cfg])
+        for x, y in zip(a, b):
+            assert np.array_equal(x, y) and x.dtype == y.dtype
