@@ -73,6 +73,8 @@ typedef struct kd_plan_layout {
   size_t off_fwd_list;   /* uint16 [B][NP][NT]   k_tile | class(q tile 2p) << 8 | class(2p+1) << 10 */
   size_t off_bwd_cnt;    /* int32  [B][NT]       entries in the backward list of a k tile */
   size_t off_bwd_list;   /* uint16 [B][NT][NT]   q_tile | class << 8 */
+  size_t off_order;      /* uint8  [B][3][NT]    tiles sorted by decreasing work: [0] forward q tile
+                                                 pairs, [1] dQ q tiles, [2] dK/dV k tiles */
   size_t off_stats;      /* uint32 [B][2]        number of FULL and of PARTIAL tiles */
   size_t off_status;     /* uint32               device status word (0 = ok) */
   size_t total;          /* bytes the caller must provide (256-byte aligned base) */

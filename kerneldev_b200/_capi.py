@@ -6,6 +6,7 @@ the operator fails with an error that says how to build it. There is no fallback
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import (POINTER, Structure, c_char_p, c_float, c_int32, c_int64, c_size_t, c_uint8,
                     c_void_p)
 from pathlib import Path
@@ -16,7 +17,8 @@ KD_TILE_EMPTY, KD_TILE_FULL, KD_TILE_PARTIAL = 0, 1, 2
 KD_STATUS_TIMEOUT = 0x10000000
 KD_STATUS_SPAN_RANGE = 0x20000000
 
-LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libkd_attention.so"
+# KD_LIB_PATH selects another build of the same library (e.g. the timeline build of build.py --trace)
+LIB_PATH = Path(os.environ.get("KD_LIB_PATH") or Path(__file__).resolve().parent / "_lib" / "libkd_attention.so")
 
 EXPORTS = (
     "kd_version", "kd_last_error", "kd_plan_layout_get", "kd_classify", "kd_mask_dense",
@@ -38,7 +40,7 @@ class KdPlanLayout(Structure):
         ("B", c_int32), ("T", c_int32), ("NT", c_int32), ("NP", c_int32),
         ("off_desc", c_size_t), ("off_summary", c_size_t), ("off_cls", c_size_t),
         ("off_fwd_cnt", c_size_t), ("off_fwd_list", c_size_t), ("off_bwd_cnt", c_size_t),
-        ("off_bwd_list", c_size_t), ("off_stats", c_size_t), ("off_status", c_size_t),
+        ("off_bwd_list", c_size_t), ("off_order", c_size_t), ("off_stats", c_size_t), ("off_status", c_size_t),
         ("total", c_size_t),
     ]
 

@@ -44,18 +44,22 @@ def _stale() -> bool:
     return any(d.stat().st_mtime > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compiles every CUDA source for sm_100a and links the shared library. Returns its path."""
-    if not force and not _stale():
+def build(force: bool = False, verbose: bool = False, trace: bool = False) -> Path:
+    """Compiles every CUDA source for sm_100a and links the shared library. Returns its path.
+
+    ``trace=True`` builds the variant with in-kernel timelines (-DKD_TRACE) as
+    libkd_attention_trace.so; it is a debugging aid and is never loaded by the package itself."""
+    lib_path = LIB_DIR / "libkd_attention_trace.so" if trace else LIB_PATH
+    if not trace and not force and not _stale():
         return LIB_PATH
     LIB_DIR.mkdir(exist_ok=True)
-    obj_dir = LIB_DIR / "obj"
+    obj_dir = LIB_DIR / ("obj_trace" if trace else "obj")
     obj_dir.mkdir(exist_ok=True)
     nvcc = _nvcc()
 
     def compile_one(src: str) -> Path:
         obj = obj_dir / (src + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-c", str(CSRC / src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, *(["-DKD_TRACE"] if trace else []), "-c", str(CSRC / src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         r = subprocess.run(cmd, capture_output=True, text=True)
@@ -67,13 +71,13 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=len(SOURCES)) as ex:
         objs = list(ex.map(compile_one, SOURCES))
-    cmd = [nvcc, "-shared", "-o", str(LIB_PATH), *map(str, objs), "-cudart", "shared"]
+    cmd = [nvcc, "-shared", "-o", str(lib_path), *map(str, objs), "-cudart", "shared"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
-    p = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    p = build(force="--force" in sys.argv, verbose="-v" in sys.argv, trace="--trace" in sys.argv)
     print(p)

@@ -14,9 +14,7 @@
 // other stream's MMAs:
 //   M1(i): S_i, dP_i  (smem x smem -> TMEM, N = 64)      compute(i): P_i / dS_i -> TMEM (16 bit)
 //   M2(i): accumulators += (P_i | dS_i) x smem operand   (A from TMEM)
-#include "common.cuh"
-#include "mask_rule.cuh"
-#include "sm100_prims.cuh"
+#include "attn_common.cuh"
 
 namespace kd {
 
@@ -29,6 +27,7 @@ struct BwdArgs {
   const uint16_t* fwd_list;
   const int32_t* bwd_cnt;
   const uint16_t* bwd_list;
+  const uint8_t* order;   // [B][3][NT]; row 1 = q tiles, row 2 = k tiles, by decreasing list length
   uint32_t* status;
   const void* o;
   int64_t o_sb, o_sh, o_st;
@@ -42,6 +41,7 @@ struct BwdArgs {
   int64_t dk_sb, dk_sh, dk_st;
   void* dv;
   int64_t dv_sb, dv_sh, dv_st;
+  unsigned long long* trace;  // timeline buffer of KD_TRACE builds, else null
 };
 
 template <int HD>
@@ -69,20 +69,6 @@ enum : uint32_t {
   W_K_ACCFULL = 0x306,
 };
 
-// stores 32 fp32 accumulator values (scaled) as 16-bit elements to a row in global memory
-template <bool kBf16>
-__device__ __forceinline__ void store_row32(uint16_t* dst, const uint32_t (&r)[32], float f) {
-#pragma unroll
-  for (int j = 0; j < 32; j += 8) {
-    uint4 v;
-    v.x = pack2<kBf16>(__uint_as_float(r[j + 0]) * f, __uint_as_float(r[j + 1]) * f);
-    v.y = pack2<kBf16>(__uint_as_float(r[j + 2]) * f, __uint_as_float(r[j + 3]) * f);
-    v.z = pack2<kBf16>(__uint_as_float(r[j + 4]) * f, __uint_as_float(r[j + 5]) * f);
-    v.w = pack2<kBf16>(__uint_as_float(r[j + 6]) * f, __uint_as_float(r[j + 7]) * f);
-    *reinterpret_cast<uint4*>(dst + j) = v;
-  }
-}
-
 // =========================================================================================
 // dQ kernel: one CTA per (b, h, query tile); streams = key halves of the current key tile.
 //   M1(i): S_i = Q K_i^T, dP_i = dO V_i^T      M2(i): dQ += dS_i K_i
@@ -108,7 +94,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   __shared__ AbortFlag abortf;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int qt = a.order[((size_t)b * 3 + 1) * a.NT + blockIdx.z];   // longest lists first
   const int pair = qt >> 1, ip = qt & 1;
 
   if (tid == 0) {
@@ -149,6 +136,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tc_fence_after_sync();
   const uint32_t tbase = tmem_base_s;
   const int na = n_act_s;
+  Tracer tr;
+  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 0 || warp == 1 || warp == 4 || warp == 8),
+          blockIdx.z * 4 + (warp == 0 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));
+  tr.ev(1);
 
   if (warp < 4) {
     reg_dealloc<56>();
@@ -189,24 +180,25 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const uint32_t tS[2] = {tbase + C::TM_S0, tbase + C::TM_S1};
       const uint32_t tP[2] = {tbase + C::TM_P0, tbase + C::TM_P1};
       const uint32_t tAcc = tbase + C::TM_ACC0;
+      const uint32_t hi = desc_hi_sw128();
+      const uint32_t loQ = desc_lo_kmajor(sQ), loDO = desc_lo_kmajor(sDO);
+      const uint32_t loRingK = desc_lo_kmajor(sRing), loRingMN = desc_lo_mnmajor(sRing);
       auto issue_m1 = [&](int i, int e) {
-        const uint32_t kb_base = sRing + (e % C::STAGES) * 2 * C::TILE_BYTES + i * 64 * 128;  // key rows 64i..
-        const uint32_t vb_base = kb_base + C::TILE_BYTES;
+        const uint32_t kb = loRingK + (e % C::STAGES) * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);  // key rows 64i..
+        const uint32_t vb = kb + (C::TILE_BYTES >> 4);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss(tS[i], desc_kmajor_sw128(sQ + (kk / 4) * 16384, kk % 4),
-                 desc_kmajor_sw128(kb_base + (kk / 4) * 16384, kk % 4), idesc_m1, kk > 0);
+          mma_ss_split(tS[i], loQ + koff_kmajor(kk), kb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss(tP[i], desc_kmajor_sw128(sDO + (kk / 4) * 16384, kk % 4),
-                 desc_kmajor_sw128(vb_base + (kk / 4) * 16384, kk % 4), idesc_m1, kk > 0);
+          mma_ss_split(tP[i], loDO + koff_kmajor(kk), vb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
         mma_commit(smem_u32(&bar_s_full[i]));
       };
       auto issue_m2 = [&](int i, int e, bool acc) {
-        const uint32_t kb_base = sRing + (e % C::STAGES) * 2 * C::TILE_BYTES + i * 64 * 128;
+        const uint32_t kb = loRingMN + (e % C::STAGES) * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // 64 keys of this stream, 16 per MMA; dS_i sits on top of S_i
-          mma_ts(tAcc, tS[i] + kk * 8, desc_mnmajor_sw128(kb_base, kk, 16384), idesc_m2, (acc || kk > 0) ? 1u : 0u);
+          mma_ts_split(tAcc, tS[i] + kk * 8, kb + koff_mnmajor(kk), hi, idesc_m2, (acc || kk > 0) ? 1u : 0u);
       };
       bool ok = mbar_wait(smem_u32(&bar_fix_full), 0, &abortf, a.status, W_Q_FIXFULL);
       if (ok) ok = mbar_wait(smem_u32(&bar_ring_full[0]), 0, &abortf, a.status, W_Q_RINGFULL);
@@ -222,6 +214,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int i = 0; i < 2; ++i) {
           ok = mbar_wait(smem_u32(&bar_p_full[i]), pphase, &abortf, a.status, W_Q_PFULL);
           if (!ok) break;
+          tr.ev(10 + 2 * i);
           tc_fence_after_sync();
           issue_m2(i, e, e > 0 || i > 0);
           if (e + 1 < na) {
@@ -234,6 +227,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             }
             issue_m1(i, e + 1);
           }
+          tr.ev(11 + 2 * i);
         }
         if (!ok) break;
         pphase ^= 1;
@@ -279,6 +273,17 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     uint32_t sphase = 0;
     bool ok = true;
 
+    // key descriptors of PARTIAL tiles are fetched one entry ahead into registers
+    uint32_t kd_pre[2] = {0u, 0u};
+    auto prefetch_kd = [&](int e) {
+      if (e < na && (sAct[e] >> 8) == KD_TILE_PARTIAL) {
+        const uint32_t* src = a.desc + (size_t)b * a.Tpad + (size_t)(sAct[e] & 0xFFu) * KD_TILE + i * 64;
+        kd_pre[0] = src[lane];
+        kd_pre[1] = src[32 + lane];
+      }
+    };
+    prefetch_kd(0);
+
     for (int e = 0; e < na; ++e) {
       const uint32_t ent = sAct[e];
       const uint32_t cls = ent >> 8;
@@ -286,16 +291,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int j0 = kt * KD_TILE + i * 64;  // first key of this stream
       if (cls == KD_TILE_PARTIAL) {
         __syncwarp();
-        const uint32_t* src = a.desc + (size_t)b * a.Tpad + j0;
-        kd_buf[lane] = src[lane];
-        kd_buf[32 + lane] = src[32 + lane];
+        kd_buf[lane] = kd_pre[0];
+        kd_buf[32 + lane] = kd_pre[1];
         __syncwarp();
       }
+      prefetch_kd(e + 1);
+      tr.ev(21);
       ok = mbar_wait(smem_u32(&bar_s_full[i]), sphase, &abortf, a.status, W_Q_SFULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       sphase ^= 1;
       tc_fence_after_sync();
+      tr.ev(22);
 
       uint32_t pk[32];
 #pragma unroll
@@ -305,22 +312,30 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tmem_ld32(tP + cb * 32, rp);
         tmem_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(rs[j]), c, neg_lse));
-          float p1 = fast_exp2(fmaf(__uint_as_float(rs[j + 1]), c, neg_lse));
+        for (int j = 0; j < 32; j += 4) {
+          float pv[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) pv[u] = fast_exp2(fmaf(__uint_as_float(rs[j + u]), c, neg_lse));
           if (cls == KD_TILE_PARTIAL) {
-            if (!rule_allowed(qd, qi, kd_buf[cb * 32 + j], j0 + cb * 32 + j)) p0 = 0.f;
-            if (!rule_allowed(qd, qi, kd_buf[cb * 32 + j + 1], j0 + cb * 32 + j + 1)) p1 = 0.f;
+            const uint4 k4 = *reinterpret_cast<const uint4*>(kd_buf + cb * 32 + j);
+            const uint32_t kw[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (!rule_allowed(qd, qi, kw[u], j0 + cb * 32 + j + u)) pv[u] = 0.f;
           }
-          const float ds0 = p0 * (__uint_as_float(rp[j]) - delta);
-          const float ds1 = p1 * (__uint_as_float(rp[j + 1]) - delta);
-          pk[cb * 16 + j / 2] = pack2<kBf16>(ds0, ds1);
+          float ds[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) ds[u] = pv[u] * (__uint_as_float(rp[j + u]) - delta);
+          pk[cb * 16 + j / 2] = pack2<kBf16>(ds[0], ds[1]);
+          pk[cb * 16 + j / 2 + 1] = pack2<kBf16>(ds[2], ds[3]);
         }
       }
+      tr.ev(24);
       tmem_st32(tS, pk);   // dS_i as 16-bit A operand on top of S_i (this thread's own row)
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&bar_p_full[i]));
+      tr.ev(25);
     }
 
     // epilogue: this warpgroup stores columns [i*HD/2, (i+1)*HD/2) of dQ
@@ -346,6 +361,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   }
 
+  tr.ev(31);
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tbase, 512);
@@ -367,6 +383,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t sV = sK + C::TILE_BYTES;
   const uint32_t sRing = smem_u32(smem + C::SMEM_RING);  // stage s: Q at +0, dO at +TILE_BYTES
   uint32_t* sStage = reinterpret_cast<uint32_t*>(smem + C::SMEM_STAGE);
+  uint16_t* sList = reinterpret_cast<uint16_t*>(smem + C::SMEM_ACT);
 
   __shared__ __align__(8) uint64_t bar_fix_full, bar_ring_full[C::STAGES], bar_ring_empty[C::STAGES],
       bar_s_full[2], bar_p_full[2], bar_acc_full;
@@ -374,9 +391,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   __shared__ AbortFlag abortf;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int kt = a.order[((size_t)b * 3 + 2) * a.NT + blockIdx.z];   // longest lists first
   const int n = a.bwd_cnt[b * a.NT + kt];
-  const uint16_t* list = a.bwd_list + ((size_t)b * a.NT + kt) * a.NT;
 
   if (tid == 0) {
     abortf.v = 0;
@@ -396,10 +413,19 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     tmem_alloc(smem_u32(&tmem_base_s), 512);
     tmem_relinquish();
   }
+  if (warp == 2) {
+    const uint16_t* glist = a.bwd_list + ((size_t)b * a.NT + kt) * a.NT;
+    for (int e = lane; e < n; e += 32) sList[e] = glist[e];
+  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tbase = tmem_base_s;
+  const uint16_t* list = sList;
+  Tracer tr;
+  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 0 || warp == 1 || warp == 4 || warp == 8),
+          blockIdx.z * 4 + (warp == 0 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));
+  tr.ev(1);
 
   if (warp < 4) {
     reg_dealloc<56>();
@@ -420,6 +446,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const uint32_t ph = (e / C::STAGES) & 1;
         const int qt = list[e] & 0xFF;
         if (!mbar_wait(smem_u32(&bar_ring_empty[s]), ph ^ 1, &abortf, a.status, W_K_RINGEMPTY)) break;
+        tr.ev(40);
         mbar_arrive_expect_tx(smem_u32(&bar_ring_full[s]), 2 * C::TILE_BYTES);
         const uint32_t dst = sRing + s * 2 * C::TILE_BYTES;
         for (int kb = 0; kb < C::KBLK; ++kb) {
@@ -440,36 +467,39 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const uint32_t tS[2] = {tbase + C::TM_S0, tbase + C::TM_S1};
       const uint32_t tP[2] = {tbase + C::TM_P0, tbase + C::TM_P1};
       const uint32_t tDK = tbase + C::TM_ACC0, tDV = tbase + C::TM_ACC1;
+      const uint32_t hi = desc_hi_sw128();
+      const uint32_t loK = desc_lo_kmajor(sK), loV = desc_lo_kmajor(sV);
+      const uint32_t loRingK = desc_lo_kmajor(sRing), loRingMN = desc_lo_mnmajor(sRing);
       auto issue_m1 = [&](int i, int e) {
-        const uint32_t qb = sRing + (e % C::STAGES) * 2 * C::TILE_BYTES + i * 64 * 128;  // query rows 64i..
-        const uint32_t dob = qb + C::TILE_BYTES;
+        const uint32_t qb = loRingK + (e % C::STAGES) * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);  // query rows 64i..
+        const uint32_t dob = qb + (C::TILE_BYTES >> 4);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss(tS[i], desc_kmajor_sw128(sK + (kk / 4) * 16384, kk % 4),
-                 desc_kmajor_sw128(qb + (kk / 4) * 16384, kk % 4), idesc_m1, kk > 0);
+          mma_ss_split(tS[i], loK + koff_kmajor(kk), qb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss(tP[i], desc_kmajor_sw128(sV + (kk / 4) * 16384, kk % 4),
-                 desc_kmajor_sw128(dob + (kk / 4) * 16384, kk % 4), idesc_m1, kk > 0);
+          mma_ss_split(tP[i], loV + koff_kmajor(kk), dob + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
         mma_commit(smem_u32(&bar_s_full[i]));
       };
       auto issue_m2 = [&](int i, int e, bool acc) {
-        const uint32_t qb = sRing + (e % C::STAGES) * 2 * C::TILE_BYTES + i * 64 * 128;
-        const uint32_t dob = qb + C::TILE_BYTES;
+        const uint32_t qb = loRingMN + (e % C::STAGES) * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
+        const uint32_t dob = qb + (C::TILE_BYTES >> 4);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // dV += P^T_i dO_i   (P^T_i on top of S^T_i)
-          mma_ts(tDV, tS[i] + kk * 8, desc_mnmajor_sw128(dob, kk, 16384), idesc_m2, (acc || kk > 0) ? 1u : 0u);
+          mma_ts_split(tDV, tS[i] + kk * 8, dob + koff_mnmajor(kk), hi, idesc_m2, (acc || kk > 0) ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // dK += dS^T_i Q_i   (dS^T_i on top of dP^T_i)
-          mma_ts(tDK, tP[i] + kk * 8, desc_mnmajor_sw128(qb, kk, 16384), idesc_m2, (acc || kk > 0) ? 1u : 0u);
+          mma_ts_split(tDK, tP[i] + kk * 8, qb + koff_mnmajor(kk), hi, idesc_m2, (acc || kk > 0) ? 1u : 0u);
       };
       bool ok = mbar_wait(smem_u32(&bar_fix_full), 0, &abortf, a.status, W_K_FIXFULL);
       if (ok) ok = mbar_wait(smem_u32(&bar_ring_full[0]), 0, &abortf, a.status, W_K_RINGFULL);
+      tr.ev(2);
       if (ok) {
         tc_fence_after_sync();
         issue_m1(0, 0);
         issue_m1(1, 0);
       }
+      tr.ev(3);
       uint32_t pphase = 0;
       for (int e = 0; e < n && ok; ++e) {
         bool ring_waited = false;
@@ -477,6 +507,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         for (int i = 0; i < 2; ++i) {
           ok = mbar_wait(smem_u32(&bar_p_full[i]), pphase, &abortf, a.status, W_K_PFULL);
           if (!ok) break;
+          tr.ev(10 + 2 * i);
           tc_fence_after_sync();
           issue_m2(i, e, e > 0 || i > 0);
           if (e + 1 < n) {
@@ -489,6 +520,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             }
             issue_m1(i, e + 1);
           }
+          tr.ev(11 + 2 * i);
         }
         if (!ok) break;
         pphase ^= 1;
@@ -514,26 +546,47 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     uint32_t sphase = 0;
     bool ok = true;
 
+    // -LSE, delta and the descriptors of the next entry's 64 queries are fetched one entry ahead
+    // into registers and handed to the warp through its shared-memory staging buffer
+    float pre_lse[2] = {0.f, 0.f}, pre_delta[2] = {0.f, 0.f};
+    uint32_t pre_desc[2] = {0u, 0u};
+    auto prefetch = [&](int e) {
+      if (e < n) {
+        const int q0 = (list[e] & 0xFF) * KD_TILE + i * 64;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const int q = q0 + r * 32 + lane;
+          const bool v = q < a.T;
+          pre_lse[r] = v ? -a.lse[bh * a.T + q] : 0.f;
+          pre_delta[r] = v ? a.delta[bh * a.T + q] : 0.f;
+          pre_desc[r] = a.desc[(size_t)b * a.Tpad + q];
+        }
+      }
+    };
+    prefetch(0);
+
     for (int e = 0; e < n; ++e) {
       const uint32_t ent = list[e];
       const uint32_t cls = ent >> 8;
       const int qt = ent & 0xFF;
       const int i0 = qt * KD_TILE + i * 64;  // first query of this stream
+      tr.ev(20);
       __syncwarp();
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
-        const int q = i0 + r * 32 + lane;
-        const bool v = q < a.T;
-        st_buf[r * 32 + lane] = __float_as_uint(v ? -a.lse[bh * a.T + q] : 0.f);
-        st_buf[64 + r * 32 + lane] = __float_as_uint(v ? a.delta[bh * a.T + q] : 0.f);
-        st_buf[128 + r * 32 + lane] = a.desc[(size_t)b * a.Tpad + q];
+        st_buf[r * 32 + lane] = __float_as_uint(pre_lse[r]);
+        st_buf[64 + r * 32 + lane] = __float_as_uint(pre_delta[r]);
+        st_buf[128 + r * 32 + lane] = pre_desc[r];
       }
       __syncwarp();
+      prefetch(e + 1);
+      tr.ev(21);
       ok = mbar_wait(smem_u32(&bar_s_full[i]), sphase, &abortf, a.status, W_K_SFULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       sphase ^= 1;
       tc_fence_after_sync();
+      tr.ev(22);
 
       uint32_t pk_p[32], pk_ds[32];
 #pragma unroll
@@ -543,25 +596,36 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tmem_ld32(tP + cb * 32, rp);
         tmem_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
+        for (int j = 0; j < 32; j += 4) {
           const int jj = cb * 32 + j;
-          float p0 = fast_exp2(fmaf(__uint_as_float(rs[j]), c, __uint_as_float(st_buf[jj])));
-          float p1 = fast_exp2(fmaf(__uint_as_float(rs[j + 1]), c, __uint_as_float(st_buf[jj + 1])));
+          const float4 l4 = *reinterpret_cast<const float4*>(st_buf + jj);
+          const float4 d4 = *reinterpret_cast<const float4*>(st_buf + 64 + jj);
+          const float lw[4] = {l4.x, l4.y, l4.z, l4.w}, dw[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pv[4], ds[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) pv[u] = fast_exp2(fmaf(__uint_as_float(rs[j + u]), c, lw[u]));
           if (cls == KD_TILE_PARTIAL) {
-            if (!rule_allowed(st_buf[128 + jj], i0 + jj, kdesc, kj)) p0 = 0.f;
-            if (!rule_allowed(st_buf[128 + jj + 1], i0 + jj + 1, kdesc, kj)) p1 = 0.f;
+            const uint4 q4 = *reinterpret_cast<const uint4*>(st_buf + 128 + jj);
+            const uint32_t qw[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (!rule_allowed(qw[u], i0 + jj + u, kdesc, kj)) pv[u] = 0.f;
           }
-          const float ds0 = p0 * (__uint_as_float(rp[j]) - __uint_as_float(st_buf[64 + jj]));
-          const float ds1 = p1 * (__uint_as_float(rp[j + 1]) - __uint_as_float(st_buf[64 + jj + 1]));
-          pk_p[cb * 16 + j / 2] = pack2<kBf16>(p0, p1);
-          pk_ds[cb * 16 + j / 2] = pack2<kBf16>(ds0, ds1);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) ds[u] = pv[u] * (__uint_as_float(rp[j + u]) - dw[u]);
+          pk_p[cb * 16 + j / 2] = pack2<kBf16>(pv[0], pv[1]);
+          pk_p[cb * 16 + j / 2 + 1] = pack2<kBf16>(pv[2], pv[3]);
+          pk_ds[cb * 16 + j / 2] = pack2<kBf16>(ds[0], ds[1]);
+          pk_ds[cb * 16 + j / 2 + 1] = pack2<kBf16>(ds[2], ds[3]);
         }
       }
+      tr.ev(24);
       tmem_st32(tS, pk_p);    // P^T_i on top of S^T_i
       tmem_st32(tP, pk_ds);   // dS^T_i on top of dP^T_i
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&bar_p_full[i]));
+      tr.ev(25);
     }
 
     // epilogue: this warpgroup stores columns [i*HD/2, (i+1)*HD/2) of dK and dV
@@ -569,6 +633,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       ok = mbar_wait(smem_u32(&bar_acc_full), 0, &abortf, a.status, W_K_ACCFULL);
       ok = __all_sync(0xffffffffu, ok);
     }
+    tr.ev(30);
     if (ok) {
       tc_fence_after_sync();
       uint16_t* krow = reinterpret_cast<uint16_t*>(a.dk) + (size_t)b * a.dk_sb + (size_t)h * a.dk_sh + (size_t)kj * a.dk_st + i * (HD / 2);
@@ -592,6 +657,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
   }
 
+  tr.ev(31);
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tbase, 512);
@@ -611,19 +677,20 @@ static int launch_bwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
   a.scale_log2 = p.sm_scale * 1.4426950408889634f;
   a.sm_scale = p.sm_scale;
   a.desc = pv.desc; a.fwd_cnt = pv.fwd_cnt; a.fwd_list = pv.fwd_list;
-  a.bwd_cnt = pv.bwd_cnt; a.bwd_list = pv.bwd_list; a.status = pv.status;
+  a.bwd_cnt = pv.bwd_cnt; a.bwd_list = pv.bwd_list; a.status = pv.status; a.order = pv.order;
   a.o = p.o.ptr; a.o_sb = p.o.stride_b; a.o_sh = p.o.stride_h; a.o_st = p.o.stride_t;
   a.d_o = p.d_o.ptr; a.do_sb = p.d_o.stride_b; a.do_sh = p.d_o.stride_h; a.do_st = p.d_o.stride_t;
   a.lse = p.lse; a.delta = p.delta;
   a.dq = p.dq.ptr; a.dq_sb = p.dq.stride_b; a.dq_sh = p.dq.stride_h; a.dq_st = p.dq.stride_t;
   a.dk = p.dk.ptr; a.dk_sb = p.dk.stride_b; a.dk_sh = p.dk.stride_h; a.dk_st = p.dk.stride_t;
   a.dv = p.dv.ptr; a.dv_sb = p.dv.stride_b; a.dv_sh = p.dv.stride_h; a.dv_st = p.dv.stride_t;
+  a.trace = trace_buffer();
   auto kq = attn_bwd_dq_kernel<HD, kBf16>;
   auto kk = attn_bwd_dkdv_kernel<HD, kBf16>;
   cudaError_t e = cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_ALLOC);
   if (e == cudaSuccess) e = cudaFuncSetAttribute(kk, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_ALLOC);
   if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "bwd smem attribute: %s", cudaGetErrorString(e));
-  dim3 grid(L.NT, p.H, p.B);
+  dim3 grid(p.H, p.B, L.NT);
   const int phases = (p.bwd_phases & 3) ? (p.bwd_phases & 3) : 3;
   if (phases & 1) kq<<<grid, 384, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
   if (phases & 2) kk<<<grid, 384, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);

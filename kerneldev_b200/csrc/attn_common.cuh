@@ -1,0 +1,73 @@
+// Device helpers shared by the forward and backward attention kernels: pre-split shared-memory
+// descriptors (so the single MMA-issuing thread spends two integer adds per MMA, not a 64-bit
+// descriptor build), work-list staging, 16-bit row stores.
+#pragma once
+#include "common.cuh"
+#include "mask_rule.cuh"
+#include "sm100_prims.cuh"
+
+namespace kd {
+
+// High words of the two descriptor kinds used here (layout, version, stride byte offset 1024);
+// the low word carries the start address and the leading byte offset.
+__device__ __forceinline__ uint32_t desc_hi_sw128() {
+  return static_cast<uint32_t>(make_smem_desc(0, 0, 1024, KD_LAYOUT_SW128) >> 32);
+}
+// low word of a K-major tile descriptor at k-step 0 (leading byte offset field = 1)
+__device__ __forceinline__ uint32_t desc_lo_kmajor(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | (1u << 16); }
+// low word of an MN-major tile descriptor whose 64-wide MN blocks are 16 KB apart
+__device__ __forceinline__ uint32_t desc_lo_mnmajor(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | (1024u << 16); }
+// offset (in 16-byte units) of k-step kk inside a K-major tile built from [rows][64] blocks 16 KB apart
+__device__ __forceinline__ constexpr uint32_t koff_kmajor(int kk) { return static_cast<uint32_t>((kk / 4) * 1024 + (kk % 4) * 2); }
+// offset (16-byte units) of k-step kk (16 rows of 128 bytes) inside an MN-major tile
+__device__ __forceinline__ constexpr uint32_t koff_mnmajor(int kk) { return static_cast<uint32_t>(kk * 128); }
+
+__device__ __forceinline__ void mma_ss_split(uint32_t d_tmem, uint32_t alo, uint32_t blo, uint32_t hi,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 da, db;\n"
+      "mov.b64 da, {%1, %3};\n"
+      "mov.b64 db, {%2, %3};\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n"
+      "}\n"
+      ::"r"(d_tmem), "r"(alo), "r"(blo), "r"(hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_split(uint32_t d_tmem, uint32_t a_tmem, uint32_t blo, uint32_t hi,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 db;\n"
+      "mov.b64 db, {%2, %3};\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(blo), "r"(hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// stores 32 fp32 accumulator values (scaled) as 16-bit elements to a row in global memory
+template <bool kBf16>
+__device__ __forceinline__ void store_row32(uint16_t* dst, const uint32_t (&r)[32], float f) {
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    uint4 v;
+    v.x = pack2<kBf16>(__uint_as_float(r[j + 0]) * f, __uint_as_float(r[j + 1]) * f);
+    v.y = pack2<kBf16>(__uint_as_float(r[j + 2]) * f, __uint_as_float(r[j + 3]) * f);
+    v.z = pack2<kBf16>(__uint_as_float(r[j + 4]) * f, __uint_as_float(r[j + 5]) * f);
+    v.w = pack2<kBf16>(__uint_as_float(r[j + 6]) * f, __uint_as_float(r[j + 7]) * f);
+    *reinterpret_cast<uint4*>(dst + j) = v;
+  }
+}
+
+// bounded wait used while unwinding after an abort: lets a TMA copy that is already in flight land
+__device__ __forceinline__ void drain_wait(uint32_t bar, uint32_t parity) {
+  for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(bar, parity); ++spin) {
+  }
+}
+
+}  // namespace kd

@@ -12,9 +12,7 @@
 // Replaces _flash_attn_fwd (original_kernel.py:278-626): same math (scores scaled by
 // sm_scale*log2(e), exp2, LSE = m + log2(l)), rows without any visible key give O = 0 and
 // LSE = -inf.
-#include "common.cuh"
-#include "mask_rule.cuh"
-#include "sm100_prims.cuh"
+#include "attn_common.cuh"
 
 namespace kd {
 
@@ -24,6 +22,8 @@ struct FwdArgs {
   const uint32_t* desc;
   const int32_t* fwd_cnt;
   const uint16_t* fwd_list;
+  const uint8_t* order;   // [B][3][NT]; row 0 = pairs sorted by decreasing list length
+  unsigned long long* trace;
   uint32_t* status;
   void* o;
   int64_t o_sb, o_sh, o_st;
@@ -38,8 +38,9 @@ struct FwdCfg {
   static constexpr int SMEM_Q = 0;
   static constexpr int SMEM_K = SMEM_Q + 2 * TILE_BYTES;
   static constexpr int SMEM_V = SMEM_K + STAGES * TILE_BYTES;
-  static constexpr int SMEM_KDESC = SMEM_V + STAGES * TILE_BYTES;  // 8 warps x 2 buffers x 128 u32
-  static constexpr int SMEM_TOTAL = SMEM_KDESC + 8 * 2 * KD_TILE * 4;
+  static constexpr int SMEM_KDESC = SMEM_V + STAGES * TILE_BYTES;  // 8 warps x 128 u32
+  static constexpr int SMEM_LIST = SMEM_KDESC + 8 * KD_TILE * 4;     // the pair's work list (<= 128 entries)
+  static constexpr int SMEM_TOTAL = SMEM_LIST + 128 * 2;
   static constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;   // slack for 1024-byte alignment
   // TMEM columns: S0, S1 (128 each, fp32), O0, O1 (HD each); P as 64 columns of packed pairs,
   // in its own region for HD = 64, on top of S for HD = 128 (the tensor pipe runs in order, so
@@ -67,6 +68,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t sK = smem_u32(smem + C::SMEM_K);
   const uint32_t sV = smem_u32(smem + C::SMEM_V);
   uint32_t* sKdesc = reinterpret_cast<uint32_t*>(smem + C::SMEM_KDESC);
+  uint16_t* sList = reinterpret_cast<uint16_t*>(smem + C::SMEM_LIST);
 
   __shared__ __align__(8) uint64_t bar_q_full, bar_k_full[C::STAGES], bar_k_empty[C::STAGES],
       bar_v_full[C::STAGES], bar_v_empty[C::STAGES], bar_s_full[2], bar_p_full[2], bar_o_full[2];
@@ -74,9 +76,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __shared__ AbortFlag abortf;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int pair = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  // blockIdx.z walks the pairs from the longest list to the shortest, so the CTAs that take
+  // longest are dispatched first
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int pair = a.order[((size_t)b * 3 + 0) * a.NT + blockIdx.z];
   const int n = a.fwd_cnt[b * a.NP + pair];
-  const uint16_t* list = a.fwd_list + ((size_t)b * a.NP + pair) * a.NT;
 
   if (tid == 0) {
     abortf.v = 0;
@@ -98,10 +102,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tmem_alloc(smem_u32(&tmem_base_s), 512);
     tmem_relinquish();
   }
+  if (warp == 2) {
+    const uint16_t* list = a.fwd_list + ((size_t)b * a.NP + pair) * a.NT;
+    for (int e = lane; e < n; e += 32) sList[e] = list[e];
+  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tbase = tmem_base_s;
+  const uint16_t* list = sList;
+  Tracer tr;
+  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 0 || warp == 1 || warp == 4 || warp == 8),
+          blockIdx.z * 4 + (warp == 0 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));
+  tr.ev(1);
 
   if (warp < 4) {
     reg_dealloc<56>();
@@ -157,19 +170,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t tS[2] = {tbase + C::TM_S0, tbase + C::TM_S1};
       const uint32_t tO[2] = {tbase + C::TM_O0, tbase + C::TM_O1};
       const uint32_t tP[2] = {tbase + C::TM_P0, tbase + C::TM_P1};
+      const uint32_t hi = desc_hi_sw128();
+      const uint32_t loQ[2] = {desc_lo_kmajor(sQ), desc_lo_kmajor(sQ + C::TILE_BYTES)};
+      const uint32_t loK0 = desc_lo_kmajor(sK), loV0 = desc_lo_mnmajor(sV);
       auto issue_s = [&](int i, int e) {
-        const uint32_t qb = sQ + i * C::TILE_BYTES, kbase = sK + (e % C::STAGES) * C::TILE_BYTES;
+        const uint32_t kb = loK0 + (e % C::STAGES) * (C::TILE_BYTES >> 4);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss(tS[i], desc_kmajor_sw128(qb + (kk / 4) * 16384, kk % 4),
-                 desc_kmajor_sw128(kbase + (kk / 4) * 16384, kk % 4), idesc_s, kk > 0);
+          mma_ss_split(tS[i], loQ[i] + koff_kmajor(kk), kb + koff_kmajor(kk), hi, idesc_s, kk > 0 ? 1u : 0u);
         mma_commit(smem_u32(&bar_s_full[i]));
       };
       auto issue_pv = [&](int i, int e, bool acc) {
-        const uint32_t vbase = sV + (e % C::STAGES) * C::TILE_BYTES;
+        const uint32_t vb = loV0 + (e % C::STAGES) * (C::TILE_BYTES >> 4);
 #pragma unroll
         for (int kk = 0; kk < KD_TILE / 16; ++kk)
-          mma_ts(tO[i], tP[i] + kk * 8, desc_mnmajor_sw128(vbase, kk, 16384), idesc_o, (acc || kk > 0) ? 1u : 0u);
+          mma_ts_split(tO[i], tP[i] + kk * 8, vb + koff_mnmajor(kk), hi, idesc_o, (acc || kk > 0) ? 1u : 0u);
       };
       int last_act[2] = {-1, -1};
       for (int e = 0; e < n; ++e) {
@@ -204,6 +219,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               if (!ok) break;
               v_waited = true;
             }
+            tr.ev(10 + 2 * i);
             tc_fence_after_sync();
             issue_pv(i, e, used[i]);
             used[i] = true;
@@ -219,6 +235,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             }
             issue_s(i, e + 1);
           }
+          tr.ev(11 + 2 * i);
         }
         if (!ok) break;
         mma_commit(smem_u32(&bar_v_empty[s]));
@@ -234,7 +251,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int qtile = 2 * pair + i;
     const int qi = qtile * KD_TILE + row;  // token index of this thread's query
     const bool tile_valid = qtile < a.NT;
-    uint32_t* my_kdesc = sKdesc + (size_t)(warp - 4) * 2 * KD_TILE;
+    uint32_t* kd_buf = sKdesc + (size_t)(warp - 4) * KD_TILE;   // this warp's copy of a key tile's descriptors
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
     const uint32_t tS = tbase + lane_base + (i == 0 ? C::TM_S0 : C::TM_S1);
     const uint32_t tO = tbase + lane_base + (i == 0 ? C::TM_O0 : C::TM_O1);
@@ -244,27 +261,47 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t qd = tile_valid ? a.desc[(size_t)b * a.Tpad + qi] : 0u;
     float m = -INFINITY, l = 0.f;
     uint32_t sphase = 0;
-    int nact = 0, npart = 0;
+    int nact = 0;
     bool ok = true;
 
-    for (int e = 0; e < n; ++e) {
+    // Key descriptors of PARTIAL tiles are fetched one active entry ahead into registers, so their
+    // global-memory latency overlaps the previous tile's softmax.
+    auto next_active = [&](int from) {
+      int e = from;
+      while (e < n && ((list[e] >> (8 + 2 * i)) & 3u) == KD_TILE_EMPTY) ++e;
+      return e;
+    };
+    uint32_t kd_pre[4] = {0u, 0u, 0u, 0u};
+    auto prefetch_kd = [&](int e) {
+      if (e < n && ((list[e] >> (8 + 2 * i)) & 3u) == KD_TILE_PARTIAL) {
+        const uint32_t* src = a.desc + (size_t)b * a.Tpad + (size_t)(list[e] & 0xFFu) * KD_TILE;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) kd_pre[j] = src[j * 32 + lane];
+      }
+    };
+    int e = next_active(0);
+    prefetch_kd(e);
+
+    while (e < n) {
       const uint32_t ent = list[e];
       const uint32_t cls = (ent >> (8 + 2 * i)) & 3;
-      if (cls == KD_TILE_EMPTY) continue;
       const int kt = ent & 0xFF;
-      uint32_t* kd_buf = my_kdesc + (npart & 1) * KD_TILE;
+      tr.ev(20);
       if (cls == KD_TILE_PARTIAL) {
-        const uint32_t* src = a.desc + (size_t)b * a.Tpad + (size_t)kt * KD_TILE;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) kd_buf[j * 32 + lane] = src[j * 32 + lane];
         __syncwarp();
-        ++npart;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) kd_buf[j * 32 + lane] = kd_pre[j];
+        __syncwarp();
       }
+      e = next_active(e + 1);
+      prefetch_kd(e);
+      tr.ev(21);
       ok = mbar_wait(smem_u32(&bar_s_full[i]), sphase, &abortf, a.status, W_F_SFULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       sphase ^= 1;
       tc_fence_after_sync();
+      tr.ev(22);
 
       float s[KD_TILE];
 #pragma unroll
@@ -275,11 +312,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int j = 0; j < 32; ++j) s[cb * 32 + j] = __uint_as_float(r[j]);
       }
       tmem_wait_ld();
+      tr.ev(23);
       if (cls == KD_TILE_PARTIAL) {
         const int j0 = kt * KD_TILE;
 #pragma unroll
-        for (int j = 0; j < KD_TILE; ++j)
-          if (!rule_allowed(qd, qi, kd_buf[j], j0 + j)) s[j] = -INFINITY;
+        for (int j = 0; j < KD_TILE; j += 4) {
+          const uint4 k4 = *reinterpret_cast<const uint4*>(kd_buf + j);
+          if (!rule_allowed(qd, qi, k4.x, j0 + j + 0)) s[j + 0] = -INFINITY;
+          if (!rule_allowed(qd, qi, k4.y, j0 + j + 1)) s[j + 1] = -INFINITY;
+          if (!rule_allowed(qd, qi, k4.z, j0 + j + 2)) s[j + 2] = -INFINITY;
+          if (!rule_allowed(qd, qi, k4.w, j0 + j + 3)) s[j + 3] = -INFINITY;
+        }
       }
       float mx = s[0];
 #pragma unroll
@@ -323,9 +366,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tmem_st32(tO + cb * 32, r);
         }
       }
+      tr.ev(24);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&bar_p_full[i]));
+      tr.ev(25);
       ++nact;
     }
 
@@ -366,6 +411,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   }
 
+  tr.ev(31);
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tbase, 512);
@@ -383,17 +429,13 @@ static int launch_fwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
   a.B = p.B; a.H = p.H; a.T = p.T; a.NT = L.NT; a.NP = L.NP; a.Tpad = L.NT * KD_TILE;
   a.scale_log2 = p.sm_scale * 1.4426950408889634f;
   a.desc = pv.desc; a.fwd_cnt = pv.fwd_cnt; a.fwd_list = pv.fwd_list; a.status = pv.status;
+  a.order = pv.order; a.trace = trace_buffer();
   a.o = p.o.ptr; a.o_sb = p.o.stride_b; a.o_sh = p.o.stride_h; a.o_st = p.o.stride_t;
   a.lse = p.lse;
   auto kern = attn_fwd_kernel<HD, kBf16>;
-  static thread_local bool attr_done = false;
-  cudaError_t e;
-  if (!attr_done) {
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_ALLOC);
-    if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "fwd smem attribute: %s", cudaGetErrorString(e));
-    attr_done = true;
-  }
-  dim3 grid(L.NP, p.H, p.B);
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_ALLOC);
+  if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "fwd smem attribute: %s", cudaGetErrorString(e));
+  dim3 grid(p.H, p.B, L.NP);
   kern<<<grid, 384, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "attn_fwd_kernel launch: %s", cudaGetErrorString(e));

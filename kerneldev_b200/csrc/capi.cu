@@ -18,6 +18,13 @@ int set_error(int code, const char* fmt, ...) {
   return code;
 }
 
+#ifdef KD_TRACE
+static unsigned long long* g_trace = nullptr;
+unsigned long long* trace_buffer() { return g_trace; }
+#else
+unsigned long long* trace_buffer() { return nullptr; }
+#endif
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -106,6 +113,15 @@ using namespace kd;
 
 extern "C" {
 
+#ifdef KD_TRACE
+// debug builds only: device buffer of 256 x uint64 per (traced CTA, role) that kernels fill with
+// (event id << 48 | clock64) records
+int kd_debug_set_trace(void* buf) {
+  kd::g_trace = static_cast<unsigned long long*>(buf);
+  return 0;
+}
+#endif
+
 int kd_version(void) { return 1; }
 
 const char* kd_last_error(void) { return g_last_error; }
@@ -125,6 +141,7 @@ int kd_plan_layout_get(int32_t B, int32_t T, kd_plan_layout* out) {
   out->off_fwd_list = off; off = up(off + (size_t)B * NP * NT * 2);
   out->off_bwd_cnt = off;  off = up(off + (size_t)B * NT * 4);
   out->off_bwd_list = off; off = up(off + (size_t)B * NT * NT * 2);
+  out->off_order = off;    off = up(off + (size_t)B * 3 * NT);
   out->off_stats = off;    off = up(off + (size_t)B * 2 * 4);
   out->off_status = off;   off = up(off + 4);
   out->total = off;

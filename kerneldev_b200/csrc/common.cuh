@@ -21,6 +21,7 @@ struct PlanView {
   uint16_t* fwd_list;
   int32_t* bwd_cnt;
   uint16_t* bwd_list;
+  uint8_t* order;
   uint32_t* stats;
   uint32_t* status;
 };
@@ -38,6 +39,7 @@ inline PlanView make_plan_view(void* plan, const kd_plan_layout& L) {
   v.fwd_list = reinterpret_cast<uint16_t*>(base + L.off_fwd_list);
   v.bwd_cnt = reinterpret_cast<int32_t*>(base + L.off_bwd_cnt);
   v.bwd_list = reinterpret_cast<uint16_t*>(base + L.off_bwd_list);
+  v.order = reinterpret_cast<uint8_t*>(base + L.off_order);
   v.stats = reinterpret_cast<uint32_t*>(base + L.off_stats);
   v.status = reinterpret_cast<uint32_t*>(base + L.off_status);
   return v;
@@ -50,6 +52,9 @@ int set_error(int code, const char* fmt, ...);
 // 128-byte swizzle, zero fill outside the tensor.
 int encode_tensor_map(CUtensorMap* out, const kd_tensor& t, int B, int H, int T, int D, int dtype,
                       int box_rows, const char* name);
+
+// timeline buffer of KD_TRACE builds (null otherwise)
+unsigned long long* trace_buffer();
 
 int launch_classify(const kd_meta& m, void* plan, cudaStream_t stream);
 int launch_mask_dense(const void* plan, int B, int T, uint8_t* out, cudaStream_t stream);

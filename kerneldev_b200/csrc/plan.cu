@@ -137,9 +137,12 @@ __global__ void __launch_bounds__(128) classify_kernel(PlanView pv, int B) {
 // ---------------------------------------------------------------------------------------
 // forward: per (b, pair p of query tiles 2p, 2p+1) the key tiles that are non-empty for either
 // backward: per (b, key tile) the query tiles that are non-empty
-__global__ void lists_kernel(PlanView pv) {
+// order:    per b, the pairs / query tiles / key tiles sorted by decreasing list length, so that the
+//           kernels can schedule the longest work items first
+__global__ void __launch_bounds__(128) lists_kernel(PlanView pv) {
+  __shared__ int s_cnt[3][128];
   const int b = blockIdx.x;
-  for (int w = threadIdx.x; w < pv.NP + pv.NT; w += blockDim.x) {
+  for (int w = threadIdx.x; w < pv.NP + 2 * pv.NT; w += blockDim.x) {
     if (w < pv.NP) {
       const int p = w, q0 = 2 * p, q1 = 2 * p + 1;
       uint16_t* list = pv.fwd_list + ((size_t)b * pv.NP + p) * pv.NT;
@@ -150,7 +153,8 @@ __global__ void lists_kernel(PlanView pv) {
         if (c0 | c1) list[n++] = static_cast<uint16_t>(kt | (c0 << 8) | (c1 << 10));
       }
       pv.fwd_cnt[b * pv.NP + p] = n;
-    } else {
+      s_cnt[0][p] = n;
+    } else if (w < pv.NP + pv.NT) {
       const int kt = w - pv.NP;
       uint16_t* list = pv.bwd_list + ((size_t)b * pv.NT + kt) * pv.NT;
       int n = 0;
@@ -159,7 +163,26 @@ __global__ void lists_kernel(PlanView pv) {
         if (c) list[n++] = static_cast<uint16_t>(qt | (c << 8));
       }
       pv.bwd_cnt[b * pv.NT + kt] = n;
+      s_cnt[2][kt] = n;
+    } else {
+      const int qt = w - pv.NP - pv.NT;
+      int n = 0;
+      for (int kt = 0; kt < pv.NT; ++kt) n += pv.cls[((size_t)b * pv.NT + qt) * pv.NT + kt] != KD_TILE_EMPTY;
+      s_cnt[1][qt] = n;
     }
+  }
+  __syncthreads();
+  for (int w = threadIdx.x; w < 3 * pv.NT; w += blockDim.x) {
+    const int kind = w / pv.NT, t = w % pv.NT;
+    const int n_items = kind == 0 ? pv.NP : pv.NT;
+    if (t >= n_items) continue;
+    const int mine = s_cnt[kind][t];
+    int rank = 0;
+    for (int u = 0; u < n_items; ++u) {
+      const int other = s_cnt[kind][u];
+      rank += (other > mine) || (other == mine && u < t);
+    }
+    pv.order[((size_t)b * 3 + kind) * pv.NT + rank] = static_cast<uint8_t>(t);
   }
 }
 

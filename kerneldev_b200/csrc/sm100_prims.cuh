@@ -338,6 +338,32 @@ __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// ---------------------------------------------------------------------------------------
+// optional in-kernel timeline (compiled in only with -DKD_TRACE; used to find the critical path)
+// ---------------------------------------------------------------------------------------
+#ifdef KD_TRACE
+struct Tracer {
+  unsigned long long* p;
+  int n;
+  __device__ __forceinline__ void init(unsigned long long* base, bool on, int slot) {
+    p = (on && base) ? base + (size_t)slot * 256 : nullptr;
+    n = 0;
+  }
+  __device__ __forceinline__ void ev(uint32_t id) {
+    if (p && n < 255) {
+      p[1 + n] = (static_cast<unsigned long long>(id) << 48) | (static_cast<unsigned long long>(clock64()) & 0xFFFFFFFFFFFFull);
+      ++n;
+      p[0] = n;
+    }
+  }
+};
+#else
+struct Tracer {
+  __device__ __forceinline__ void init(unsigned long long*, bool, int) {}
+  __device__ __forceinline__ void ev(uint32_t) {}
+};
+#endif
+
 template <uint32_t kRegs>
 __device__ __forceinline__ void reg_dealloc() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
