@@ -44,22 +44,24 @@ def _stale() -> bool:
     return any(d.stat().st_mtime > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False, trace: bool = False) -> Path:
+def build(force: bool = False, verbose: bool = False, trace: bool = False, extra_flags=(), name=None) -> Path:
     """Compiles every CUDA source for sm_100a and links the shared library. Returns its path.
 
     ``trace=True`` builds the variant with in-kernel timelines (-DKD_TRACE) as
     libkd_attention_trace.so; it is a debugging aid and is never loaded by the package itself."""
     lib_path = LIB_DIR / "libkd_attention_trace.so" if trace else LIB_PATH
-    if not trace and not force and not _stale():
+    if name:  # experimental variant built with extra compiler flags
+        lib_path = LIB_DIR / f"libkd_attention_{name}.so"
+    if not trace and not name and not force and not _stale():
         return LIB_PATH
     LIB_DIR.mkdir(exist_ok=True)
-    obj_dir = LIB_DIR / ("obj_trace" if trace else "obj")
+    obj_dir = LIB_DIR / (f"obj_{name}" if name else "obj_trace" if trace else "obj")
     obj_dir.mkdir(exist_ok=True)
     nvcc = _nvcc()
 
     def compile_one(src: str) -> Path:
         obj = obj_dir / (src + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, *(["-DKD_TRACE"] if trace else []), "-c", str(CSRC / src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, *(["-DKD_TRACE"] if trace else []), *extra_flags, "-c", str(CSRC / src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         r = subprocess.run(cmd, capture_output=True, text=True)

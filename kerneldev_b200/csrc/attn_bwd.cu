@@ -9,11 +9,12 @@
 //
 // Shared structure (384 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warps 4-7 and
 // 8-11 = two compute warpgroups. The backward needs no row reductions, so the 128 columns of a
-// score tile are split into two independent 64-column streams, one per warpgroup; the MMA
-// issuer alternates between the streams so that one stream's element-wise work overlaps the
-// other stream's MMAs:
-//   M1(i): S_i, dP_i  (smem x smem -> TMEM, N = 64)      compute(i): P_i / dS_i -> TMEM (16 bit)
-//   M2(i): accumulators += (P_i | dS_i) x smem operand   (A from TMEM)
+// score tile are split into two 64-column halves, one per warpgroup. A "unit" u = 2*entry + half;
+// it owns TMEM buffer u % NBUF (64 columns of scores + 64 of dP) and the issuer runs NBUF units
+// ahead, so that a warpgroup finishing unit u finds its next unit's scores already in TMEM:
+//   M1(u): S_u, dP_u  (smem x smem -> TMEM, N = 64)      compute(u): P_u / dS_u -> TMEM (16 bit)
+//   M2(u): accumulators += (P_u | dS_u) x smem operand   (A from TMEM);   then M1(u + NBUF)
+// The tensor pipe executes in issue order, so M1(u + NBUF) may overwrite the buffer M2(u) read.
 #include "attn_common.cuh"
 
 namespace kd {
@@ -48,7 +49,8 @@ template <int HD>
 struct BwdCfg {
   static constexpr int KBLK = HD / 64;
   static constexpr int TILE_BYTES = KD_TILE * HD * 2;
-  static constexpr int STAGES = (HD == 64) ? 3 : 2;   // ring of (tile, tile) pairs
+  static constexpr int NBUF = (HD == 64) ? 3 : 2;     // score / dP buffers in TMEM
+  static constexpr int STAGES = NBUF;                 // ring of (tile, tile) pairs
   static constexpr int SMEM_FIX = 0;                               // two resident tiles
   static constexpr int SMEM_RING = SMEM_FIX + 2 * TILE_BYTES;      // STAGES x two streamed tiles
   static constexpr int SMEM_STAGE = SMEM_RING + STAGES * 2 * TILE_BYTES;  // per-warp staging
@@ -57,9 +59,11 @@ struct BwdCfg {
   static constexpr int SMEM_TOTAL = SMEM_ACT + 128 * 2;
   static constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;
   // TMEM columns
-  static constexpr uint32_t TM_S0 = 0, TM_S1 = 64, TM_P0 = 128, TM_P1 = 192;  // scores / dP streams
-  static constexpr uint32_t TM_ACC0 = 256;        // dQ, or dK
-  static constexpr uint32_t TM_ACC1 = 256 + HD;   // dV
+  // buffer j: scores at 128*j, dP at 128*j + 64; accumulators behind the buffers
+  static constexpr uint32_t TM_ACC0 = NBUF * 128;        // dQ, or dK
+  static constexpr uint32_t TM_ACC1 = NBUF * 128 + HD;   // dV
+  static_assert(TM_ACC1 + HD <= 512, "TMEM budget");
+  static_assert(SMEM_ALLOC <= 232448, "shared memory budget");
 };
 
 enum : uint32_t {
@@ -88,7 +92,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint16_t* sAct = reinterpret_cast<uint16_t*>(smem + C::SMEM_ACT);
 
   __shared__ __align__(8) uint64_t bar_fix_full, bar_ring_full[C::STAGES], bar_ring_empty[C::STAGES],
-      bar_s_full[2], bar_p_full[2], bar_acc_full;
+      bar_s_full[C::NBUF], bar_p_full[C::NBUF], bar_acc_full;
   __shared__ uint32_t tmem_base_s;
   __shared__ int n_act_s;
   __shared__ AbortFlag abortf;
@@ -105,7 +109,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_init(smem_u32(&bar_ring_full[s]), 1);
       mbar_init(smem_u32(&bar_ring_empty[s]), 1);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < C::NBUF; ++i) {
       mbar_init(smem_u32(&bar_s_full[i]), 1);
       mbar_init(smem_u32(&bar_p_full[i]), 128);
     }
@@ -142,7 +146,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tr.ev(1);
 
   if (warp < 4) {
-    reg_dealloc<56>();
+    reg_dealloc<KD_REGS_ISSUE>();
     if (warp == 0 && lane == 0 && na > 0) {
       // ------------------------------ TMA producer ------------------------------
       tma_prefetch_desc(&tmQ);
@@ -175,68 +179,56 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
     } else if (warp == 1 && lane == 0 && na > 0) {
       // ------------------------------ MMA issuer ------------------------------
-      const uint32_t idesc_m1 = make_idesc_f16(kBf16, 0, 0, KD_TILE, 64);   // S_i, dP_i: N = 64 keys
+      const uint32_t idesc_m1 = make_idesc_f16(kBf16, 0, 0, KD_TILE, 64);   // S_u, dP_u: N = 64 keys
       const uint32_t idesc_m2 = make_idesc_f16(kBf16, 0, 1, KD_TILE, HD);   // dQ: B = K rows, MN-major
-      const uint32_t tS[2] = {tbase + C::TM_S0, tbase + C::TM_S1};
-      const uint32_t tP[2] = {tbase + C::TM_P0, tbase + C::TM_P1};
       const uint32_t tAcc = tbase + C::TM_ACC0;
       const uint32_t hi = desc_hi_sw128();
       const uint32_t loQ = desc_lo_kmajor(sQ), loDO = desc_lo_kmajor(sDO);
       const uint32_t loRingK = desc_lo_kmajor(sRing), loRingMN = desc_lo_mnmajor(sRing);
-      auto issue_m1 = [&](int i, int e) {
+      const int U = 2 * na;
+      int ring_ready = -1;
+      bool ok = mbar_wait(smem_u32(&bar_fix_full), 0, &abortf, a.status, W_Q_FIXFULL);
+      auto issue_m1 = [&](int u) -> bool {
+        const int e = u >> 1, i = u & 1;
+        if (e != ring_ready) {
+          if (!mbar_wait(smem_u32(&bar_ring_full[e % C::STAGES]), (e / C::STAGES) & 1, &abortf, a.status, W_Q_RINGFULL)) return false;
+          ring_ready = e;
+          tc_fence_after_sync();
+        }
         const uint32_t kb = loRingK + (e % C::STAGES) * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);  // key rows 64i..
         const uint32_t vb = kb + (C::TILE_BYTES >> 4);
+        const uint32_t dS = tbase + (u % C::NBUF) * 128, dP = dS + 64;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss_split(tS[i], loQ + koff_kmajor(kk), kb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
+          mma_ss_split(dS, loQ + koff_kmajor(kk), kb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss_split(tP[i], loDO + koff_kmajor(kk), vb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
-        mma_commit(smem_u32(&bar_s_full[i]));
+          mma_ss_split(dP, loDO + koff_kmajor(kk), vb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
+        mma_commit(smem_u32(&bar_s_full[u % C::NBUF]));
+        return true;
       };
-      auto issue_m2 = [&](int i, int e, bool acc) {
-        const uint32_t kb = loRingMN + (e % C::STAGES) * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)  // 64 keys of this stream, 16 per MMA; dS_i sits on top of S_i
-          mma_ts_split(tAcc, tS[i] + kk * 8, kb + koff_mnmajor(kk), hi, idesc_m2, (acc || kk > 0) ? 1u : 0u);
-      };
-      bool ok = mbar_wait(smem_u32(&bar_fix_full), 0, &abortf, a.status, W_Q_FIXFULL);
-      if (ok) ok = mbar_wait(smem_u32(&bar_ring_full[0]), 0, &abortf, a.status, W_Q_RINGFULL);
-      if (ok) {
-        tc_fence_after_sync();
-        issue_m1(0, 0);
-        issue_m1(1, 0);
-      }
-      uint32_t pphase = 0;
-      for (int e = 0; e < na && ok; ++e) {
-        bool ring_waited = false;
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          ok = mbar_wait(smem_u32(&bar_p_full[i]), pphase, &abortf, a.status, W_Q_PFULL);
-          if (!ok) break;
-          tr.ev(10 + 2 * i);
-          tc_fence_after_sync();
-          issue_m2(i, e, e > 0 || i > 0);
-          if (e + 1 < na) {
-            if (!ring_waited) {
-              ok = mbar_wait(smem_u32(&bar_ring_full[(e + 1) % C::STAGES]), ((e + 1) / C::STAGES) & 1, &abortf,
-                             a.status, W_Q_RINGFULL);
-              if (!ok) break;
-              ring_waited = true;
-              tc_fence_after_sync();
-            }
-            issue_m1(i, e + 1);
-          }
-          tr.ev(11 + 2 * i);
-        }
+      for (int u = 0; u < C::NBUF && u < U && ok; ++u) ok = issue_m1(u);
+      for (int u = 0; u < U && ok; ++u) {
+        const int e = u >> 1, i = u & 1, buf = u % C::NBUF;
+        ok = mbar_wait(smem_u32(&bar_p_full[buf]), (u / C::NBUF) & 1, &abortf, a.status, W_Q_PFULL);
         if (!ok) break;
-        pphase ^= 1;
-        mma_commit(smem_u32(&bar_ring_empty[e % C::STAGES]));
+        tr.ev(10);
+        tc_fence_after_sync();
+        {
+          const uint32_t kb = loRingMN + (e % C::STAGES) * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
+          const uint32_t aS = tbase + buf * 128;   // dS_u sits on top of S_u
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)  // 64 keys of this unit, 16 per MMA
+            mma_ts_split(tAcc, aS + kk * 8, kb + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
+        }
+        if (i == 1) mma_commit(smem_u32(&bar_ring_empty[e % C::STAGES]));
+        if (u + C::NBUF < U) ok = issue_m1(u + C::NBUF);
+        tr.ev(11);
       }
       if (ok) mma_commit(smem_u32(&bar_acc_full));
     }
   } else {
-    reg_alloc<224>();
+    reg_alloc<KD_REGS_COMPUTE>();
     // ------------------------------ compute warpgroups ------------------------------
     const int i = (warp - 4) >> 2;   // stream: key half of each key tile
     const int wq = warp & 3;
@@ -244,8 +236,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int qi = qt * KD_TILE + row;
     const bool q_valid = qi < a.T;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
-    const uint32_t tS = tbase + lane_base + (i == 0 ? C::TM_S0 : C::TM_S1);
-    const uint32_t tP = tbase + lane_base + (i == 0 ? C::TM_P0 : C::TM_P1);
     uint32_t* kd_buf = sStage + (size_t)(warp - 4) * C::STAGE_WORDS;
     const float c = a.scale_log2;
     const size_t bh = (size_t)b * a.H + h;
@@ -270,7 +260,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     const float neg_lse = q_valid ? -a.lse[bh * a.T + qi] : 0.f;
     const uint32_t qd = a.desc[(size_t)b * a.Tpad + qi];
-    uint32_t sphase = 0;
     bool ok = true;
 
     // key descriptors of PARTIAL tiles are fetched one entry ahead into registers
@@ -296,11 +285,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         __syncwarp();
       }
       prefetch_kd(e + 1);
+      const int u = 2 * e + i, buf = u % C::NBUF;
+      const uint32_t tS = tbase + lane_base + buf * 128, tP = tS + 64;
       tr.ev(21);
-      ok = mbar_wait(smem_u32(&bar_s_full[i]), sphase, &abortf, a.status, W_Q_SFULL);
+      ok = mbar_wait(smem_u32(&bar_s_full[buf]), (u / C::NBUF) & 1, &abortf, a.status, W_Q_SFULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      sphase ^= 1;
       tc_fence_after_sync();
       tr.ev(22);
 
@@ -331,10 +321,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
       tr.ev(24);
-      tmem_st32(tS, pk);   // dS_i as 16-bit A operand on top of S_i (this thread's own row)
+      tmem_st32(tS, pk);   // dS_u as 16-bit A operand on top of S_u (this thread's own row)
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(smem_u32(&bar_p_full[i]));
+      mbar_arrive(smem_u32(&bar_p_full[buf]));
       tr.ev(25);
     }
 
@@ -386,7 +376,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint16_t* sList = reinterpret_cast<uint16_t*>(smem + C::SMEM_ACT);
 
   __shared__ __align__(8) uint64_t bar_fix_full, bar_ring_full[C::STAGES], bar_ring_empty[C::STAGES],
-      bar_s_full[2], bar_p_full[2], bar_acc_full;
+      bar_s_full[C::NBUF], bar_p_full[C::NBUF], bar_acc_full;
   __shared__ uint32_t tmem_base_s;
   __shared__ AbortFlag abortf;
 
@@ -402,7 +392,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       mbar_init(smem_u32(&bar_ring_full[s]), 1);
       mbar_init(smem_u32(&bar_ring_empty[s]), 1);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < C::NBUF; ++i) {
       mbar_init(smem_u32(&bar_s_full[i]), 1);
       mbar_init(smem_u32(&bar_p_full[i]), 128);
     }
@@ -428,7 +418,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   tr.ev(1);
 
   if (warp < 4) {
-    reg_dealloc<56>();
+    reg_dealloc<KD_REGS_ISSUE>();
     if (warp == 0 && lane == 0 && n > 0) {
       // ------------------------------ TMA producer ------------------------------
       tma_prefetch_desc(&tmQ);
@@ -462,74 +452,62 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
     } else if (warp == 1 && lane == 0 && n > 0) {
       // ------------------------------ MMA issuer ------------------------------
-      const uint32_t idesc_m1 = make_idesc_f16(kBf16, 0, 0, KD_TILE, 64);   // S^T_i, dP^T_i: N = 64 queries
+      const uint32_t idesc_m1 = make_idesc_f16(kBf16, 0, 0, KD_TILE, 64);   // S^T_u, dP^T_u: N = 64 queries
       const uint32_t idesc_m2 = make_idesc_f16(kBf16, 0, 1, KD_TILE, HD);   // dV, dK: B = dO / Q rows, MN-major
-      const uint32_t tS[2] = {tbase + C::TM_S0, tbase + C::TM_S1};
-      const uint32_t tP[2] = {tbase + C::TM_P0, tbase + C::TM_P1};
       const uint32_t tDK = tbase + C::TM_ACC0, tDV = tbase + C::TM_ACC1;
       const uint32_t hi = desc_hi_sw128();
       const uint32_t loK = desc_lo_kmajor(sK), loV = desc_lo_kmajor(sV);
       const uint32_t loRingK = desc_lo_kmajor(sRing), loRingMN = desc_lo_mnmajor(sRing);
-      auto issue_m1 = [&](int i, int e) {
+      const int U = 2 * n;
+      int ring_ready = -1;
+      bool ok = mbar_wait(smem_u32(&bar_fix_full), 0, &abortf, a.status, W_K_FIXFULL);
+      tr.ev(2);
+      auto issue_m1 = [&](int u) -> bool {
+        const int e = u >> 1, i = u & 1;
+        if (e != ring_ready) {
+          if (!mbar_wait(smem_u32(&bar_ring_full[e % C::STAGES]), (e / C::STAGES) & 1, &abortf, a.status, W_K_RINGFULL)) return false;
+          ring_ready = e;
+          tc_fence_after_sync();
+        }
         const uint32_t qb = loRingK + (e % C::STAGES) * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);  // query rows 64i..
         const uint32_t dob = qb + (C::TILE_BYTES >> 4);
+        const uint32_t dS = tbase + (u % C::NBUF) * 128, dP = dS + 64;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss_split(tS[i], loK + koff_kmajor(kk), qb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
+          mma_ss_split(dS, loK + koff_kmajor(kk), qb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss_split(tP[i], loV + koff_kmajor(kk), dob + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
-        mma_commit(smem_u32(&bar_s_full[i]));
+          mma_ss_split(dP, loV + koff_kmajor(kk), dob + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
+        mma_commit(smem_u32(&bar_s_full[u % C::NBUF]));
+        return true;
       };
-      auto issue_m2 = [&](int i, int e, bool acc) {
-        const uint32_t qb = loRingMN + (e % C::STAGES) * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
-        const uint32_t dob = qb + (C::TILE_BYTES >> 4);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)  // dV += P^T_i dO_i   (P^T_i on top of S^T_i)
-          mma_ts_split(tDV, tS[i] + kk * 8, dob + koff_mnmajor(kk), hi, idesc_m2, (acc || kk > 0) ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)  // dK += dS^T_i Q_i   (dS^T_i on top of dP^T_i)
-          mma_ts_split(tDK, tP[i] + kk * 8, qb + koff_mnmajor(kk), hi, idesc_m2, (acc || kk > 0) ? 1u : 0u);
-      };
-      bool ok = mbar_wait(smem_u32(&bar_fix_full), 0, &abortf, a.status, W_K_FIXFULL);
-      if (ok) ok = mbar_wait(smem_u32(&bar_ring_full[0]), 0, &abortf, a.status, W_K_RINGFULL);
-      tr.ev(2);
-      if (ok) {
-        tc_fence_after_sync();
-        issue_m1(0, 0);
-        issue_m1(1, 0);
-      }
+      for (int u = 0; u < C::NBUF && u < U && ok; ++u) ok = issue_m1(u);
       tr.ev(3);
-      uint32_t pphase = 0;
-      for (int e = 0; e < n && ok; ++e) {
-        bool ring_waited = false;
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          ok = mbar_wait(smem_u32(&bar_p_full[i]), pphase, &abortf, a.status, W_K_PFULL);
-          if (!ok) break;
-          tr.ev(10 + 2 * i);
-          tc_fence_after_sync();
-          issue_m2(i, e, e > 0 || i > 0);
-          if (e + 1 < n) {
-            if (!ring_waited) {
-              ok = mbar_wait(smem_u32(&bar_ring_full[(e + 1) % C::STAGES]), ((e + 1) / C::STAGES) & 1, &abortf,
-                             a.status, W_K_RINGFULL);
-              if (!ok) break;
-              ring_waited = true;
-              tc_fence_after_sync();
-            }
-            issue_m1(i, e + 1);
-          }
-          tr.ev(11 + 2 * i);
-        }
+      for (int u = 0; u < U && ok; ++u) {
+        const int e = u >> 1, i = u & 1, buf = u % C::NBUF;
+        ok = mbar_wait(smem_u32(&bar_p_full[buf]), (u / C::NBUF) & 1, &abortf, a.status, W_K_PFULL);
         if (!ok) break;
-        pphase ^= 1;
-        mma_commit(smem_u32(&bar_ring_empty[e % C::STAGES]));
+        tr.ev(10);
+        tc_fence_after_sync();
+        {
+          const uint32_t qb = loRingMN + (e % C::STAGES) * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
+          const uint32_t dob = qb + (C::TILE_BYTES >> 4);
+          const uint32_t aS = tbase + buf * 128, aP = aS + 64;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)  // dV += P^T_u dO_u   (P^T_u on top of S^T_u)
+            mma_ts_split(tDV, aS + kk * 8, dob + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)  // dK += dS^T_u Q_u   (dS^T_u on top of dP^T_u)
+            mma_ts_split(tDK, aP + kk * 8, qb + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
+        }
+        if (i == 1) mma_commit(smem_u32(&bar_ring_empty[e % C::STAGES]));
+        if (u + C::NBUF < U) ok = issue_m1(u + C::NBUF);
+        tr.ev(11);
       }
       if (ok) mma_commit(smem_u32(&bar_acc_full));
     }
   } else {
-    reg_alloc<224>();
+    reg_alloc<KD_REGS_COMPUTE>();
     // ------------------------------ compute warpgroups ------------------------------
     const int i = (warp - 4) >> 2;   // stream: query half of each query tile
     const int wq = warp & 3;
@@ -537,13 +515,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const int kj = kt * KD_TILE + row;   // this thread's key
     const bool k_valid = kj < a.T;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
-    const uint32_t tS = tbase + lane_base + (i == 0 ? C::TM_S0 : C::TM_S1);
-    const uint32_t tP = tbase + lane_base + (i == 0 ? C::TM_P0 : C::TM_P1);
     uint32_t* st_buf = sStage + (size_t)(warp - 4) * C::STAGE_WORDS;  // [64 -lse][64 delta][64 desc]
     const float c = a.scale_log2;
     const size_t bh = (size_t)b * a.H + h;
     const uint32_t kdesc = a.desc[(size_t)b * a.Tpad + kj];
-    uint32_t sphase = 0;
     bool ok = true;
 
     // -LSE, delta and the descriptors of the next entry's 64 queries are fetched one entry ahead
@@ -580,11 +555,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       __syncwarp();
       prefetch(e + 1);
+      const int u = 2 * e + i, buf = u % C::NBUF;
+      const uint32_t tS = tbase + lane_base + buf * 128, tP = tS + 64;
       tr.ev(21);
-      ok = mbar_wait(smem_u32(&bar_s_full[i]), sphase, &abortf, a.status, W_K_SFULL);
+      ok = mbar_wait(smem_u32(&bar_s_full[buf]), (u / C::NBUF) & 1, &abortf, a.status, W_K_SFULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      sphase ^= 1;
       tc_fence_after_sync();
       tr.ev(22);
 
@@ -620,11 +596,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
       }
       tr.ev(24);
-      tmem_st32(tS, pk_p);    // P^T_i on top of S^T_i
-      tmem_st32(tP, pk_ds);   // dS^T_i on top of dP^T_i
+      tmem_st32(tS, pk_p);    // P^T_u on top of S^T_u
+      tmem_st32(tP, pk_ds);   // dS^T_u on top of dP^T_u
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(smem_u32(&bar_p_full[i]));
+      mbar_arrive(smem_u32(&bar_p_full[buf]));
       tr.ev(25);
     }
 

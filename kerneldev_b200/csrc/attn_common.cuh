@@ -6,6 +6,15 @@
 #include "mask_rule.cuh"
 #include "sm100_prims.cuh"
 
+// Register split between the four light warps (producer, MMA issuer, list builder, idle) and the
+// eight compute warps: 4*32*ISSUE + 8*32*COMPUTE must not exceed 65536.
+#ifndef KD_REGS_ISSUE
+#define KD_REGS_ISSUE 56
+#endif
+#ifndef KD_REGS_COMPUTE
+#define KD_REGS_COMPUTE 224
+#endif
+
 namespace kd {
 
 // High words of the two descriptor kinds used here (layout, version, stride byte offset 1024);

@@ -3,14 +3,25 @@
 // One CTA owns a pair of 128-row query tiles of one (batch, head) and walks the plan's list of
 // key tiles that are non-empty for either of them. Roles (warp-specialised, 384 threads):
 //   warp 0      TMA producer: Q pair once, then K and V tiles through two rings
-//   warp 1      MMA issuer:   S_i = Q_i K^T  (smem x smem -> TMEM),  O_i += P_i V (TMEM x smem)
+//   warp 1      P V issuer:   O_i += P V    (TMEM x smem -> TMEM)
+//   warp 3      S issuer:     S = Q_i K^T   (smem x smem -> TMEM)
+//   warp 2      builds the unit list and the issuers' per-unit commands in shared memory at start-up
 //   warps 4-7   softmax of query tile 0: TMEM -> registers, rule on PARTIAL tiles, online
 //   warps 8-11  softmax of query tile 1  softmax in base 2, P back to TMEM as 16-bit operand
-// The two query tiles alternate on the tensor core, so one tile's softmax overlaps the other
-// tile's MMAs. EMPTY tiles never appear in the list: they are neither loaded nor multiplied.
+//
+// A "unit" is one (key tile, query tile) product that is not EMPTY. Units are numbered in list
+// order; unit u computes its scores into TMEM buffer u % NBUF (128 fp32 columns), and P (64
+// columns of packed pairs) is written over the same buffer. The S issuer runs NBUF units ahead of
+// the P V issuer:   S(u + NBUF) is issued as soon as P(u) V has been issued,
+// so a softmax warpgroup that finishes unit u finds the scores of its next unit already in
+// TMEM, and the tensor core works on other units while it computes. The tensor pipe executes
+// in issue order, which is what allows S(u + NBUF) to overwrite the buffer P(u) was read from.
+// The two issuers are single threads that share their schedulers with the softmax warps, so
+// everything they need per unit is precomputed into one 16-byte command each.
+// EMPTY tiles never appear in the list: they are neither loaded nor multiplied.
 //
 // Replaces _flash_attn_fwd (original_kernel.py:278-626): same math (scores scaled by
-// sm_scale*log2(e), exp2, LSE = m + log2(l)), rows without any visible key give O = 0 and
+// sm_scale*log2(e), exp2, LSE = m + log2(l)); rows without any visible key give O = 0 and
 // LSE = -inf.
 #include "attn_common.cuh"
 
@@ -34,27 +45,42 @@ template <int HD>
 struct FwdCfg {
   static constexpr int KBLK = HD / 64;                   // 64-element blocks along D
   static constexpr int TILE_BYTES = KD_TILE * HD * 2;    // one Q / K / V tile
-  static constexpr int STAGES = (HD == 64) ? 3 : 2;
+  static constexpr int NBUF = (HD == 64) ? 3 : 2;        // score buffers in TMEM
+  static constexpr int KST = NBUF;                       // K ring stages
+  static constexpr int VST = (HD == 64) ? 3 : 2;         // V ring stages
   static constexpr int SMEM_Q = 0;
   static constexpr int SMEM_K = SMEM_Q + 2 * TILE_BYTES;
-  static constexpr int SMEM_V = SMEM_K + STAGES * TILE_BYTES;
-  static constexpr int SMEM_KDESC = SMEM_V + STAGES * TILE_BYTES;  // 8 warps x 128 u32
-  static constexpr int SMEM_LIST = SMEM_KDESC + 8 * KD_TILE * 4;     // the pair's work list (<= 128 entries)
-  static constexpr int SMEM_TOTAL = SMEM_LIST + 128 * 2;
+  static constexpr int SMEM_V = SMEM_K + KST * TILE_BYTES;
+  static constexpr int SMEM_KDESC = SMEM_V + VST * TILE_BYTES;     // 8 warps x 128 u32
+  static constexpr int SMEM_LIST = SMEM_KDESC + 8 * KD_TILE * 4;   // the pair's work list (<= 128 entries)
+  static constexpr int SMEM_UNITS = SMEM_LIST + 128 * 2;           // unit list (<= 256 units)
+  static constexpr int SMEM_CMD = SMEM_UNITS + 256 * 2;            // 256 x {S command, P V command} (uint4 each)
+  static constexpr int SMEM_WCMD = SMEM_CMD + 256 * 2 * 16;        // 2 x 256 softmax commands (u32 each)
+  static constexpr int SMEM_TOTAL = SMEM_WCMD + 2 * 256 * 4;
   static constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;   // slack for 1024-byte alignment
-  // TMEM columns: S0, S1 (128 each, fp32), O0, O1 (HD each); P as 64 columns of packed pairs,
-  // in its own region for HD = 64, on top of S for HD = 128 (the tensor pipe runs in order, so
-  // S(j+1) is written only after P(j) was consumed by the MMA issued before it).
-  static constexpr uint32_t TM_S0 = 0, TM_S1 = 128;
-  static constexpr uint32_t TM_O0 = 256, TM_O1 = 256 + HD;
-  static constexpr uint32_t TM_P0 = (HD == 64) ? 384 : 0;
-  static constexpr uint32_t TM_P1 = (HD == 64) ? 448 : 128;
+  // TMEM columns: NBUF score buffers of 128, then O0 and O1 (HD each)
+  static constexpr uint32_t TM_O0 = NBUF * 128, TM_O1 = NBUF * 128 + HD;
+  static_assert(TM_O1 + HD <= 512, "TMEM budget");
+  static_assert(SMEM_ALLOC <= 232448, "shared memory budget");
 };
+
+// unit descriptor: entry index (7 bits) | query tile of the pair << 7 | tile class << 8
+__device__ __forceinline__ int unit_entry(uint32_t u) { return u & 0x7F; }
+__device__ __forceinline__ int unit_tile(uint32_t u) { return (u >> 7) & 1; }
+__device__ __forceinline__ uint32_t unit_class(uint32_t u) { return (u >> 8) & 3; }
+
+// command flags (word z of a command): ring stage, phase parity, wait / release markers
+constexpr uint32_t CMD_STAGE = 3u, CMD_PARITY = 4u, CMD_WAIT = 8u, CMD_RELEASE = 16u, CMD_ACC = 32u, CMD_TILE1 = 64u;
+// softmax command of a warpgroup's k-th unit: key tile | class << 8 | buffer << 10 | s_full parity << 12
+__device__ __forceinline__ int wcmd_kt(uint32_t c) { return c & 0xFF; }
+__device__ __forceinline__ uint32_t wcmd_class(uint32_t c) { return (c >> 8) & 3; }
+__device__ __forceinline__ int wcmd_buf(uint32_t c) { return (c >> 10) & 3; }
+__device__ __forceinline__ uint32_t wcmd_parity(uint32_t c) { return (c >> 12) & 1; }
 
 // wait-site codes reported in the status word
 enum : uint32_t {
   W_F_QFULL = 0x101, W_F_KEMPTY = 0x102, W_F_VEMPTY = 0x103, W_F_KFULL = 0x104, W_F_VFULL = 0x105,
-  W_F_PFULL = 0x106, W_F_SFULL = 0x107, W_F_OFULL = 0x108,
+  W_F_PFULL = 0x106, W_F_SFULL = 0x107, W_F_PVDONE = 0x108, W_F_PVISSUED = 0x109,
 };
 
 template <int HD, bool kBf16>
@@ -69,10 +95,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t sV = smem_u32(smem + C::SMEM_V);
   uint32_t* sKdesc = reinterpret_cast<uint32_t*>(smem + C::SMEM_KDESC);
   uint16_t* sList = reinterpret_cast<uint16_t*>(smem + C::SMEM_LIST);
+  uint16_t* sUnits = reinterpret_cast<uint16_t*>(smem + C::SMEM_UNITS);
+  uint4* sCmd = reinterpret_cast<uint4*>(smem + C::SMEM_CMD);   // [u][0] = S command, [u][1] = P V command
+  uint32_t* sWcmd = reinterpret_cast<uint32_t*>(smem + C::SMEM_WCMD);   // [tile][k]
 
-  __shared__ __align__(8) uint64_t bar_q_full, bar_k_full[C::STAGES], bar_k_empty[C::STAGES],
-      bar_v_full[C::STAGES], bar_v_empty[C::STAGES], bar_s_full[2], bar_p_full[2], bar_o_full[2];
+  __shared__ __align__(8) uint64_t bar_q_full, bar_k_full[C::KST], bar_k_empty[C::KST], bar_v_full[C::VST],
+      bar_v_empty[C::VST], bar_s_full[2 * C::NBUF], bar_p_full[C::NBUF], bar_pv_issued[C::NBUF], bar_pv_done[2];
   __shared__ uint32_t tmem_base_s;
+  __shared__ int n_units_s, n_own_s[2];
   __shared__ AbortFlag abortf;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -85,17 +115,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (tid == 0) {
     abortf.v = 0;
     mbar_init(smem_u32(&bar_q_full), 1);
-    for (int s = 0; s < C::STAGES; ++s) {
+    for (int s = 0; s < C::KST; ++s) {
       mbar_init(smem_u32(&bar_k_full[s]), 1);
       mbar_init(smem_u32(&bar_k_empty[s]), 1);
+    }
+    for (int s = 0; s < C::VST; ++s) {
       mbar_init(smem_u32(&bar_v_full[s]), 1);
       mbar_init(smem_u32(&bar_v_empty[s]), 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&bar_s_full[i]), 1);
-      mbar_init(smem_u32(&bar_p_full[i]), 128);
-      mbar_init(smem_u32(&bar_o_full[i]), 1);
+    for (int s = 0; s < C::NBUF; ++s) {
+      // one "scores ready" barrier per (buffer, query tile): each softmax warpgroup then sees every
+      // phase of the barriers it waits on, which is what makes a parity wait sound
+      mbar_init(smem_u32(&bar_s_full[2 * s]), 1);
+      mbar_init(smem_u32(&bar_s_full[2 * s + 1]), 1);
+      mbar_init(smem_u32(&bar_p_full[s]), 128);
+      mbar_init(smem_u32(&bar_pv_issued[s]), 1);
     }
+    mbar_init(smem_u32(&bar_pv_done[0]), 1);
+    mbar_init(smem_u32(&bar_pv_done[1]), 1);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -103,21 +140,97 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tmem_relinquish();
   }
   if (warp == 2) {
-    const uint16_t* list = a.fwd_list + ((size_t)b * a.NP + pair) * a.NT;
-    for (int e = lane; e < n; e += 32) sList[e] = list[e];
+    // stage the pair's list and expand it into units (one per non-empty (key tile, query tile))
+    const uint16_t* glist = a.fwd_list + ((size_t)b * a.NP + pair) * a.NT;
+    int nu = 0;
+    for (int base = 0; base < n; base += 32) {
+      const int e = base + lane;
+      const uint32_t ent = e < n ? glist[e] : 0u;
+      if (e < n) sList[e] = static_cast<uint16_t>(ent);
+      const uint32_t c0 = (ent >> 8) & 3u, c1 = (ent >> 10) & 3u;
+      const int cnt = (c0 != 0u) + (c1 != 0u);
+      int incl = cnt;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      int pos = nu + incl - cnt;
+      if (c0) sUnits[pos++] = static_cast<uint16_t>(e | (0 << 7) | (c0 << 8));
+      if (c1) sUnits[pos++] = static_cast<uint16_t>(e | (1 << 7) | (c1 << 8));
+      nu += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) n_units_s = nu;
+    __syncwarp();
+    // per-unit commands for the two issuers and for the softmax warpgroups
+    const uint32_t loQ0 = desc_lo_kmajor(sQ), loK0 = desc_lo_kmajor(sK), loV0 = desc_lo_mnmajor(sV);
+    int cnt_key[2 * C::NBUF];   // units seen so far per (buffer, tile)
+#pragma unroll
+    for (int j = 0; j < 2 * C::NBUF; ++j) cnt_key[j] = 0;
+    const uint32_t lt_mask = (1u << lane) - 1u;
+    for (int base = 0; base < nu; base += 32) {
+      const int u = base + lane;
+      const bool valid = u < nu;
+      const uint32_t un = valid ? sUnits[u] : 0u;
+      const int e = unit_entry(un), i = unit_tile(un), buf = u % C::NBUF, key = 2 * buf + i;
+      // rank of this unit among the units of its query tile (counts still exclude this chunk)
+      int rank_tile = 0;
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const uint32_t bal = __ballot_sync(0xffffffffu, valid && i == t);
+        int before = 0;
+#pragma unroll
+        for (int j = 0; j < C::NBUF; ++j) before += cnt_key[2 * j + t];
+        if (i == t) rank_tile = before + __popc(bal & lt_mask);
+      }
+      // rank among the units that share its (buffer, tile) barrier; then add this chunk to the counts
+      int rank_key = 0;
+#pragma unroll
+      for (int j = 0; j < 2 * C::NBUF; ++j) {
+        const uint32_t bal = __ballot_sync(0xffffffffu, valid && key == j);
+        if (key == j) rank_key = cnt_key[j] + __popc(bal & lt_mask);
+        cnt_key[j] += __popc(bal);
+      }
+      if (valid) {
+        const bool first_of_entry = (u == 0) || unit_entry(sUnits[u - 1]) != e;
+        const bool last_of_entry = (u + 1 >= nu) || unit_entry(sUnits[u + 1]) != e;
+        uint4 cs, cp;
+        cs.x = loQ0 + i * (C::TILE_BYTES >> 4);
+        cs.y = loK0 + (e % C::KST) * (C::TILE_BYTES >> 4);
+        cs.z = (e % C::KST) | (((e / C::KST) & 1) ? CMD_PARITY : 0u) | (first_of_entry ? CMD_WAIT : 0u) | (last_of_entry ? CMD_RELEASE : 0u) |
+               (i ? CMD_TILE1 : 0u);
+        cs.w = 0u;
+        cp.x = 0u;
+        cp.y = loV0 + (e % C::VST) * (C::TILE_BYTES >> 4);
+        cp.z = (e % C::VST) | (((e / C::VST) & 1) ? CMD_PARITY : 0u) | (first_of_entry ? CMD_WAIT : 0u) | (last_of_entry ? CMD_RELEASE : 0u) |
+               (rank_tile == 0 ? 0u : CMD_ACC) | (i ? CMD_TILE1 : 0u);
+        cp.w = 0u;
+        sCmd[2 * u] = cs;
+        sCmd[2 * u + 1] = cp;
+        sWcmd[i * 256 + rank_tile] = (sList[e] & 0xFFu) | (unit_class(un) << 8) | (static_cast<uint32_t>(buf) << 10) |
+                                     (static_cast<uint32_t>(rank_key & 1) << 12);
+      }
+    }
+    if (lane == 0) {
+      int t0 = 0, t1 = 0;
+#pragma unroll
+      for (int j = 0; j < C::NBUF; ++j) { t0 += cnt_key[2 * j]; t1 += cnt_key[2 * j + 1]; }
+      n_own_s[0] = t0;
+      n_own_s[1] = t1;
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tbase = tmem_base_s;
-  const uint16_t* list = sList;
+  const int U = n_units_s;
   Tracer tr;
-  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 0 || warp == 1 || warp == 4 || warp == 8),
-          blockIdx.z * 4 + (warp == 0 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));
+  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 3 || warp == 1 || warp == 4 || warp == 8),
+          blockIdx.z * 4 + (warp == 3 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));
   tr.ev(1);
 
   if (warp < 4) {
-    reg_dealloc<56>();
+    reg_dealloc<KD_REGS_ISSUE>();
     if (warp == 0 && lane == 0 && n > 0) {
       // ------------------------------ TMA producer ------------------------------
       tma_prefetch_desc(&tmQ);
@@ -129,121 +242,99 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int kb = 0; kb < C::KBLK; ++kb)
           tma_load_4d(sQ + t * C::TILE_BYTES + kb * 16384, &tmQ, smem_u32(&bar_q_full), kb * 64,
                       (2 * pair + t) * KD_TILE, h, b);
-      bool ok = true;
-      int issued = 0;
-      for (int e = 0; e < n && ok; ++e) {
-        const int s = e % C::STAGES;
-        const uint32_t ph = (e / C::STAGES) & 1;
-        const int kt = list[e] & 0xFF;
-        ok = mbar_wait(smem_u32(&bar_k_empty[s]), ph ^ 1, &abortf, a.status, W_F_KEMPTY);
-        if (!ok) break;
-        mbar_arrive_expect_tx(smem_u32(&bar_k_full[s]), C::TILE_BYTES);
-        for (int kb = 0; kb < C::KBLK; ++kb)
-          tma_load_4d(sK + s * C::TILE_BYTES + kb * 16384, &tmK, smem_u32(&bar_k_full[s]), kb * 64,
-                      kt * KD_TILE, h, b);
-        ok = mbar_wait(smem_u32(&bar_v_empty[s]), ph ^ 1, &abortf, a.status, W_F_VEMPTY);
-        if (!ok) {
-          // the K load just issued must land before this CTA may exit
-          for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_k_full[s]), ph); ++spin) {}
-          break;
+      int k_issued = 0, v_issued = 0;
+      for (int e = 0; e < n; ++e) {
+        const int kt = sList[e] & 0xFF;
+        {
+          const int s = e % C::KST;
+          if (!mbar_wait(smem_u32(&bar_k_empty[s]), ((e / C::KST) & 1) ^ 1, &abortf, a.status, W_F_KEMPTY)) break;
+          mbar_arrive_expect_tx(smem_u32(&bar_k_full[s]), C::TILE_BYTES);
+          for (int kb = 0; kb < C::KBLK; ++kb)
+            tma_load_4d(sK + s * C::TILE_BYTES + kb * 16384, &tmK, smem_u32(&bar_k_full[s]), kb * 64, kt * KD_TILE, h, b);
+          k_issued = e + 1;
         }
-        mbar_arrive_expect_tx(smem_u32(&bar_v_full[s]), C::TILE_BYTES);
-        for (int kb = 0; kb < C::KBLK; ++kb)
-          tma_load_4d(sV + s * C::TILE_BYTES + kb * 16384, &tmV, smem_u32(&bar_v_full[s]), kb * 64,
-                      kt * KD_TILE, h, b);
-        issued = e + 1;
+        {
+          const int s = e % C::VST;
+          if (!mbar_wait(smem_u32(&bar_v_empty[s]), ((e / C::VST) & 1) ^ 1, &abortf, a.status, W_F_VEMPTY)) break;
+          mbar_arrive_expect_tx(smem_u32(&bar_v_full[s]), C::TILE_BYTES);
+          for (int kb = 0; kb < C::KBLK; ++kb)
+            tma_load_4d(sV + s * C::TILE_BYTES + kb * 16384, &tmV, smem_u32(&bar_v_full[s]), kb * 64, kt * KD_TILE, h, b);
+          v_issued = e + 1;
+        }
       }
       if (abortf.v != 0) {
         // unwinding: let every copy already in flight land (bounded) before the CTA exits
-        for (int e = max(0, issued - C::STAGES); e < issued; ++e) {
-          const int s = e % C::STAGES;
-          const uint32_t ph = (e / C::STAGES) & 1;
-          for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_k_full[s]), ph); ++spin) {}
-          for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_v_full[s]), ph); ++spin) {}
-        }
-        for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_q_full), 0); ++spin) {}
+        for (int e = max(0, k_issued - C::KST); e < k_issued; ++e) drain_wait(smem_u32(&bar_k_full[e % C::KST]), (e / C::KST) & 1);
+        for (int e = max(0, v_issued - C::VST); e < v_issued; ++e) drain_wait(smem_u32(&bar_v_full[e % C::VST]), (e / C::VST) & 1);
+        drain_wait(smem_u32(&bar_q_full), 0);
       }
-    } else if (warp == 1 && lane == 0 && n > 0) {
-      // ------------------------------ MMA issuer ------------------------------
+    } else if (warp == 3 && lane == 0 && U > 0) {
+      // ------------------------------ S issuer ------------------------------
       const uint32_t idesc_s = make_idesc_f16(kBf16, 0, 0, KD_TILE, KD_TILE);
-      const uint32_t idesc_o = make_idesc_f16(kBf16, 0, 1, KD_TILE, HD);
-      const uint32_t tS[2] = {tbase + C::TM_S0, tbase + C::TM_S1};
-      const uint32_t tO[2] = {tbase + C::TM_O0, tbase + C::TM_O1};
-      const uint32_t tP[2] = {tbase + C::TM_P0, tbase + C::TM_P1};
       const uint32_t hi = desc_hi_sw128();
-      const uint32_t loQ[2] = {desc_lo_kmajor(sQ), desc_lo_kmajor(sQ + C::TILE_BYTES)};
-      const uint32_t loK0 = desc_lo_kmajor(sK), loV0 = desc_lo_mnmajor(sV);
-      auto issue_s = [&](int i, int e) {
-        const uint32_t kb = loK0 + (e % C::STAGES) * (C::TILE_BYTES >> 4);
+      bool ok = mbar_wait(smem_u32(&bar_q_full), 0, &abortf, a.status, W_F_QFULL);
+      int buf = 0, round = 0;      // unit u uses buffer u % NBUF in round u / NBUF
+      for (int u = 0; u < U && ok; ++u) {
+        const uint4 c = sCmd[2 * u];
+        if (round > 0) {
+          // the buffer is free once P V of the unit that used it in the previous round has been issued
+          ok = mbar_wait(smem_u32(&bar_pv_issued[buf]), (round - 1) & 1, &abortf, a.status, W_F_PVISSUED);
+          if (!ok) break;
+        }
+        if (c.z & CMD_WAIT) {
+          ok = mbar_wait(smem_u32(&bar_k_full[c.z & CMD_STAGE]), (c.z & CMD_PARITY) ? 1u : 0u, &abortf, a.status, W_F_KFULL);
+          if (!ok) break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d = tbase + buf * 128;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss_split(tS[i], loQ[i] + koff_kmajor(kk), kb + koff_kmajor(kk), hi, idesc_s, kk > 0 ? 1u : 0u);
-        mma_commit(smem_u32(&bar_s_full[i]));
-      };
-      auto issue_pv = [&](int i, int e, bool acc) {
-        const uint32_t vb = loV0 + (e % C::STAGES) * (C::TILE_BYTES >> 4);
+          mma_ss_split(d, c.x + koff_kmajor(kk), c.y + koff_kmajor(kk), hi, idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(smem_u32(&bar_s_full[2 * buf + ((c.z & CMD_TILE1) ? 1 : 0)]));
+        if (c.z & CMD_RELEASE) mma_commit(smem_u32(&bar_k_empty[c.z & CMD_STAGE]));
+        tr.ev(15);
+        if (++buf == C::NBUF) {
+          buf = 0;
+          ++round;
+        }
+      }
+    } else if (warp == 1 && lane == 0 && U > 0) {
+      // ------------------------------ P V issuer ------------------------------
+      const uint32_t idesc_o = make_idesc_f16(kBf16, 0, 1, KD_TILE, HD);
+      const uint32_t hi = desc_hi_sw128();
+      bool ok = true;
+      int buf = 0;
+      uint32_t round_parity = 0;
+      for (int u = 0; u < U && ok; ++u) {
+        const uint4 c = sCmd[2 * u + 1];
+        ok = mbar_wait(smem_u32(&bar_p_full[buf]), round_parity, &abortf, a.status, W_F_PFULL);
+        if (!ok) break;
+        tr.ev(10);
+        if (c.z & CMD_WAIT) {
+          ok = mbar_wait(smem_u32(&bar_v_full[c.z & CMD_STAGE]), (c.z & CMD_PARITY) ? 1u : 0u, &abortf, a.status, W_F_VFULL);
+          if (!ok) break;
+        }
+        tc_fence_after_sync();
+        const uint32_t i = (c.z & CMD_TILE1) ? 1u : 0u;
+        const uint32_t dO = tbase + C::TM_O0 + i * HD, aP = tbase + buf * 128;
+        const uint32_t acc0 = (c.z & CMD_ACC) ? 1u : 0u;
 #pragma unroll
         for (int kk = 0; kk < KD_TILE / 16; ++kk)
-          mma_ts_split(tO[i], tP[i] + kk * 8, vb + koff_mnmajor(kk), hi, idesc_o, (acc || kk > 0) ? 1u : 0u);
-      };
-      int last_act[2] = {-1, -1};
-      for (int e = 0; e < n; ++e) {
-        const uint32_t ent = list[e];
-        if ((ent >> 8) & 3) last_act[0] = e;
-        if ((ent >> 10) & 3) last_act[1] = e;
-      }
-      bool ok = mbar_wait(smem_u32(&bar_q_full), 0, &abortf, a.status, W_F_QFULL);
-      if (ok) ok = mbar_wait(smem_u32(&bar_k_full[0]), 0, &abortf, a.status, W_F_KFULL);
-      if (ok) {
-        tc_fence_after_sync();
-        const uint32_t ent0 = list[0];
-        if ((ent0 >> 8) & 3) issue_s(0, 0);
-        if ((ent0 >> 10) & 3) issue_s(1, 0);
-        mma_commit(smem_u32(&bar_k_empty[0]));
-      }
-      bool used[2] = {false, false};
-      uint32_t pphase[2] = {0, 0};
-      for (int e = 0; e < n && ok; ++e) {
-        const uint32_t ent = list[e];
-        const uint32_t nxt = (e + 1 < n) ? list[e + 1] : 0u;
-        const int s = e % C::STAGES;
-        bool v_waited = false, k_waited = false;
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          if ((ent >> (8 + 2 * i)) & 3) {
-            ok = mbar_wait(smem_u32(&bar_p_full[i]), pphase[i], &abortf, a.status, W_F_PFULL);
-            if (!ok) break;
-            pphase[i] ^= 1;
-            if (!v_waited) {
-              ok = mbar_wait(smem_u32(&bar_v_full[s]), (e / C::STAGES) & 1, &abortf, a.status, W_F_VFULL);
-              if (!ok) break;
-              v_waited = true;
-            }
-            tr.ev(10 + 2 * i);
-            tc_fence_after_sync();
-            issue_pv(i, e, used[i]);
-            used[i] = true;
-            if (e == last_act[i]) mma_commit(smem_u32(&bar_o_full[i]));
-          }
-          if ((nxt >> (8 + 2 * i)) & 3) {
-            if (!k_waited) {
-              ok = mbar_wait(smem_u32(&bar_k_full[(e + 1) % C::STAGES]), ((e + 1) / C::STAGES) & 1, &abortf,
-                             a.status, W_F_KFULL);
-              if (!ok) break;
-              k_waited = true;
-              tc_fence_after_sync();
-            }
-            issue_s(i, e + 1);
-          }
-          tr.ev(11 + 2 * i);
+          mma_ts_split(dO, aP + kk * 8, c.y + koff_mnmajor(kk), hi, idesc_o, kk > 0 ? 1u : acc0);
+        mma_commit(smem_u32(&bar_pv_done[i]));
+        if (c.z & CMD_RELEASE) mma_commit(smem_u32(&bar_v_empty[c.z & CMD_STAGE]));
+        // hand the buffer back to the S issuer, ordered after the MMAs above
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(&bar_pv_issued[buf]));
+        tr.ev(11);
+        if (++buf == C::NBUF) {
+          buf = 0;
+          round_parity ^= 1;
         }
-        if (!ok) break;
-        mma_commit(smem_u32(&bar_v_empty[s]));
-        if (e + 1 < n) mma_commit(smem_u32(&bar_k_empty[(e + 1) % C::STAGES]));
       }
     }
   } else {
-    reg_alloc<224>();
+    reg_alloc<KD_REGS_COMPUTE>();
     // ------------------------------ softmax warpgroups ------------------------------
     const int i = (warp - 4) >> 2;        // query tile of the pair
     const int wq = warp & 3;              // TMEM lane quadrant of this warp
@@ -253,39 +344,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const bool tile_valid = qtile < a.NT;
     uint32_t* kd_buf = sKdesc + (size_t)(warp - 4) * KD_TILE;   // this warp's copy of a key tile's descriptors
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
-    const uint32_t tS = tbase + lane_base + (i == 0 ? C::TM_S0 : C::TM_S1);
     const uint32_t tO = tbase + lane_base + (i == 0 ? C::TM_O0 : C::TM_O1);
-    const uint32_t tP = tbase + lane_base + (i == 0 ? C::TM_P0 : C::TM_P1);
     const float c = a.scale_log2;
 
     const uint32_t qd = tile_valid ? a.desc[(size_t)b * a.Tpad + qi] : 0u;
     float m = -INFINITY, l = 0.f;
-    uint32_t sphase = 0;
     int nact = 0;
     bool ok = true;
 
-    // Key descriptors of PARTIAL tiles are fetched one active entry ahead into registers, so their
+    // Key descriptors of PARTIAL tiles are fetched one unit ahead into registers, so their
     // global-memory latency overlaps the previous tile's softmax.
-    auto next_active = [&](int from) {
-      int e = from;
-      while (e < n && ((list[e] >> (8 + 2 * i)) & 3u) == KD_TILE_EMPTY) ++e;
-      return e;
-    };
+    const int n_own = n_own_s[i];
+    const uint32_t* wcmd = sWcmd + i * 256;
     uint32_t kd_pre[4] = {0u, 0u, 0u, 0u};
-    auto prefetch_kd = [&](int e) {
-      if (e < n && ((list[e] >> (8 + 2 * i)) & 3u) == KD_TILE_PARTIAL) {
-        const uint32_t* src = a.desc + (size_t)b * a.Tpad + (size_t)(list[e] & 0xFFu) * KD_TILE;
+    auto prefetch_kd = [&](uint32_t c) {
+      if (wcmd_class(c) == KD_TILE_PARTIAL) {
+        const uint32_t* src = a.desc + (size_t)b * a.Tpad + (size_t)wcmd_kt(c) * KD_TILE;
 #pragma unroll
         for (int j = 0; j < 4; ++j) kd_pre[j] = src[j * 32 + lane];
       }
     };
-    int e = next_active(0);
-    prefetch_kd(e);
+    uint32_t cmd_next = n_own > 0 ? wcmd[0] : 0u;
+    if (n_own > 0) prefetch_kd(cmd_next);
 
-    while (e < n) {
-      const uint32_t ent = list[e];
-      const uint32_t cls = (ent >> (8 + 2 * i)) & 3;
-      const int kt = ent & 0xFF;
+    for (int k = 0; k < n_own; ++k) {
+      const uint32_t cmd = cmd_next;
+      const uint32_t cls = wcmd_class(cmd);
+      const int kt = wcmd_kt(cmd);
+      const int buf = wcmd_buf(cmd);
+      const uint32_t tS = tbase + lane_base + buf * 128;
       tr.ev(20);
       if (cls == KD_TILE_PARTIAL) {
         __syncwarp();
@@ -293,13 +380,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int j = 0; j < 4; ++j) kd_buf[j * 32 + lane] = kd_pre[j];
         __syncwarp();
       }
-      e = next_active(e + 1);
-      prefetch_kd(e);
+      if (k + 1 < n_own) {
+        cmd_next = wcmd[k + 1];
+        prefetch_kd(cmd_next);
+      }
       tr.ev(21);
-      ok = mbar_wait(smem_u32(&bar_s_full[i]), sphase, &abortf, a.status, W_F_SFULL);
+      ok = mbar_wait(smem_u32(&bar_s_full[2 * buf + i]), wcmd_parity(cmd), &abortf, a.status, W_F_SFULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      sphase ^= 1;
       tc_fence_after_sync();
       tr.ev(22);
 
@@ -352,9 +440,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         uint32_t r[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) r[j] = pk[cb * 32 + j];
-        tmem_st32(tP + cb * 32, r);
+        tmem_st32(tS + cb * 32, r);   // P over the first 64 columns of this thread's own score row
+      }
+      if (nact > 0) {
+        // O_i may be touched only after the previous P V product of this query tile has completed;
+        // the wait is taken for every unit so that no phase of the barrier goes unobserved
+        ok = mbar_wait(smem_u32(&bar_pv_done[i]), (nact - 1) & 1, &abortf, a.status, W_F_PVDONE);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
       }
       if (__any_sync(0xffffffffu, need_rescale)) {
+        tc_fence_after_sync();
         const float f = need_rescale ? alpha : 1.f;
 #pragma unroll
         for (int cb = 0; cb < HD / 32; ++cb) {
@@ -369,16 +465,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tr.ev(24);
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(smem_u32(&bar_p_full[i]));
+      mbar_arrive(smem_u32(&bar_p_full[buf]));
       tr.ev(25);
       ++nact;
     }
 
     // epilogue: normalise, convert, store O and LSE
     if (ok && nact > 0) {
-      ok = mbar_wait(smem_u32(&bar_o_full[i]), 0, &abortf, a.status, W_F_OFULL);
+      ok = mbar_wait(smem_u32(&bar_pv_done[i]), (nact - 1) & 1, &abortf, a.status, W_F_PVDONE);
       ok = __all_sync(0xffffffffu, ok);
     }
+    tr.ev(30);
     if (ok && tile_valid && qi < a.T) {
       a.lse[((size_t)b * a.H + h) * a.T + qi] = (l > 0.f) ? (m * c + log2f(l)) : -INFINITY;
     }
@@ -396,17 +493,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
-        if (tile_valid && qi < a.T) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            uint4 v;
-            v.x = pack2<kBf16>(__uint_as_float(r[j + 0]) * inv_l, __uint_as_float(r[j + 1]) * inv_l);
-            v.y = pack2<kBf16>(__uint_as_float(r[j + 2]) * inv_l, __uint_as_float(r[j + 3]) * inv_l);
-            v.z = pack2<kBf16>(__uint_as_float(r[j + 4]) * inv_l, __uint_as_float(r[j + 5]) * inv_l);
-            v.w = pack2<kBf16>(__uint_as_float(r[j + 6]) * inv_l, __uint_as_float(r[j + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(orow + cb * 32 + j) = v;
-          }
-        }
+        if (tile_valid && qi < a.T) store_row32<kBf16>(orow + cb * 32, r, inv_l);
       }
     }
   }
