@@ -15,6 +15,8 @@
 //   M1(u): S_u, dP_u  (smem x smem -> TMEM, N = 64)      compute(u): P_u / dS_u -> TMEM (16 bit)
 //   M2(u): accumulators += (P_u | dS_u) x smem operand   (A from TMEM);   then M1(u + NBUF)
 // The tensor pipe executes in issue order, so M1(u + NBUF) may overwrite the buffer M2(u) read.
+// M1 and M2 are issued by two different single threads (warps 3 and 1): each shares its scheduler
+// with two compute warps, and splitting the work keeps either one off the critical path.
 #include "attn_common.cuh"
 
 namespace kd {
@@ -68,9 +70,9 @@ struct BwdCfg {
 
 enum : uint32_t {
   W_Q_FIXFULL = 0x201, W_Q_RINGEMPTY = 0x202, W_Q_RINGFULL = 0x203, W_Q_PFULL = 0x204, W_Q_SFULL = 0x205,
-  W_Q_ACCFULL = 0x206,
+  W_Q_ACCFULL = 0x206, W_Q_M2ISSUED = 0x207,
   W_K_FIXFULL = 0x301, W_K_RINGEMPTY = 0x302, W_K_RINGFULL = 0x303, W_K_PFULL = 0x304, W_K_SFULL = 0x305,
-  W_K_ACCFULL = 0x306,
+  W_K_ACCFULL = 0x306, W_K_M2ISSUED = 0x307,
 };
 
 // =========================================================================================
@@ -92,7 +94,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint16_t* sAct = reinterpret_cast<uint16_t*>(smem + C::SMEM_ACT);
 
   __shared__ __align__(8) uint64_t bar_fix_full, bar_ring_full[C::STAGES], bar_ring_empty[C::STAGES],
-      bar_s_full[C::NBUF], bar_p_full[C::NBUF], bar_acc_full;
+      bar_s_full[C::NBUF], bar_p_full[C::NBUF], bar_m2_issued[C::NBUF], bar_acc_full;
   __shared__ uint32_t tmem_base_s;
   __shared__ int n_act_s;
   __shared__ AbortFlag abortf;
@@ -112,6 +114,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int i = 0; i < C::NBUF; ++i) {
       mbar_init(smem_u32(&bar_s_full[i]), 1);
       mbar_init(smem_u32(&bar_p_full[i]), 128);
+      mbar_init(smem_u32(&bar_m2_issued[i]), 1);
     }
     mbar_init(smem_u32(&bar_acc_full), 1);
     fence_barrier_init();
@@ -141,8 +144,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t tbase = tmem_base_s;
   const int na = n_act_s;
   Tracer tr;
-  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 0 || warp == 1 || warp == 4 || warp == 8),
-          blockIdx.z * 4 + (warp == 0 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));
+  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 3 || warp == 1 || warp == 4 || warp == 8),
+          blockIdx.z * 4 + (warp == 3 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));
   tr.ev(1);
 
   if (warp < 4) {
@@ -177,53 +180,67 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_ring_full[e % C::STAGES]), (e / C::STAGES) & 1); ++spin) {}
         for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_fix_full), 0); ++spin) {}
       }
-    } else if (warp == 1 && lane == 0 && na > 0) {
-      // ------------------------------ MMA issuer ------------------------------
-      const uint32_t idesc_m1 = make_idesc_f16(kBf16, 0, 0, KD_TILE, 64);   // S_u, dP_u: N = 64 keys
-      const uint32_t idesc_m2 = make_idesc_f16(kBf16, 0, 1, KD_TILE, HD);   // dQ: B = K rows, MN-major
-      const uint32_t tAcc = tbase + C::TM_ACC0;
+    } else if (warp == 3 && lane == 0 && na > 0) {
+      // ------------------------------ M1 issuer: S_u = Q K_u^T, dP_u = dO V_u^T ------------------------------
+      const uint32_t idesc_m1 = make_idesc_f16(kBf16, 0, 0, KD_TILE, 64);   // N = 64 keys
       const uint32_t hi = desc_hi_sw128();
-      const uint32_t loQ = desc_lo_kmajor(sQ), loDO = desc_lo_kmajor(sDO);
-      const uint32_t loRingK = desc_lo_kmajor(sRing), loRingMN = desc_lo_mnmajor(sRing);
+      const uint32_t loQ = desc_lo_kmajor(sQ), loDO = desc_lo_kmajor(sDO), loRingK = desc_lo_kmajor(sRing);
       const int U = 2 * na;
-      int ring_ready = -1;
       bool ok = mbar_wait(smem_u32(&bar_fix_full), 0, &abortf, a.status, W_Q_FIXFULL);
-      auto issue_m1 = [&](int u) -> bool {
-        const int e = u >> 1, i = u & 1;
-        if (e != ring_ready) {
-          if (!mbar_wait(smem_u32(&bar_ring_full[e % C::STAGES]), (e / C::STAGES) & 1, &abortf, a.status, W_Q_RINGFULL)) return false;
-          ring_ready = e;
-          tc_fence_after_sync();
+      int buf = 0, round = 0, stage = 0;
+      uint32_t ring_parity = 0;
+      for (int u = 0; u < U && ok; ++u) {
+        const int i = u & 1;
+        if (round > 0) {   // buffer free once M2 of its previous unit has been issued
+          ok = mbar_wait(smem_u32(&bar_m2_issued[buf]), (round - 1) & 1, &abortf, a.status, W_Q_M2ISSUED);
+          if (!ok) break;
         }
-        const uint32_t kb = loRingK + (e % C::STAGES) * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);  // key rows 64i..
+        if (i == 0) {      // first unit of a new entry: its K and V tiles must have landed
+          ok = mbar_wait(smem_u32(&bar_ring_full[stage]), ring_parity, &abortf, a.status, W_Q_RINGFULL);
+          if (!ok) break;
+        }
+        tc_fence_after_sync();
+        const uint32_t kb = loRingK + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);  // key rows 64i..
         const uint32_t vb = kb + (C::TILE_BYTES >> 4);
-        const uint32_t dS = tbase + (u % C::NBUF) * 128, dP = dS + 64;
+        const uint32_t dS = tbase + buf * 128, dP = dS + 64;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
           mma_ss_split(dS, loQ + koff_kmajor(kk), kb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
           mma_ss_split(dP, loDO + koff_kmajor(kk), vb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
-        mma_commit(smem_u32(&bar_s_full[u % C::NBUF]));
-        return true;
-      };
-      for (int u = 0; u < C::NBUF && u < U && ok; ++u) ok = issue_m1(u);
+        mma_commit(smem_u32(&bar_s_full[buf]));
+        tr.ev(15);
+        if (++buf == C::NBUF) { buf = 0; ++round; }
+        if (i == 1 && ++stage == C::STAGES) { stage = 0; ring_parity ^= 1; }
+      }
+    } else if (warp == 1 && lane == 0 && na > 0) {
+      // ------------------------------ M2 issuer: dQ += dS_u K_u ------------------------------
+      const uint32_t idesc_m2 = make_idesc_f16(kBf16, 0, 1, KD_TILE, HD);   // B = K rows, MN-major
+      const uint32_t tAcc = tbase + C::TM_ACC0;
+      const uint32_t hi = desc_hi_sw128();
+      const uint32_t loRingMN = desc_lo_mnmajor(sRing);
+      const int U = 2 * na;
+      bool ok = true;
+      int buf = 0, stage = 0;
+      uint32_t round_parity = 0;
       for (int u = 0; u < U && ok; ++u) {
-        const int e = u >> 1, i = u & 1, buf = u % C::NBUF;
-        ok = mbar_wait(smem_u32(&bar_p_full[buf]), (u / C::NBUF) & 1, &abortf, a.status, W_Q_PFULL);
+        const int i = u & 1;
+        ok = mbar_wait(smem_u32(&bar_p_full[buf]), round_parity, &abortf, a.status, W_Q_PFULL);
         if (!ok) break;
         tr.ev(10);
         tc_fence_after_sync();
-        {
-          const uint32_t kb = loRingMN + (e % C::STAGES) * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
-          const uint32_t aS = tbase + buf * 128;   // dS_u sits on top of S_u
+        const uint32_t kb = loRingMN + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
+        const uint32_t aS = tbase + buf * 128;   // dS_u sits on top of S_u
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)  // 64 keys of this unit, 16 per MMA
-            mma_ts_split(tAcc, aS + kk * 8, kb + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
-        }
-        if (i == 1) mma_commit(smem_u32(&bar_ring_empty[e % C::STAGES]));
-        if (u + C::NBUF < U) ok = issue_m1(u + C::NBUF);
+        for (int kk = 0; kk < 4; ++kk)  // 64 keys of this unit, 16 per MMA
+          mma_ts_split(tAcc, aS + kk * 8, kb + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
+        if (i == 1) mma_commit(smem_u32(&bar_ring_empty[stage]));
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(&bar_m2_issued[buf]));
         tr.ev(11);
+        if (++buf == C::NBUF) { buf = 0; round_parity ^= 1; }
+        if (i == 1 && ++stage == C::STAGES) stage = 0;
       }
       if (ok) mma_commit(smem_u32(&bar_acc_full));
     }
@@ -376,7 +393,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint16_t* sList = reinterpret_cast<uint16_t*>(smem + C::SMEM_ACT);
 
   __shared__ __align__(8) uint64_t bar_fix_full, bar_ring_full[C::STAGES], bar_ring_empty[C::STAGES],
-      bar_s_full[C::NBUF], bar_p_full[C::NBUF], bar_acc_full;
+      bar_s_full[C::NBUF], bar_p_full[C::NBUF], bar_m2_issued[C::NBUF], bar_acc_full;
   __shared__ uint32_t tmem_base_s;
   __shared__ AbortFlag abortf;
 
@@ -395,6 +412,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     for (int i = 0; i < C::NBUF; ++i) {
       mbar_init(smem_u32(&bar_s_full[i]), 1);
       mbar_init(smem_u32(&bar_p_full[i]), 128);
+      mbar_init(smem_u32(&bar_m2_issued[i]), 1);
     }
     mbar_init(smem_u32(&bar_acc_full), 1);
     fence_barrier_init();
@@ -413,8 +431,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t tbase = tmem_base_s;
   const uint16_t* list = sList;
   Tracer tr;
-  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 0 || warp == 1 || warp == 4 || warp == 8),
-          blockIdx.z * 4 + (warp == 0 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));
+  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 3 || warp == 1 || warp == 4 || warp == 8),
+          blockIdx.z * 4 + (warp == 3 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));
   tr.ev(1);
 
   if (warp < 4) {
@@ -450,59 +468,71 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_ring_full[e % C::STAGES]), (e / C::STAGES) & 1); ++spin) {}
         for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_fix_full), 0); ++spin) {}
       }
-    } else if (warp == 1 && lane == 0 && n > 0) {
-      // ------------------------------ MMA issuer ------------------------------
-      const uint32_t idesc_m1 = make_idesc_f16(kBf16, 0, 0, KD_TILE, 64);   // S^T_u, dP^T_u: N = 64 queries
-      const uint32_t idesc_m2 = make_idesc_f16(kBf16, 0, 1, KD_TILE, HD);   // dV, dK: B = dO / Q rows, MN-major
-      const uint32_t tDK = tbase + C::TM_ACC0, tDV = tbase + C::TM_ACC1;
+    } else if (warp == 3 && lane == 0 && n > 0) {
+      // ------------------------------ M1 issuer: S^T_u = K Q_u^T, dP^T_u = V dO_u^T ------------------------------
+      const uint32_t idesc_m1 = make_idesc_f16(kBf16, 0, 0, KD_TILE, 64);   // N = 64 queries
       const uint32_t hi = desc_hi_sw128();
-      const uint32_t loK = desc_lo_kmajor(sK), loV = desc_lo_kmajor(sV);
-      const uint32_t loRingK = desc_lo_kmajor(sRing), loRingMN = desc_lo_mnmajor(sRing);
+      const uint32_t loK = desc_lo_kmajor(sK), loV = desc_lo_kmajor(sV), loRingK = desc_lo_kmajor(sRing);
       const int U = 2 * n;
-      int ring_ready = -1;
       bool ok = mbar_wait(smem_u32(&bar_fix_full), 0, &abortf, a.status, W_K_FIXFULL);
-      tr.ev(2);
-      auto issue_m1 = [&](int u) -> bool {
-        const int e = u >> 1, i = u & 1;
-        if (e != ring_ready) {
-          if (!mbar_wait(smem_u32(&bar_ring_full[e % C::STAGES]), (e / C::STAGES) & 1, &abortf, a.status, W_K_RINGFULL)) return false;
-          ring_ready = e;
-          tc_fence_after_sync();
+      int buf = 0, round = 0, stage = 0;
+      uint32_t ring_parity = 0;
+      for (int u = 0; u < U && ok; ++u) {
+        const int i = u & 1;
+        if (round > 0) {   // buffer free once M2 of its previous unit has been issued
+          ok = mbar_wait(smem_u32(&bar_m2_issued[buf]), (round - 1) & 1, &abortf, a.status, W_K_M2ISSUED);
+          if (!ok) break;
         }
-        const uint32_t qb = loRingK + (e % C::STAGES) * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);  // query rows 64i..
+        if (i == 0) {      // first unit of a new entry: its Q and dO tiles must have landed
+          ok = mbar_wait(smem_u32(&bar_ring_full[stage]), ring_parity, &abortf, a.status, W_K_RINGFULL);
+          if (!ok) break;
+        }
+        tc_fence_after_sync();
+        const uint32_t qb = loRingK + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);  // query rows 64i..
         const uint32_t dob = qb + (C::TILE_BYTES >> 4);
-        const uint32_t dS = tbase + (u % C::NBUF) * 128, dP = dS + 64;
+        const uint32_t dS = tbase + buf * 128, dP = dS + 64;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
           mma_ss_split(dS, loK + koff_kmajor(kk), qb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
           mma_ss_split(dP, loV + koff_kmajor(kk), dob + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
-        mma_commit(smem_u32(&bar_s_full[u % C::NBUF]));
-        return true;
-      };
-      for (int u = 0; u < C::NBUF && u < U && ok; ++u) ok = issue_m1(u);
-      tr.ev(3);
+        mma_commit(smem_u32(&bar_s_full[buf]));
+        tr.ev(15);
+        if (++buf == C::NBUF) { buf = 0; ++round; }
+        if (i == 1 && ++stage == C::STAGES) { stage = 0; ring_parity ^= 1; }
+      }
+    } else if (warp == 1 && lane == 0 && n > 0) {
+      // ------------------------------ M2 issuer: dV += P^T_u dO_u, dK += dS^T_u Q_u ------------------------------
+      const uint32_t idesc_m2 = make_idesc_f16(kBf16, 0, 1, KD_TILE, HD);   // B = dO / Q rows, MN-major
+      const uint32_t tDK = tbase + C::TM_ACC0, tDV = tbase + C::TM_ACC1;
+      const uint32_t hi = desc_hi_sw128();
+      const uint32_t loRingMN = desc_lo_mnmajor(sRing);
+      const int U = 2 * n;
+      bool ok = true;
+      int buf = 0, stage = 0;
+      uint32_t round_parity = 0;
       for (int u = 0; u < U && ok; ++u) {
-        const int e = u >> 1, i = u & 1, buf = u % C::NBUF;
-        ok = mbar_wait(smem_u32(&bar_p_full[buf]), (u / C::NBUF) & 1, &abortf, a.status, W_K_PFULL);
+        const int i = u & 1;
+        ok = mbar_wait(smem_u32(&bar_p_full[buf]), round_parity, &abortf, a.status, W_K_PFULL);
         if (!ok) break;
         tr.ev(10);
         tc_fence_after_sync();
-        {
-          const uint32_t qb = loRingMN + (e % C::STAGES) * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
-          const uint32_t dob = qb + (C::TILE_BYTES >> 4);
-          const uint32_t aS = tbase + buf * 128, aP = aS + 64;
+        const uint32_t qb = loRingMN + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
+        const uint32_t dob = qb + (C::TILE_BYTES >> 4);
+        const uint32_t aS = tbase + buf * 128, aP = aS + 64;
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)  // dV += P^T_u dO_u   (P^T_u on top of S^T_u)
-            mma_ts_split(tDV, aS + kk * 8, dob + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < 4; ++kk)  // dV += P^T_u dO_u   (P^T_u on top of S^T_u)
+          mma_ts_split(tDV, aS + kk * 8, dob + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)  // dK += dS^T_u Q_u   (dS^T_u on top of dP^T_u)
-            mma_ts_split(tDK, aP + kk * 8, qb + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
-        }
-        if (i == 1) mma_commit(smem_u32(&bar_ring_empty[e % C::STAGES]));
-        if (u + C::NBUF < U) ok = issue_m1(u + C::NBUF);
+        for (int kk = 0; kk < 4; ++kk)  // dK += dS^T_u Q_u   (dS^T_u on top of dP^T_u)
+          mma_ts_split(tDK, aP + kk * 8, qb + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
+        if (i == 1) mma_commit(smem_u32(&bar_ring_empty[stage]));
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(&bar_m2_issued[buf]));
         tr.ev(11);
+        if (++buf == C::NBUF) { buf = 0; round_parity ^= 1; }
+        if (i == 1 && ++stage == C::STAGES) stage = 0;
       }
       if (ok) mma_commit(smem_u32(&bar_acc_full));
     }

@@ -412,9 +412,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           if (!rule_allowed(qd, qi, k4.w, j0 + j + 3)) s[j + 3] = -INFINITY;
         }
       }
-      float mx = s[0];
+      // four independent chains for the row maximum and for the row sum: a single chain of 127
+      // dependent operations would be latency-bound
+      float mx4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-      for (int j = 1; j < KD_TILE; ++j) mx = fmaxf(mx, s[j]);
+      for (int j = 4; j < KD_TILE; j += 4) {
+        mx4[0] = fmaxf(mx4[0], s[j + 0]);
+        mx4[1] = fmaxf(mx4[1], s[j + 1]);
+        mx4[2] = fmaxf(mx4[2], s[j + 2]);
+        mx4[3] = fmaxf(mx4[3], s[j + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // The running maximum is refreshed only when it would grow by more than 2^8 in the
       // exponent; until then the stale value is used consistently for P, l and O, which leaves
       // the normalised result unchanged and skips most O rescales.
@@ -424,15 +432,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const float alpha = (m == -INFINITY) ? 0.f : fast_exp2((m - m_new) * c);
       const bool need_rescale = (nact > 0) && (m_new != m);
       const float neg_mc = -m_use * c;
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pk[KD_TILE / 2];
 #pragma unroll
-      for (int j = 0; j < KD_TILE; j += 2) {
+      for (int j = 0; j < KD_TILE; j += 4) {
         const float p0 = fast_exp2(fmaf(s[j], c, neg_mc));
         const float p1 = fast_exp2(fmaf(s[j + 1], c, neg_mc));
-        sum += p0 + p1;
+        const float p2 = fast_exp2(fmaf(s[j + 2], c, neg_mc));
+        const float p3 = fast_exp2(fmaf(s[j + 3], c, neg_mc));
+        sum4[0] += p0;
+        sum4[1] += p1;
+        sum4[2] += p2;
+        sum4[3] += p3;
         pk[j / 2] = pack2<kBf16>(p0, p1);
+        pk[j / 2 + 1] = pack2<kBf16>(p2, p3);
       }
+      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       l = l * alpha + sum;
       m = m_new;
 #pragma unroll
