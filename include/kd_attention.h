@@ -73,6 +73,9 @@ typedef struct kd_plan_layout {
   size_t off_fwd_list;   /* uint16 [B][NP][NT]   k_tile | class(q tile 2p) << 8 | class(2p+1) << 10 */
   size_t off_bwd_cnt;    /* int32  [B][NT]       entries in the backward list of a k tile */
   size_t off_bwd_list;   /* uint16 [B][NT][NT]   q_tile | class << 8 */
+  size_t off_tilebits;   /* uint32 [B][NT][8][4] 128-bit masks over the tokens of a tile: 0 is_prefix, 1 context,
+                                                 2 in_span, 3..5 "as a query sees prefix / context / in_span keys
+                                                 regardless of position", 6 same-span rule armed, 7 unused */
   size_t off_order;      /* uint8  [B][3][NT]    tiles sorted by decreasing work: [0] forward q tile
                                                  pairs, [1] dQ q tiles, [2] dK/dV k tiles */
   size_t off_stats;      /* uint32 [B][2]        number of FULL and of PARTIAL tiles */

@@ -40,7 +40,7 @@ class KdPlanLayout(Structure):
         ("B", c_int32), ("T", c_int32), ("NT", c_int32), ("NP", c_int32),
         ("off_desc", c_size_t), ("off_summary", c_size_t), ("off_cls", c_size_t),
         ("off_fwd_cnt", c_size_t), ("off_fwd_list", c_size_t), ("off_bwd_cnt", c_size_t),
-        ("off_bwd_list", c_size_t), ("off_order", c_size_t), ("off_stats", c_size_t), ("off_status", c_size_t),
+        ("off_bwd_list", c_size_t), ("off_tilebits", c_size_t), ("off_order", c_size_t), ("off_stats", c_size_t), ("off_status", c_size_t),
         ("total", c_size_t),
     ]
 

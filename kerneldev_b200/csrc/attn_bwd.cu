@@ -26,6 +26,7 @@ struct BwdArgs {
   float scale_log2;  // sm_scale * log2(e)
   float sm_scale;
   const uint32_t* desc;
+  const uint32_t* tilebits;   // [B][NT][8][4] class masks of every 128-token tile
   const int32_t* fwd_cnt;
   const uint16_t* fwd_list;
   const int32_t* bwd_cnt;
@@ -112,7 +113,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_init(smem_u32(&bar_ring_empty[s]), 1);
     }
     for (int i = 0; i < C::NBUF; ++i) {
-      mbar_init(smem_u32(&bar_s_full[i]), 1);
+      mbar_init(smem_u32(&bar_s_full[i]), 2);     // one commit from each of the two M1 issuers
       mbar_init(smem_u32(&bar_p_full[i]), 128);
       mbar_init(smem_u32(&bar_m2_issued[i]), 1);
     }
@@ -180,8 +181,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_ring_full[e % C::STAGES]), (e / C::STAGES) & 1); ++spin) {}
         for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_fix_full), 0); ++spin) {}
       }
-    } else if (warp == 3 && lane == 0 && na > 0) {
-      // ------------------------------ M1 issuer: S_u = Q K_u^T, dP_u = dO V_u^T ------------------------------
+    } else if ((warp == 3 || warp == 2) && lane == 0 && na > 0) {
+      // ------------------------------ M1 issuers: warp 3: S_u = Q K_u^T; warp 2: dP_u = dO V_u^T ------------------------------
+      const bool dp_part = (warp == 2);
       const uint32_t idesc_m1 = make_idesc_f16(kBf16, 0, 0, KD_TILE, 64);   // N = 64 keys
       const uint32_t hi = desc_hi_sw128();
       const uint32_t loQ = desc_lo_kmajor(sQ), loDO = desc_lo_kmajor(sDO), loRingK = desc_lo_kmajor(sRing);
@@ -203,12 +205,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const uint32_t kb = loRingK + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);  // key rows 64i..
         const uint32_t vb = kb + (C::TILE_BYTES >> 4);
         const uint32_t dS = tbase + buf * 128, dP = dS + 64;
+        if (!dp_part) {
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss_split(dS, loQ + koff_kmajor(kk), kb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < HD / 16; ++kk)
+            mma_ss_split(dS, loQ + koff_kmajor(kk), kb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
+        } else {
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss_split(dP, loDO + koff_kmajor(kk), vb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < HD / 16; ++kk)
+            mma_ss_split(dP, loDO + koff_kmajor(kk), vb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
+        }
         mma_commit(smem_u32(&bar_s_full[buf]));
         tr.ev(15);
         if (++buf == C::NBUF) { buf = 0; ++round; }
@@ -281,11 +286,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
     // key descriptors of PARTIAL tiles are fetched one entry ahead into registers
     uint32_t kd_pre[2] = {0u, 0u};
+    uint32_t tb_pre[6] = {0u, 0u, 0u, 0u, 0u, 0u};   // key-side class masks of this half: is_prefix[2], context[2], in_span[2]
     auto prefetch_kd = [&](int e) {
       if (e < na && (sAct[e] >> 8) == KD_TILE_PARTIAL) {
         const uint32_t* src = a.desc + (size_t)b * a.Tpad + (size_t)(sAct[e] & 0xFFu) * KD_TILE + i * 64;
         kd_pre[0] = src[lane];
         kd_pre[1] = src[32 + lane];
+        const uint2* tbp = reinterpret_cast<const uint2*>(a.tilebits + ((size_t)b * a.NT + (sAct[e] & 0xFFu)) * 32);
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+          const uint2 v = tbp[2 * j + i];   // words 2i, 2i+1 of masks TB_PRE, TB_CTX, TB_INS
+          tb_pre[2 * j] = v.x;
+          tb_pre[2 * j + 1] = v.y;
+        }
       }
     };
     prefetch_kd(0);
@@ -295,11 +308,25 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const uint32_t cls = ent >> 8;
       const int kt = ent & 0xFF;
       const int j0 = kt * KD_TILE + i * 64;  // first key of this stream
+      uint32_t mk[2] = {0xFFFFFFFFu, 0xFFFFFFFFu};   // visibility of this unit's 64 keys for this query row
       if (cls == KD_TILE_PARTIAL) {
         __syncwarp();
         kd_buf[lane] = kd_pre[0];
         kd_buf[32 + lane] = kd_pre[1];
         __syncwarp();
+        query_row_mask<2>(qd, qi, j0, tb_pre + 0, tb_pre + 2, tb_pre + 4, mk);
+        if ((tb_pre[4] | tb_pre[5]) != 0u && __any_sync(0xffffffffu, (qd & TD_SIDPOS) != 0u)) {
+#pragma unroll
+          for (int j = 0; j < 64; j += 4) {
+            const uint4 k4 = *reinterpret_cast<const uint4*>(kd_buf + j);
+            uint32_t add = 0u;
+            if (same_span(qd, k4.x)) add |= 1u << ((j + 0) & 31);
+            if (same_span(qd, k4.y)) add |= 1u << ((j + 1) & 31);
+            if (same_span(qd, k4.z)) add |= 1u << ((j + 2) & 31);
+            if (same_span(qd, k4.w)) add |= 1u << ((j + 3) & 31);
+            mk[j >> 5] |= add;
+          }
+        }
       }
       prefetch_kd(e + 1);
       const int u = 2 * e + i, buf = u % C::NBUF;
@@ -324,11 +351,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
           for (int u = 0; u < 4; ++u) pv[u] = fast_exp2(fmaf(__uint_as_float(rs[j + u]), c, neg_lse));
           if (cls == KD_TILE_PARTIAL) {
-            const uint4 k4 = *reinterpret_cast<const uint4*>(kd_buf + cb * 32 + j);
-            const uint32_t kw[4] = {k4.x, k4.y, k4.z, k4.w};
 #pragma unroll
             for (int u = 0; u < 4; ++u)
-              if (!rule_allowed(qd, qi, kw[u], j0 + cb * 32 + j + u)) pv[u] = 0.f;
+              if ((mk[cb] & (1u << (j + u))) == 0u) pv[u] = 0.f;
           }
           float ds[4];
 #pragma unroll
@@ -410,7 +435,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       mbar_init(smem_u32(&bar_ring_empty[s]), 1);
     }
     for (int i = 0; i < C::NBUF; ++i) {
-      mbar_init(smem_u32(&bar_s_full[i]), 1);
+      mbar_init(smem_u32(&bar_s_full[i]), 2);     // one commit from each of the two M1 issuers
       mbar_init(smem_u32(&bar_p_full[i]), 128);
       mbar_init(smem_u32(&bar_m2_issued[i]), 1);
     }
@@ -468,8 +493,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_ring_full[e % C::STAGES]), (e / C::STAGES) & 1); ++spin) {}
         for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_fix_full), 0); ++spin) {}
       }
-    } else if (warp == 3 && lane == 0 && n > 0) {
-      // ------------------------------ M1 issuer: S^T_u = K Q_u^T, dP^T_u = V dO_u^T ------------------------------
+    } else if ((warp == 3 || warp == 2) && lane == 0 && n > 0) {
+      // ------------------------------ M1 issuers: warp 3: S^T_u = K Q_u^T; warp 2: dP^T_u = V dO_u^T ------------------------------
+      const bool dp_part = (warp == 2);
       const uint32_t idesc_m1 = make_idesc_f16(kBf16, 0, 0, KD_TILE, 64);   // N = 64 queries
       const uint32_t hi = desc_hi_sw128();
       const uint32_t loK = desc_lo_kmajor(sK), loV = desc_lo_kmajor(sV), loRingK = desc_lo_kmajor(sRing);
@@ -491,12 +517,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const uint32_t qb = loRingK + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);  // query rows 64i..
         const uint32_t dob = qb + (C::TILE_BYTES >> 4);
         const uint32_t dS = tbase + buf * 128, dP = dS + 64;
+        if (!dp_part) {
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss_split(dS, loK + koff_kmajor(kk), qb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < HD / 16; ++kk)
+            mma_ss_split(dS, loK + koff_kmajor(kk), qb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
+        } else {
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss_split(dP, loV + koff_kmajor(kk), dob + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < HD / 16; ++kk)
+            mma_ss_split(dP, loV + koff_kmajor(kk), dob + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
+        }
         mma_commit(smem_u32(&bar_s_full[buf]));
         tr.ev(15);
         if (++buf == C::NBUF) { buf = 0; ++round; }
@@ -555,8 +584,22 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     // into registers and handed to the warp through its shared-memory staging buffer
     float pre_lse[2] = {0.f, 0.f}, pre_delta[2] = {0.f, 0.f};
     uint32_t pre_desc[2] = {0u, 0u};
+    // query-side class masks of the next unit: sees-prefix[2], sees-context[2], sees-in_span[2], context[2], same-span armed[2]
+    uint32_t tb_pre[10];
+#pragma unroll
+    for (int j = 0; j < 10; ++j) tb_pre[j] = 0u;
     auto prefetch = [&](int e) {
       if (e < n) {
+        if ((list[e] >> 8) == KD_TILE_PARTIAL) {
+          const uint2* tbp = reinterpret_cast<const uint2*>(a.tilebits + ((size_t)b * a.NT + (list[e] & 0xFFu)) * 32);
+          const int which[5] = {TB_SEES_PRE, TB_SEES_CTX, TB_SEES_INS, TB_CTX, TB_SIDPOS};
+#pragma unroll
+          for (int j = 0; j < 5; ++j) {
+            const uint2 v = tbp[2 * which[j] + i];
+            tb_pre[2 * j] = v.x;
+            tb_pre[2 * j + 1] = v.y;
+          }
+        }
         const int q0 = (list[e] & 0xFF) * KD_TILE + i * 64;
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
@@ -584,6 +627,22 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         st_buf[128 + r * 32 + lane] = pre_desc[r];
       }
       __syncwarp();
+      uint32_t mk[2] = {0xFFFFFFFFu, 0xFFFFFFFFu};   // visibility of this key for the unit's 64 queries
+      if (cls == KD_TILE_PARTIAL) {
+        key_row_mask<2>(kdesc, kj, i0, tb_pre + 0, tb_pre + 2, tb_pre + 4, tb_pre + 6, mk);
+        if ((tb_pre[8] | tb_pre[9]) != 0u && __any_sync(0xffffffffu, (kdesc & TD_INS) != 0u)) {
+#pragma unroll
+          for (int j = 0; j < 64; j += 4) {
+            const uint4 q4 = *reinterpret_cast<const uint4*>(st_buf + 128 + j);
+            uint32_t add = 0u;
+            if (same_span(q4.x, kdesc)) add |= 1u << ((j + 0) & 31);
+            if (same_span(q4.y, kdesc)) add |= 1u << ((j + 1) & 31);
+            if (same_span(q4.z, kdesc)) add |= 1u << ((j + 2) & 31);
+            if (same_span(q4.w, kdesc)) add |= 1u << ((j + 3) & 31);
+            mk[j >> 5] |= add;
+          }
+        }
+      }
       prefetch(e + 1);
       const int u = 2 * e + i, buf = u % C::NBUF;
       const uint32_t tS = tbase + lane_base + buf * 128, tP = tS + 64;
@@ -602,23 +661,21 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tmem_ld32(tP + cb * 32, rp);
         tmem_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          const int jj = cb * 32 + j;
-          const float4 l4 = *reinterpret_cast<const float4*>(st_buf + jj);
-          const float4 d4 = *reinterpret_cast<const float4*>(st_buf + 64 + jj);
+        for (int g = 0; g < 8; ++g) {
+          const int j = g * 4;
+          const float4 l4 = *reinterpret_cast<const float4*>(st_buf + cb * 32 + j);        // -LSE of 4 queries
+          const float4 d4 = *reinterpret_cast<const float4*>(st_buf + 64 + cb * 32 + j);   // delta of 4 queries
           const float lw[4] = {l4.x, l4.y, l4.z, l4.w}, dw[4] = {d4.x, d4.y, d4.z, d4.w};
           float pv[4], ds[4];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) pv[u] = fast_exp2(fmaf(__uint_as_float(rs[j + u]), c, lw[u]));
+          for (int u2 = 0; u2 < 4; ++u2) pv[u2] = fast_exp2(fmaf(__uint_as_float(rs[j + u2]), c, lw[u2]));
           if (cls == KD_TILE_PARTIAL) {
-            const uint4 q4 = *reinterpret_cast<const uint4*>(st_buf + 128 + jj);
-            const uint32_t qw[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-              if (!rule_allowed(qw[u], i0 + jj + u, kdesc, kj)) pv[u] = 0.f;
+            for (int u2 = 0; u2 < 4; ++u2)
+              if ((mk[cb] & (1u << (j + u2))) == 0u) pv[u2] = 0.f;
           }
 #pragma unroll
-          for (int u = 0; u < 4; ++u) ds[u] = pv[u] * (__uint_as_float(rp[j + u]) - dw[u]);
+          for (int u2 = 0; u2 < 4; ++u2) ds[u2] = pv[u2] * (__uint_as_float(rp[j + u2]) - dw[u2]);
           pk_p[cb * 16 + j / 2] = pack2<kBf16>(pv[0], pv[1]);
           pk_p[cb * 16 + j / 2 + 1] = pack2<kBf16>(pv[2], pv[3]);
           pk_ds[cb * 16 + j / 2] = pack2<kBf16>(ds[0], ds[1]);
@@ -683,7 +740,7 @@ static int launch_bwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
   a.scale_log2 = p.sm_scale * 1.4426950408889634f;
   a.sm_scale = p.sm_scale;
   a.desc = pv.desc; a.fwd_cnt = pv.fwd_cnt; a.fwd_list = pv.fwd_list;
-  a.bwd_cnt = pv.bwd_cnt; a.bwd_list = pv.bwd_list; a.status = pv.status; a.order = pv.order;
+  a.bwd_cnt = pv.bwd_cnt; a.bwd_list = pv.bwd_list; a.status = pv.status; a.order = pv.order; a.tilebits = pv.tilebits;
   a.o = p.o.ptr; a.o_sb = p.o.stride_b; a.o_sh = p.o.stride_h; a.o_st = p.o.stride_t;
   a.d_o = p.d_o.ptr; a.do_sb = p.d_o.stride_b; a.do_sh = p.d_o.stride_h; a.do_st = p.d_o.stride_t;
   a.lse = p.lse; a.delta = p.delta;

@@ -31,6 +31,7 @@ struct FwdArgs {
   int B, H, T, NT, NP, Tpad;
   float scale_log2;  // sm_scale * log2(e)
   const uint32_t* desc;
+  const uint32_t* tilebits;   // [B][NT][8][4] class masks of every 128-token tile
   const int32_t* fwd_cnt;
   const uint16_t* fwd_list;
   const uint8_t* order;   // [B][3][NT]; row 0 = pairs sorted by decreasing list length
@@ -357,11 +358,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int n_own = n_own_s[i];
     const uint32_t* wcmd = sWcmd + i * 256;
     uint32_t kd_pre[4] = {0u, 0u, 0u, 0u};
+    uint32_t tb_pre[12];   // key-side class masks of the tile: is_prefix[4], context[4], in_span[4]
+#pragma unroll
+    for (int j = 0; j < 12; ++j) tb_pre[j] = 0u;
     auto prefetch_kd = [&](uint32_t c) {
       if (wcmd_class(c) == KD_TILE_PARTIAL) {
         const uint32_t* src = a.desc + (size_t)b * a.Tpad + (size_t)wcmd_kt(c) * KD_TILE;
 #pragma unroll
         for (int j = 0; j < 4; ++j) kd_pre[j] = src[j * 32 + lane];
+        const uint4* tb = reinterpret_cast<const uint4*>(a.tilebits + ((size_t)b * a.NT + wcmd_kt(c)) * 32);
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+          const uint4 v = tb[j];   // masks TB_PRE, TB_CTX, TB_INS
+          tb_pre[4 * j + 0] = v.x; tb_pre[4 * j + 1] = v.y; tb_pre[4 * j + 2] = v.z; tb_pre[4 * j + 3] = v.w;
+        }
       }
     };
     uint32_t cmd_next = n_own > 0 ? wcmd[0] : 0u;
@@ -374,10 +384,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int buf = wcmd_buf(cmd);
       const uint32_t tS = tbase + lane_base + buf * 128;
       tr.ev(20);
+      uint32_t tb[12];
       if (cls == KD_TILE_PARTIAL) {
         __syncwarp();
 #pragma unroll
         for (int j = 0; j < 4; ++j) kd_buf[j * 32 + lane] = kd_pre[j];
+#pragma unroll
+        for (int j = 0; j < 12; ++j) tb[j] = tb_pre[j];
         __syncwarp();
       }
       if (k + 1 < n_own) {
@@ -402,15 +415,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tmem_wait_ld();
       tr.ev(23);
       if (cls == KD_TILE_PARTIAL) {
+        // The row's 128-bit visibility mask comes from the tile's class masks with a few word-wide
+        // operations; only the "same span" term needs the individual key descriptors.
         const int j0 = kt * KD_TILE;
+        uint32_t mk[4];
+        query_row_mask<4>(qd, qi, j0, tb + 0, tb + 4, tb + 8, mk);
+        const bool tile_has_span_keys = (tb[8] | tb[9] | tb[10] | tb[11]) != 0u;
+        if (tile_has_span_keys && __any_sync(0xffffffffu, (qd & TD_SIDPOS) != 0u)) {
 #pragma unroll
-        for (int j = 0; j < KD_TILE; j += 4) {
-          const uint4 k4 = *reinterpret_cast<const uint4*>(kd_buf + j);
-          if (!rule_allowed(qd, qi, k4.x, j0 + j + 0)) s[j + 0] = -INFINITY;
-          if (!rule_allowed(qd, qi, k4.y, j0 + j + 1)) s[j + 1] = -INFINITY;
-          if (!rule_allowed(qd, qi, k4.z, j0 + j + 2)) s[j + 2] = -INFINITY;
-          if (!rule_allowed(qd, qi, k4.w, j0 + j + 3)) s[j + 3] = -INFINITY;
+          for (int j = 0; j < KD_TILE; j += 4) {
+            const uint4 k4 = *reinterpret_cast<const uint4*>(kd_buf + j);
+            uint32_t add = 0u;
+            if (same_span(qd, k4.x)) add |= 1u << ((j + 0) & 31);
+            if (same_span(qd, k4.y)) add |= 1u << ((j + 1) & 31);
+            if (same_span(qd, k4.z)) add |= 1u << ((j + 2) & 31);
+            if (same_span(qd, k4.w)) add |= 1u << ((j + 3) & 31);
+            mk[j >> 5] |= add;
+          }
         }
+#pragma unroll
+        for (int j = 0; j < KD_TILE; ++j)
+          if ((mk[j >> 5] & (1u << (j & 31))) == 0u) s[j] = -INFINITY;
       }
       // four independent chains for the row maximum and for the row sum: a single chain of 127
       // dependent operations would be latency-bound
@@ -531,7 +556,7 @@ static int launch_fwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
   a.B = p.B; a.H = p.H; a.T = p.T; a.NT = L.NT; a.NP = L.NP; a.Tpad = L.NT * KD_TILE;
   a.scale_log2 = p.sm_scale * 1.4426950408889634f;
   a.desc = pv.desc; a.fwd_cnt = pv.fwd_cnt; a.fwd_list = pv.fwd_list; a.status = pv.status;
-  a.order = pv.order; a.trace = trace_buffer();
+  a.order = pv.order; a.trace = trace_buffer(); a.tilebits = pv.tilebits;
   a.o = p.o.ptr; a.o_sb = p.o.stride_b; a.o_sh = p.o.stride_h; a.o_st = p.o.stride_t;
   a.lse = p.lse;
   auto kern = attn_fwd_kernel<HD, kBf16>;

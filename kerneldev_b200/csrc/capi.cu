@@ -141,6 +141,7 @@ int kd_plan_layout_get(int32_t B, int32_t T, kd_plan_layout* out) {
   out->off_fwd_list = off; off = up(off + (size_t)B * NP * NT * 2);
   out->off_bwd_cnt = off;  off = up(off + (size_t)B * NT * 4);
   out->off_bwd_list = off; off = up(off + (size_t)B * NT * NT * 2);
+  out->off_tilebits = off; off = up(off + (size_t)B * NT * 8 * 4 * 4);
   out->off_order = off;    off = up(off + (size_t)B * 3 * NT);
   out->off_stats = off;    off = up(off + (size_t)B * 2 * 4);
   out->off_status = off;   off = up(off + 4);

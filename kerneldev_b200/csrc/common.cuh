@@ -21,6 +21,7 @@ struct PlanView {
   uint16_t* fwd_list;
   int32_t* bwd_cnt;
   uint16_t* bwd_list;
+  uint32_t* tilebits;
   uint8_t* order;
   uint32_t* stats;
   uint32_t* status;
@@ -39,6 +40,7 @@ inline PlanView make_plan_view(void* plan, const kd_plan_layout& L) {
   v.fwd_list = reinterpret_cast<uint16_t*>(base + L.off_fwd_list);
   v.bwd_cnt = reinterpret_cast<int32_t*>(base + L.off_bwd_cnt);
   v.bwd_list = reinterpret_cast<uint16_t*>(base + L.off_bwd_list);
+  v.tilebits = reinterpret_cast<uint32_t*>(base + L.off_tilebits);
   v.order = reinterpret_cast<uint8_t*>(base + L.off_order);
   v.stats = reinterpret_cast<uint32_t*>(base + L.off_stats);
   v.status = reinterpret_cast<uint32_t*>(base + L.off_status);

@@ -61,4 +61,51 @@ __host__ __device__ __forceinline__ bool rule_allowed(uint32_t qd, int i, uint32
   return a || c || s;
 }
 
+// ---------------------------------------------------------------------------------------
+// Bit-parallel form of the rule for one row against a run of W*32 tokens of the other side.
+// The plan stores, per 128-token tile, eight 128-bit masks (index = TB_*); a row combines a few of
+// them with word-wide logic instead of evaluating the rule per element.
+// ---------------------------------------------------------------------------------------
+constexpr int TB_PRE = 0, TB_CTX = 1, TB_INS = 2, TB_SEES_PRE = 3, TB_SEES_CTX = 4, TB_SEES_INS = 5, TB_SIDPOS = 6;
+
+// mask with the lowest n bits set, n clamped to [0, 32]
+__host__ __device__ __forceinline__ uint32_t low_bits(int n) {
+  return n <= 0 ? 0u : (n >= 32 ? 0xFFFFFFFFu : ((1u << n) - 1u));
+}
+
+// Query row with descriptor qd at index i against W words of key-side masks (PRE, CTX, INS) of the
+// keys j0 .. j0 + 32 W - 1: every term of the rule except "same span".
+template <int W>
+__host__ __device__ __forceinline__ void query_row_mask(uint32_t qd, int i, int j0, const uint32_t* k_pre,
+                                                        const uint32_t* k_ctx, const uint32_t* k_ins, uint32_t* m) {
+  const uint32_t sees = qd >> TD_SEES_SHIFT;
+  const uint32_t s_pre = (sees & TD_PRE) ? 0xFFFFFFFFu : 0u, s_ctx = (sees & TD_CTX) ? 0xFFFFFFFFu : 0u,
+                 s_ins = (sees & TD_INS) ? 0xFFFFFFFFu : 0u, q_ctx = (qd & TD_CTX) ? 0xFFFFFFFFu : 0u;
+#pragma unroll
+  for (int w = 0; w < W; ++w) {
+    const uint32_t causal = low_bits(i - j0 - 32 * w + 1);   // keys j <= i
+    m[w] = (k_pre[w] & s_pre) | (k_ctx[w] & (s_ctx | (q_ctx & causal))) | (k_ins[w] & s_ins);
+  }
+}
+
+// Key row with descriptor kd at index j against W words of query-side masks of the queries
+// i0 .. i0 + 32 W - 1: every term of the rule except "same span".
+template <int W>
+__host__ __device__ __forceinline__ void key_row_mask(uint32_t kdesc, int j, int i0, const uint32_t* q_sees_pre,
+                                                      const uint32_t* q_sees_ctx, const uint32_t* q_sees_ins,
+                                                      const uint32_t* q_ctx, uint32_t* m) {
+  const uint32_t is_pre = (kdesc & TD_PRE) ? 0xFFFFFFFFu : 0u, is_ctx = (kdesc & TD_CTX) ? 0xFFFFFFFFu : 0u,
+                 is_ins = (kdesc & TD_INS) ? 0xFFFFFFFFu : 0u;
+#pragma unroll
+  for (int w = 0; w < W; ++w) {
+    const uint32_t causal = ~low_bits(j - i0 - 32 * w);      // queries i >= j
+    m[w] = (q_sees_pre[w] & is_pre) | (is_ctx & (q_sees_ctx[w] | (q_ctx[w] & causal))) | (q_sees_ins[w] & is_ins);
+  }
+}
+
+// "same span" term for one pair of descriptors
+__host__ __device__ __forceinline__ bool same_span(uint32_t qd, uint32_t kdesc) {
+  return ((qd & TD_SIDPOS) != 0u) && ((kdesc & TD_INS) != 0u) && (((qd ^ kdesc) >> TD_SID_SHIFT) == 0u);
+}
+
 }  // namespace kd

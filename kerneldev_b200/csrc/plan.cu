@@ -30,6 +30,18 @@ __global__ void __launch_bounds__(KD_TILE) pack_kernel(kd_meta m, PlanView pv) {
     }
   }
   pv.desc[(size_t)b * pv.Tpad + t] = d;
+  {
+    // 128-bit class masks of the tile: bit t of mask k = descriptor bit k of token t
+    // (bits 0..2 = classes as a key, bits 5..7 = classes seen as a query, bit 4 = same-span armed)
+    const uint32_t src_bit[8] = {TD_PRE, TD_CTX, TD_INS, TD_PRE << TD_SEES_SHIFT, TD_CTX << TD_SEES_SHIFT,
+                                 TD_INS << TD_SEES_SHIFT, TD_SIDPOS, 0u};
+    uint32_t* tb = pv.tilebits + ((size_t)b * pv.NT + tile) * 32;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const uint32_t bal = __ballot_sync(0xffffffffu, (d & src_bit[k]) != 0u);
+      if ((tid & 31) == 0) tb[k * 4 + (tid >> 5)] = bal;
+    }
+  }
 
   uint32_t f_or = d & TD_FLAGS, f_and = d & TD_FLAGS;
   int32_t smin = INT32_MAX, smax = INT32_MIN;
