@@ -316,15 +316,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         __syncwarp();
         query_row_mask<2>(qd, qi, j0, tb_pre + 0, tb_pre + 2, tb_pre + 4, mk);
         if ((tb_pre[4] | tb_pre[5]) != 0u && __any_sync(0xffffffffu, (qd & TD_SIDPOS) != 0u)) {
+          const uint32_t key = span_key_of_query(qd);
 #pragma unroll
           for (int j = 0; j < 64; j += 4) {
             const uint4 k4 = *reinterpret_cast<const uint4*>(kd_buf + j);
-            uint32_t add = 0u;
-            if (same_span(qd, k4.x)) add |= 1u << ((j + 0) & 31);
-            if (same_span(qd, k4.y)) add |= 1u << ((j + 1) & 31);
-            if (same_span(qd, k4.z)) add |= 1u << ((j + 2) & 31);
-            if (same_span(qd, k4.w)) add |= 1u << ((j + 3) & 31);
-            mk[j >> 5] |= add;
+            mk[j >> 5] |= (span_match_key(key, k4.x) << ((j + 0) & 31)) | (span_match_key(key, k4.y) << ((j + 1) & 31)) |
+                          (span_match_key(key, k4.z) << ((j + 2) & 31)) | (span_match_key(key, k4.w) << ((j + 3) & 31));
           }
         }
       }
@@ -631,15 +628,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if (cls == KD_TILE_PARTIAL) {
         key_row_mask<2>(kdesc, kj, i0, tb_pre + 0, tb_pre + 2, tb_pre + 4, tb_pre + 6, mk);
         if ((tb_pre[8] | tb_pre[9]) != 0u && __any_sync(0xffffffffu, (kdesc & TD_INS) != 0u)) {
+          const uint32_t key = span_key_of_key(kdesc);
 #pragma unroll
           for (int j = 0; j < 64; j += 4) {
             const uint4 q4 = *reinterpret_cast<const uint4*>(st_buf + 128 + j);
-            uint32_t add = 0u;
-            if (same_span(q4.x, kdesc)) add |= 1u << ((j + 0) & 31);
-            if (same_span(q4.y, kdesc)) add |= 1u << ((j + 1) & 31);
-            if (same_span(q4.z, kdesc)) add |= 1u << ((j + 2) & 31);
-            if (same_span(q4.w, kdesc)) add |= 1u << ((j + 3) & 31);
-            mk[j >> 5] |= add;
+            mk[j >> 5] |= (span_match_query(key, q4.x) << ((j + 0) & 31)) | (span_match_query(key, q4.y) << ((j + 1) & 31)) |
+                          (span_match_query(key, q4.z) << ((j + 2) & 31)) | (span_match_query(key, q4.w) << ((j + 3) & 31));
           }
         }
       }

@@ -420,22 +420,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int j0 = kt * KD_TILE;
         uint32_t mk[4];
         query_row_mask<4>(qd, qi, j0, tb + 0, tb + 4, tb + 8, mk);
+        tr.ev(26);
         const bool tile_has_span_keys = (tb[8] | tb[9] | tb[10] | tb[11]) != 0u;
         if (tile_has_span_keys && __any_sync(0xffffffffu, (qd & TD_SIDPOS) != 0u)) {
+          const uint32_t key = span_key_of_query(qd);
 #pragma unroll
           for (int j = 0; j < KD_TILE; j += 4) {
             const uint4 k4 = *reinterpret_cast<const uint4*>(kd_buf + j);
-            uint32_t add = 0u;
-            if (same_span(qd, k4.x)) add |= 1u << ((j + 0) & 31);
-            if (same_span(qd, k4.y)) add |= 1u << ((j + 1) & 31);
-            if (same_span(qd, k4.z)) add |= 1u << ((j + 2) & 31);
-            if (same_span(qd, k4.w)) add |= 1u << ((j + 3) & 31);
-            mk[j >> 5] |= add;
+            mk[j >> 5] |= (span_match_key(key, k4.x) << ((j + 0) & 31)) | (span_match_key(key, k4.y) << ((j + 1) & 31)) |
+                          (span_match_key(key, k4.z) << ((j + 2) & 31)) | (span_match_key(key, k4.w) << ((j + 3) & 31));
           }
         }
+        tr.ev(27);
 #pragma unroll
         for (int j = 0; j < KD_TILE; ++j)
           if ((mk[j >> 5] & (1u << (j & 31))) == 0u) s[j] = -INFINITY;
+        tr.ev(28);
       }
       // four independent chains for the row maximum and for the row sum: a single chain of 127
       // dependent operations would be latency-bound
@@ -473,6 +473,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         pk[j / 2 + 1] = pack2<kBf16>(p2, p3);
       }
       const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      tr.ev(32);
       l = l * alpha + sum;
       m = m_new;
 #pragma unroll
@@ -489,6 +490,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
       }
+      tr.ev(33);
       if (__any_sync(0xffffffffu, need_rescale)) {
         tc_fence_after_sync();
         const float f = need_rescale ? alpha : 1.f;

@@ -108,4 +108,24 @@ __host__ __device__ __forceinline__ bool same_span(uint32_t qd, uint32_t kdesc) 
   return ((qd & TD_SIDPOS) != 0u) && ((kdesc & TD_INS) != 0u) && (((qd ^ kdesc) >> TD_SID_SHIFT) == 0u);
 }
 
+// Branch-free form for inner loops: the row side is folded once into a match key (span id bits
+// plus the in_span flag, or a value no descriptor can produce when the rule is not armed); each
+// token of the other side then costs one AND and one compare.
+constexpr uint32_t TD_SPAN_KEY_BITS = 0xFFFFFF00u | TD_INS;
+// key of a QUERY row matched against KEY descriptors: key needs in_span and the same id
+__host__ __device__ __forceinline__ uint32_t span_key_of_query(uint32_t qd) {
+  return (qd & TD_SIDPOS) ? ((qd & 0xFFFFFF00u) | TD_INS) : 0x00000001u;   // bit 0 is outside TD_SPAN_KEY_BITS: never matches
+}
+__host__ __device__ __forceinline__ uint32_t span_match_key(uint32_t key, uint32_t kdesc) {
+  return ((kdesc & TD_SPAN_KEY_BITS) == key) ? 1u : 0u;
+}
+// key of a KEY row matched against QUERY descriptors: query needs the rule armed and the same id
+constexpr uint32_t TD_SPAN_QUERY_BITS = 0xFFFFFF00u | TD_SIDPOS;
+__host__ __device__ __forceinline__ uint32_t span_key_of_key(uint32_t kdesc) {
+  return (kdesc & TD_INS) ? ((kdesc & 0xFFFFFF00u) | TD_SIDPOS) : 0x00000001u;
+}
+__host__ __device__ __forceinline__ uint32_t span_match_query(uint32_t key, uint32_t qd) {
+  return ((qd & TD_SPAN_QUERY_BITS) == key) ? 1u : 0u;
+}
+
 }  // namespace kd

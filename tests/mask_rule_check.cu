@@ -44,6 +44,8 @@ int main() {
       query_row_mask<4>(q[r], i_base + r, j_base, kp, kc, ki, m);
       for (int j = 0; j < 128; ++j) {
         bool got = ((m[j >> 5] >> (j & 31)) & 1u) || same_span(q[r], k[j]);
+        bad += (span_match_key(span_key_of_query(q[r]), k[j]) != 0u) != same_span(q[r], k[j]);
+        bad += (span_match_query(span_key_of_key(k[j]), q[r]) != 0u) != same_span(q[r], k[j]);
         bool ref = rule_allowed(q[r], i_base + r, k[j], j_base + j);
         bad += got != ref; ++checked;
       }
