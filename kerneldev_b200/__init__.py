@@ -2,10 +2,23 @@
 
 Public surface (mirrors the reference's ``original_kernel`` module for the attention path):
   flash_attention, generate_hadamard_signs, hadamard_transform  -- the operator
-  AttentionPlan, get_plan                                       -- tile classification of a batch
-"""
-from .original_kernel import flash_attention, generate_hadamard_signs, hadamard_transform
-from .plan import AttentionPlan, clear_plan_cache, get_plan
+  AttentionPlan, get_plan, clear_plan_cache                     -- tile classification of a batch
 
-__all__ = ["flash_attention", "generate_hadamard_signs", "hadamard_transform", "AttentionPlan",
-           "get_plan", "clear_plan_cache"]
+Names are resolved on first use, so that ``python -m kerneldev_b200.build`` can (re)build the
+shared library before anything tries to load it. The first use of the operator loads
+libkd_attention.so and fails loudly if it is missing or stale; there is no other compute path.
+"""
+_EXPORTS = {
+    "flash_attention": "original_kernel", "generate_hadamard_signs": "original_kernel",
+    "hadamard_transform": "original_kernel", "AttentionPlan": "plan", "get_plan": "plan",
+    "clear_plan_cache": "plan",
+}
+
+__all__ = sorted(_EXPORTS)
+
+
+def __getattr__(name):
+    if name in _EXPORTS:
+        import importlib
+        return getattr(importlib.import_module(f"{__name__}.{_EXPORTS[name]}"), name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
