@@ -129,6 +129,21 @@ int kd_attn_fwd(const kd_attn_params* p, void* stream);
  * with its dQ and dK/dV workers (:713-838, :1173-1525). */
 int kd_attn_bwd(const kd_attn_params* p, void* stream);
 
+/* kd_attn_bwd without any caller-provided scratch. This entry point has no counterpart in the
+ * reference. It is for hosts that are not allowed to allocate device memory where they call the
+ * backward -- an engine that reserves all of HBM for its own arena at start-up and bans cudaMalloc
+ * in plugin code, or a caller already inside a region where the allocator must not run. The
+ * `delta` field of the params is ignored: the kernels use a fixed 4 MiB array inside the library
+ * (every GPU that loads the library holds it until the process exits), so B*H*T must not exceed
+ * 1,048,576 rows; larger problems are rejected with KD_ERR_LIMIT. The call allocates nothing.
+ *  - The first call on each device looks up the array's device address (one cudaGetSymbolAddress,
+ *    with that device current); make that first call before starting any stream capture.
+ *  - All calls share the one array. Nothing in it has to start at zero (the dQ kernel rewrites every
+ *    row before the dK/dV kernel reads it), but two calls that overlap on the GPU -- different
+ *    streams, or different host threads -- race on it. Serialise them.
+ *  - Inputs, outputs and results are exactly those of kd_attn_bwd. */
+int kd_attn_bwd_static(const kd_attn_params* p, void* stream);
+
 /* Bytes of the scratch buffer `delta` that kd_attn_bwd needs. */
 int kd_workspace_bytes(int32_t B, int32_t H, int32_t T, int32_t D, size_t* bytes);
 

@@ -17,6 +17,8 @@
 // The tensor pipe executes in issue order, so M1(u + NBUF) may overwrite the buffer M2(u) read.
 // M1 and M2 are issued by two different single threads (warps 3 and 1): each shares its scheduler
 // with two compute warps, and splitting the work keeps either one off the critical path.
+#include <mutex>
+
 #include "attn_common.cuh"
 
 namespace kd {
@@ -753,6 +755,47 @@ static int launch_bwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
   if (phases & 2) kk<<<grid, 384, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "attn_bwd kernels launch: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// Library-owned scratch for kd_attn_bwd_static.
+//
+// Some hosts may not allocate device memory on the path that calls the backward: an inference or
+// training engine that hands every byte of HBM to its own arena at start-up and forbids plugin
+// code to call cudaMalloc afterwards, or a caller that is already inside a region where the
+// allocator must not run. For them the `delta` scratch of the backward (one float per
+// (batch, head, token) row) lives in this fixed array instead of in a caller-supplied buffer.
+// Every GPU that loads the library holds the array (4 MiB) until the process exits.
+//
+// In host code the name of a __device__ array is only a handle; the device address a kernel can
+// use is obtained with cudaGetSymbolAddress, once per device, with that device current.
+// ---------------------------------------------------------------------------------------
+constexpr size_t KD_STATIC_DELTA_ROWS = size_t(1) << 20;   // B*H*T may not exceed this
+static __device__ __align__(256) float g_static_delta[KD_STATIC_DELTA_ROWS];
+
+constexpr int KD_MAX_DEVICES = 64;
+static float* g_static_delta_addr[KD_MAX_DEVICES] = {};
+static std::mutex g_static_delta_mutex;
+
+// Device address of the static scratch on the current device (looked up on first use per device).
+int static_delta_address(size_t rows_needed, float** out) {
+  if (rows_needed > KD_STATIC_DELTA_ROWS)
+    return set_error(KD_ERR_LIMIT, "kd_attn_bwd_static: B*H*T = %zu rows exceed the built-in scratch of %zu rows; "
+                     "use kd_attn_bwd with a caller-provided delta buffer", rows_needed, KD_STATIC_DELTA_ROWS);
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= KD_MAX_DEVICES) return set_error(KD_ERR_LIMIT, "device ordinal %d beyond %d", dev, KD_MAX_DEVICES);
+  std::lock_guard<std::mutex> lock(g_static_delta_mutex);
+  if (g_static_delta_addr[dev] == nullptr) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_delta);
+    if (e != cudaSuccess || ptr == nullptr)
+      return set_error(KD_ERR_DEVICE, "cudaGetSymbolAddress(static delta scratch): %s", cudaGetErrorString(e));
+    g_static_delta_addr[dev] = ptr;
+  }
+  *out = g_static_delta_addr[dev];
   return 0;
 }
 

@@ -181,6 +181,19 @@ int kd_attn_bwd(const kd_attn_params* p, void* stream) {
   return launch_attn_bwd(*p, static_cast<cudaStream_t>(stream));
 }
 
+int kd_attn_bwd_static(const kd_attn_params* p, void* stream) {
+  if (!p) return set_error(KD_ERR_ARG, "params is null");
+  if (p->B < 1 || p->H < 1 || p->T < 1) return set_error(KD_ERR_ARG, "bad shape B=%d H=%d T=%d", p->B, p->H, p->T);
+  int rc = check_device();
+  if (rc) return rc;
+  kd_attn_params q = *p;   // same call as kd_attn_bwd, with the scratch pointed at the library's own array
+  float* scratch = nullptr;
+  if ((rc = static_delta_address((size_t)p->B * p->H * p->T, &scratch)) != 0) return rc;
+  q.delta = scratch;
+  if ((rc = check_attn(&q, true)) != 0) return rc;
+  return launch_attn_bwd(q, static_cast<cudaStream_t>(stream));
+}
+
 int kd_workspace_bytes(int32_t B, int32_t H, int32_t T, int32_t D, size_t* bytes) {
   if (!bytes || B < 1 || H < 1 || T < 1 || D < 1) return set_error(KD_ERR_ARG, "bad workspace query");
   (void)D;

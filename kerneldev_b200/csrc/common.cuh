@@ -62,6 +62,7 @@ int launch_classify(const kd_meta& m, void* plan, cudaStream_t stream);
 int launch_mask_dense(const void* plan, int B, int T, uint8_t* out, cudaStream_t stream);
 int launch_attn_fwd(const kd_attn_params& p, cudaStream_t stream);
 int launch_attn_bwd(const kd_attn_params& p, cudaStream_t stream);
+int static_delta_address(size_t rows_needed, float** out);
 int launch_hadamard(const kd_tensor& x, const kd_tensor& y, int B, int H, int T, int D, int dtype,
                     const float* signs, int inverse, cudaStream_t stream);
 
