@@ -51,6 +51,11 @@ CONFIGS = {
             name="config3: hierarchical-mask + Hadamard fwd+bwd fp16 B4 H32 L8192 D128"),
 }
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch and per batch row of config 2,
+# from the ncu capture summarised in profiles/attention_kernels_config2_batch4.md (batch 4: 102.2,
+# 187.0 and 160.5 MB); traffic grows in proportion to the number of (batch, head) pairs.
+NCU_TRAFFIC_PER_BATCH_ROW = {"attn_fwd_kernel": 102.2e6 / 4, "attn_bwd_dq_kernel": 187.0e6 / 4,
+                             "attn_bwd_dkdv_kernel": 160.5e6 / 4}
 
 
 def load_peaks():
@@ -267,7 +272,6 @@ def run_ours(args, cfg):
     ev1.record()
     barrier()
     ms_total = ev0.elapsed_time(ev1)
-    clocks = sampler.stop() if rank == 0 else None
     plan.check_status()
     t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
     feff_t = torch.tensor([f_eff], device=dev, dtype=torch.float64)
@@ -308,7 +312,10 @@ def run_ours(args, cfg):
     achieved = dom_alg / (dom_ms * 1e-3) / 1e12
     roofline = {
         "bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
-        "frac": achieved / peak_tf, "traffic": None, "peak_kind": peak_kind + " burst (kernel timed alone)",
+        "frac": achieved / peak_tf,
+        "traffic": (NCU_TRAFFIC_PER_BATCH_ROW[dom] * B) if (args.config == 2) else None,
+        "traffic_note": "bytes per launch: ncu capture at batch 4 scaled to this batch",
+        "peak_kind": peak_kind + " burst (kernel timed alone)",
         "executed_tflops": dom_exec / (dom_ms * 1e-3) / 1e12,
         "kernels_ms": {n: kernels[n][0] for n in kernels},
         "kernels_algorithmic_tflops": {n: kernels[n][1] / (kernels[n][0] * 1e-3) / 1e12 for n in kernels},
@@ -348,6 +355,8 @@ def run_ours(args, cfg):
         ms_e2e = float(t.item()) / e2e_steps
         e2e_value = float(feff_t.item()) / (ms_e2e * 1e-3) / 1e12
 
+    # the sampler covers the timed region and the per-kernel / end-to-end legs that follow it (all GPU load)
+    clocks = sampler.stop() if rank == 0 else None
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu_baseline and not args.kernels_only:

@@ -2,6 +2,8 @@
 // descriptors (so the single MMA-issuing thread spends two integer adds per MMA, not a 64-bit
 // descriptor build), work-list staging, 16-bit row stores.
 #pragma once
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "mask_rule.cuh"
 #include "sm100_prims.cuh"
@@ -71,6 +73,27 @@ __device__ __forceinline__ void store_row32(uint16_t* dst, const uint32_t (&r)[3
     v.w = pack2<kBf16>(__uint_as_float(r[j + 6]) * f, __uint_as_float(r[j + 7]) * f);
     *reinterpret_cast<uint4*>(dst + j) = v;
   }
+}
+
+// Heads a CTA handles one after the other (they share the plan's work list, so the list staging,
+// the TMEM allocation and the pipeline fill are paid once): as many as keeps about 8 CTAs per SM.
+inline int heads_per_cta(int B, int H, int items_per_batch) {
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
+      sm_count = 148;
+  }
+  const long long ctas = (long long)B * H * items_per_batch;
+  long long g = ctas / ((long long)sm_count * 8);
+  if (g < 1) g = 1;
+  if (g > 8) g = 8;
+  if (g > H) g = H;
+  if (const char* env = getenv("KD_HEADS_PER_CTA")) {   // tuning aid
+    const int v = atoi(env);
+    if (v >= 1 && v <= H) g = v;
+  }
+  return static_cast<int>(g);
 }
 
 // bounded wait used while unwinding after an abort: lets a TMA copy that is already in flight land

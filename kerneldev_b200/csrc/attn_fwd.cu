@@ -29,6 +29,7 @@ namespace kd {
 
 struct FwdArgs {
   int B, H, T, NT, NP, Tpad;
+  int G;             // heads handled one after the other by a CTA (they share the pair's work list)
   float scale_log2;  // sm_scale * log2(e)
   const uint32_t* desc;
   const uint32_t* tilebits;   // [B][NT][8][4] class masks of every 128-token tile
@@ -49,8 +50,9 @@ struct FwdCfg {
   static constexpr int NBUF = (HD == 64) ? 3 : 2;        // score buffers in TMEM
   static constexpr int KST = NBUF;                       // K ring stages
   static constexpr int VST = (HD == 64) ? 3 : 2;         // V ring stages
+  static constexpr int NQ = (HD == 64) ? 2 : 1;          // Q pair buffers: the next head's Q loads while this head computes
   static constexpr int SMEM_Q = 0;
-  static constexpr int SMEM_K = SMEM_Q + 2 * TILE_BYTES;
+  static constexpr int SMEM_K = SMEM_Q + NQ * 2 * TILE_BYTES;
   static constexpr int SMEM_V = SMEM_K + KST * TILE_BYTES;
   static constexpr int SMEM_KDESC = SMEM_V + VST * TILE_BYTES;     // 8 warps x 128 u32
   static constexpr int SMEM_LIST = SMEM_KDESC + 8 * KD_TILE * 4;   // the pair's work list (<= 128 entries)
@@ -70,18 +72,17 @@ __device__ __forceinline__ int unit_entry(uint32_t u) { return u & 0x7F; }
 __device__ __forceinline__ int unit_tile(uint32_t u) { return (u >> 7) & 1; }
 __device__ __forceinline__ uint32_t unit_class(uint32_t u) { return (u >> 8) & 3; }
 
-// command flags (word z of a command): ring stage, phase parity, wait / release markers
-constexpr uint32_t CMD_STAGE = 3u, CMD_PARITY = 4u, CMD_WAIT = 8u, CMD_RELEASE = 16u, CMD_ACC = 32u, CMD_TILE1 = 64u;
-// softmax command of a warpgroup's k-th unit: key tile | class << 8 | buffer << 10 | s_full parity << 12
+// command flags (word z of a command)
+constexpr uint32_t CMD_WAIT = 8u, CMD_RELEASE = 16u, CMD_ACC = 32u, CMD_TILE1 = 64u;
+// softmax command of a warpgroup's k-th unit: key tile | class << 8 | (unit index mod NBUF) << 10
 __device__ __forceinline__ int wcmd_kt(uint32_t c) { return c & 0xFF; }
 __device__ __forceinline__ uint32_t wcmd_class(uint32_t c) { return (c >> 8) & 3; }
 __device__ __forceinline__ int wcmd_buf(uint32_t c) { return (c >> 10) & 3; }
-__device__ __forceinline__ uint32_t wcmd_parity(uint32_t c) { return (c >> 12) & 1; }
 
 // wait-site codes reported in the status word
 enum : uint32_t {
   W_F_QFULL = 0x101, W_F_KEMPTY = 0x102, W_F_VEMPTY = 0x103, W_F_KFULL = 0x104, W_F_VFULL = 0x105,
-  W_F_PFULL = 0x106, W_F_SFULL = 0x107, W_F_PVDONE = 0x108, W_F_PVISSUED = 0x109,
+  W_F_PFULL = 0x106, W_F_SFULL = 0x107, W_F_PVDONE = 0x108, W_F_PVISSUED = 0x109, W_F_QEMPTY = 0x10A, W_F_OFREE = 0x10B,
 };
 
 template <int HD, bool kBf16>
@@ -100,8 +101,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint4* sCmd = reinterpret_cast<uint4*>(smem + C::SMEM_CMD);   // [u][0] = S command, [u][1] = P V command
   uint32_t* sWcmd = reinterpret_cast<uint32_t*>(smem + C::SMEM_WCMD);   // [tile][k]
 
-  __shared__ __align__(8) uint64_t bar_q_full, bar_k_full[C::KST], bar_k_empty[C::KST], bar_v_full[C::VST],
-      bar_v_empty[C::VST], bar_s_full[2 * C::NBUF], bar_p_full[C::NBUF], bar_pv_issued[C::NBUF], bar_pv_done[2];
+  __shared__ __align__(8) uint64_t bar_q_full[C::NQ], bar_q_empty[C::NQ], bar_k_full[C::KST], bar_k_empty[C::KST],
+      bar_v_full[C::VST], bar_v_empty[C::VST], bar_s_full[2 * C::NBUF], bar_p_full[C::NBUF], bar_pv_issued[C::NBUF],
+      bar_pv_done[2], bar_o_free[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int n_units_s, n_own_s[2];
   __shared__ AbortFlag abortf;
@@ -109,13 +111,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // blockIdx.z walks the pairs from the longest list to the shortest, so the CTAs that take
   // longest are dispatched first
-  const int h = blockIdx.x, b = blockIdx.y;
+  const int h0 = blockIdx.x * a.G, b = blockIdx.y;
+  const int nh = min(a.G, a.H - h0);   // this CTA handles heads h0 .. h0 + nh - 1, one after the other
   const int pair = a.order[((size_t)b * 3 + 0) * a.NT + blockIdx.z];
   const int n = a.fwd_cnt[b * a.NP + pair];
 
   if (tid == 0) {
     abortf.v = 0;
-    mbar_init(smem_u32(&bar_q_full), 1);
+    for (int s = 0; s < C::NQ; ++s) {
+      mbar_init(smem_u32(&bar_q_full[s]), 1);
+      mbar_init(smem_u32(&bar_q_empty[s]), 1);
+    }
     for (int s = 0; s < C::KST; ++s) {
       mbar_init(smem_u32(&bar_k_full[s]), 1);
       mbar_init(smem_u32(&bar_k_empty[s]), 1);
@@ -134,6 +140,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     mbar_init(smem_u32(&bar_pv_done[0]), 1);
     mbar_init(smem_u32(&bar_pv_done[1]), 1);
+    mbar_init(smem_u32(&bar_o_free[0]), 128);
+    mbar_init(smem_u32(&bar_o_free[1]), 128);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -196,20 +204,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const bool first_of_entry = (u == 0) || unit_entry(sUnits[u - 1]) != e;
         const bool last_of_entry = (u + 1 >= nu) || unit_entry(sUnits[u + 1]) != e;
         uint4 cs, cp;
+        // ring stages and barrier parities run on across heads, so the issuers keep them in counters;
+        // the commands carry what is the same for every head
         cs.x = loQ0 + i * (C::TILE_BYTES >> 4);
-        cs.y = loK0 + (e % C::KST) * (C::TILE_BYTES >> 4);
-        cs.z = (e % C::KST) | (((e / C::KST) & 1) ? CMD_PARITY : 0u) | (first_of_entry ? CMD_WAIT : 0u) | (last_of_entry ? CMD_RELEASE : 0u) |
-               (i ? CMD_TILE1 : 0u);
+        cs.y = loK0;
+        cs.z = (first_of_entry ? CMD_WAIT : 0u) | (last_of_entry ? CMD_RELEASE : 0u) | (i ? CMD_TILE1 : 0u);
         cs.w = 0u;
         cp.x = 0u;
-        cp.y = loV0 + (e % C::VST) * (C::TILE_BYTES >> 4);
-        cp.z = (e % C::VST) | (((e / C::VST) & 1) ? CMD_PARITY : 0u) | (first_of_entry ? CMD_WAIT : 0u) | (last_of_entry ? CMD_RELEASE : 0u) |
-               (rank_tile == 0 ? 0u : CMD_ACC) | (i ? CMD_TILE1 : 0u);
+        cp.y = loV0;
+        cp.z = (first_of_entry ? CMD_WAIT : 0u) | (last_of_entry ? CMD_RELEASE : 0u) | (rank_tile == 0 ? 0u : CMD_ACC) |
+               (i ? CMD_TILE1 : 0u);
         cp.w = 0u;
         sCmd[2 * u] = cs;
         sCmd[2 * u + 1] = cp;
-        sWcmd[i * 256 + rank_tile] = (sList[e] & 0xFFu) | (unit_class(un) << 8) | (static_cast<uint32_t>(buf) << 10) |
-                                     (static_cast<uint32_t>(rank_key & 1) << 12);
+        sWcmd[i * 256 + rank_tile] = (sList[e] & 0xFFu) | (unit_class(un) << 8) | (static_cast<uint32_t>(buf) << 10);
+        (void)rank_key;
       }
     }
     if (lane == 0) {
@@ -238,99 +247,144 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
       const int ntile_q = (2 * pair + 1 < a.NT) ? 2 : 1;
-      mbar_arrive_expect_tx(smem_u32(&bar_q_full), ntile_q * C::TILE_BYTES);
-      for (int t = 0; t < ntile_q; ++t)
-        for (int kb = 0; kb < C::KBLK; ++kb)
-          tma_load_4d(sQ + t * C::TILE_BYTES + kb * 16384, &tmQ, smem_u32(&bar_q_full), kb * 64,
-                      (2 * pair + t) * KD_TILE, h, b);
-      int k_issued = 0, v_issued = 0;
-      for (int e = 0; e < n; ++e) {
-        const int kt = sList[e] & 0xFF;
-        {
-          const int s = e % C::KST;
-          if (!mbar_wait(smem_u32(&bar_k_empty[s]), ((e / C::KST) & 1) ^ 1, &abortf, a.status, W_F_KEMPTY)) break;
-          mbar_arrive_expect_tx(smem_u32(&bar_k_full[s]), C::TILE_BYTES);
+      bool ok = true;
+      auto load_q = [&](int hh) -> bool {   // Q pair of head h0 + hh into buffer hh % NQ
+        const int qb = hh % C::NQ, qround = hh / C::NQ;
+        if (qround > 0 && !mbar_wait(smem_u32(&bar_q_empty[qb]), (qround - 1) & 1, &abortf, a.status, W_F_QEMPTY)) return false;
+        mbar_arrive_expect_tx(smem_u32(&bar_q_full[qb]), ntile_q * C::TILE_BYTES);
+        for (int t = 0; t < ntile_q; ++t)
           for (int kb = 0; kb < C::KBLK; ++kb)
-            tma_load_4d(sK + s * C::TILE_BYTES + kb * 16384, &tmK, smem_u32(&bar_k_full[s]), kb * 64, kt * KD_TILE, h, b);
-          k_issued = e + 1;
+            tma_load_4d(sQ + (qb * 2 + t) * C::TILE_BYTES + kb * 16384, &tmQ, smem_u32(&bar_q_full[qb]), kb * 64,
+                        (2 * pair + t) * KD_TILE, h0 + hh, b);
+        return true;
+      };
+      int k_cnt = 0, v_cnt = 0, q_loaded = 0;   // tiles issued so far, over all heads
+      ok = load_q(0);
+      q_loaded = 1;
+      for (int hh = 0; hh < nh && ok; ++hh) {
+        if (C::NQ > 1 && hh + 1 < nh) {       // next head's Q lands while this head runs
+          ok = load_q(hh + 1);
+          q_loaded = hh + 2;
+          if (!ok) break;
         }
-        {
-          const int s = e % C::VST;
-          if (!mbar_wait(smem_u32(&bar_v_empty[s]), ((e / C::VST) & 1) ^ 1, &abortf, a.status, W_F_VEMPTY)) break;
-          mbar_arrive_expect_tx(smem_u32(&bar_v_full[s]), C::TILE_BYTES);
-          for (int kb = 0; kb < C::KBLK; ++kb)
-            tma_load_4d(sV + s * C::TILE_BYTES + kb * 16384, &tmV, smem_u32(&bar_v_full[s]), kb * 64, kt * KD_TILE, h, b);
-          v_issued = e + 1;
+        for (int e = 0; e < n && ok; ++e) {
+          const int kt = sList[e] & 0xFF;
+          {
+            const int s = k_cnt % C::KST;
+            ok = mbar_wait(smem_u32(&bar_k_empty[s]), ((k_cnt / C::KST) & 1) ^ 1, &abortf, a.status, W_F_KEMPTY);
+            if (!ok) break;
+            mbar_arrive_expect_tx(smem_u32(&bar_k_full[s]), C::TILE_BYTES);
+            for (int kb = 0; kb < C::KBLK; ++kb)
+              tma_load_4d(sK + s * C::TILE_BYTES + kb * 16384, &tmK, smem_u32(&bar_k_full[s]), kb * 64, kt * KD_TILE, h0 + hh, b);
+            ++k_cnt;
+          }
+          {
+            const int s = v_cnt % C::VST;
+            ok = mbar_wait(smem_u32(&bar_v_empty[s]), ((v_cnt / C::VST) & 1) ^ 1, &abortf, a.status, W_F_VEMPTY);
+            if (!ok) break;
+            mbar_arrive_expect_tx(smem_u32(&bar_v_full[s]), C::TILE_BYTES);
+            for (int kb = 0; kb < C::KBLK; ++kb)
+              tma_load_4d(sV + s * C::TILE_BYTES + kb * 16384, &tmV, smem_u32(&bar_v_full[s]), kb * 64, kt * KD_TILE, h0 + hh, b);
+            ++v_cnt;
+          }
+        }
+        if (C::NQ == 1 && hh + 1 < nh && ok) {
+          ok = load_q(hh + 1);
+          q_loaded = hh + 2;
         }
       }
       if (abortf.v != 0) {
         // unwinding: let every copy already in flight land (bounded) before the CTA exits
-        for (int e = max(0, k_issued - C::KST); e < k_issued; ++e) drain_wait(smem_u32(&bar_k_full[e % C::KST]), (e / C::KST) & 1);
-        for (int e = max(0, v_issued - C::VST); e < v_issued; ++e) drain_wait(smem_u32(&bar_v_full[e % C::VST]), (e / C::VST) & 1);
-        drain_wait(smem_u32(&bar_q_full), 0);
+        for (int e = max(0, k_cnt - C::KST); e < k_cnt; ++e) drain_wait(smem_u32(&bar_k_full[e % C::KST]), (e / C::KST) & 1);
+        for (int e = max(0, v_cnt - C::VST); e < v_cnt; ++e) drain_wait(smem_u32(&bar_v_full[e % C::VST]), (e / C::VST) & 1);
+        for (int hh = max(0, q_loaded - C::NQ); hh < q_loaded; ++hh) drain_wait(smem_u32(&bar_q_full[hh % C::NQ]), (hh / C::NQ) & 1);
       }
     } else if (warp == 3 && lane == 0 && U > 0) {
       // ------------------------------ S issuer ------------------------------
       const uint32_t idesc_s = make_idesc_f16(kBf16, 0, 0, KD_TILE, KD_TILE);
       const uint32_t hi = desc_hi_sw128();
-      bool ok = mbar_wait(smem_u32(&bar_q_full), 0, &abortf, a.status, W_F_QFULL);
-      int buf = 0, round = 0;      // unit u uses buffer u % NBUF in round u / NBUF
-      for (int u = 0; u < U && ok; ++u) {
-        const uint4 c = sCmd[2 * u];
-        if (round > 0) {
-          // the buffer is free once P V of the unit that used it in the previous round has been issued
-          ok = mbar_wait(smem_u32(&bar_pv_issued[buf]), (round - 1) & 1, &abortf, a.status, W_F_PVISSUED);
-          if (!ok) break;
-        }
-        if (c.z & CMD_WAIT) {
-          ok = mbar_wait(smem_u32(&bar_k_full[c.z & CMD_STAGE]), (c.z & CMD_PARITY) ? 1u : 0u, &abortf, a.status, W_F_KFULL);
-          if (!ok) break;
-        }
-        tc_fence_after_sync();
-        const uint32_t d = tbase + buf * 128;
+      bool ok = true;
+      int buf = 0, round = 0;      // the g-th unit over all heads uses buffer g % NBUF in round g / NBUF
+      int kstage = 0;
+      uint32_t kparity = 0;
+      for (int hh = 0; hh < nh && ok; ++hh) {
+        const int qb = hh % C::NQ;
+        ok = mbar_wait(smem_u32(&bar_q_full[qb]), (hh / C::NQ) & 1, &abortf, a.status, W_F_QFULL);
+        const uint32_t q_off = qb * (2 * C::TILE_BYTES >> 4);
+        for (int u = 0; u < U && ok; ++u) {
+          const uint4 c = sCmd[2 * u];
+          if (round > 0) {
+            // the buffer is free once P V of the unit that used it in the previous round has been issued
+            ok = mbar_wait(smem_u32(&bar_pv_issued[buf]), (round - 1) & 1, &abortf, a.status, W_F_PVISSUED);
+            if (!ok) break;
+          }
+          if (c.z & CMD_WAIT) {
+            ok = mbar_wait(smem_u32(&bar_k_full[kstage]), kparity, &abortf, a.status, W_F_KFULL);
+            if (!ok) break;
+          }
+          tc_fence_after_sync();
+          const uint32_t d = tbase + buf * 128;
+          const uint32_t qlo = c.x + q_off, klo = c.y + kstage * (C::TILE_BYTES >> 4);
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss_split(d, c.x + koff_kmajor(kk), c.y + koff_kmajor(kk), hi, idesc_s, kk > 0 ? 1u : 0u);
-        mma_commit(smem_u32(&bar_s_full[2 * buf + ((c.z & CMD_TILE1) ? 1 : 0)]));
-        if (c.z & CMD_RELEASE) mma_commit(smem_u32(&bar_k_empty[c.z & CMD_STAGE]));
-        tr.ev(15);
-        if (++buf == C::NBUF) {
-          buf = 0;
-          ++round;
+          for (int kk = 0; kk < HD / 16; ++kk)
+            mma_ss_split(d, qlo + koff_kmajor(kk), klo + koff_kmajor(kk), hi, idesc_s, kk > 0 ? 1u : 0u);
+          mma_commit(smem_u32(&bar_s_full[2 * buf + ((c.z & CMD_TILE1) ? 1 : 0)]));
+          if (c.z & CMD_RELEASE) {
+            mma_commit(smem_u32(&bar_k_empty[kstage]));
+            if (++kstage == C::KST) { kstage = 0; kparity ^= 1; }
+          }
+          tr.ev(15);
+          if (++buf == C::NBUF) {
+            buf = 0;
+            ++round;
+          }
         }
+        if (ok) mma_commit(smem_u32(&bar_q_empty[qb]));   // Q of this head is no longer read once the MMAs above are done
       }
     } else if (warp == 1 && lane == 0 && U > 0) {
       // ------------------------------ P V issuer ------------------------------
       const uint32_t idesc_o = make_idesc_f16(kBf16, 0, 1, KD_TILE, HD);
       const uint32_t hi = desc_hi_sw128();
       bool ok = true;
-      int buf = 0;
-      uint32_t round_parity = 0;
-      for (int u = 0; u < U && ok; ++u) {
-        const uint4 c = sCmd[2 * u + 1];
-        ok = mbar_wait(smem_u32(&bar_p_full[buf]), round_parity, &abortf, a.status, W_F_PFULL);
-        if (!ok) break;
-        tr.ev(10);
-        if (c.z & CMD_WAIT) {
-          ok = mbar_wait(smem_u32(&bar_v_full[c.z & CMD_STAGE]), (c.z & CMD_PARITY) ? 1u : 0u, &abortf, a.status, W_F_VFULL);
+      int buf = 0, vstage = 0;
+      uint32_t round_parity = 0, vparity = 0;
+      for (int hh = 0; hh < nh && ok; ++hh) {
+        for (int u = 0; u < U && ok; ++u) {
+          const uint4 c = sCmd[2 * u + 1];
+          ok = mbar_wait(smem_u32(&bar_p_full[buf]), round_parity, &abortf, a.status, W_F_PFULL);
           if (!ok) break;
-        }
-        tc_fence_after_sync();
-        const uint32_t i = (c.z & CMD_TILE1) ? 1u : 0u;
-        const uint32_t dO = tbase + C::TM_O0 + i * HD, aP = tbase + buf * 128;
-        const uint32_t acc0 = (c.z & CMD_ACC) ? 1u : 0u;
+          tr.ev(10);
+          if (c.z & CMD_WAIT) {
+            ok = mbar_wait(smem_u32(&bar_v_full[vstage]), vparity, &abortf, a.status, W_F_VFULL);
+            if (!ok) break;
+          }
+          const uint32_t i = (c.z & CMD_TILE1) ? 1u : 0u;
+          const uint32_t acc0 = (c.z & CMD_ACC) ? 1u : 0u;
+          if (acc0 == 0u && hh > 0) {
+            // first product of this query tile for a new head overwrites O_i: the softmax warpgroup must
+            // have read the previous head's result out of it
+            ok = mbar_wait(smem_u32(&bar_o_free[i]), (hh - 1) & 1, &abortf, a.status, W_F_OFREE);
+            if (!ok) break;
+          }
+          tc_fence_after_sync();
+          const uint32_t dO = tbase + C::TM_O0 + i * HD, aP = tbase + buf * 128;
+          const uint32_t vlo = c.y + vstage * (C::TILE_BYTES >> 4);
 #pragma unroll
-        for (int kk = 0; kk < KD_TILE / 16; ++kk)
-          mma_ts_split(dO, aP + kk * 8, c.y + koff_mnmajor(kk), hi, idesc_o, kk > 0 ? 1u : acc0);
-        mma_commit(smem_u32(&bar_pv_done[i]));
-        if (c.z & CMD_RELEASE) mma_commit(smem_u32(&bar_v_empty[c.z & CMD_STAGE]));
-        // hand the buffer back to the S issuer, ordered after the MMAs above
-        tc_fence_before_sync();
-        mbar_arrive(smem_u32(&bar_pv_issued[buf]));
-        tr.ev(11);
-        if (++buf == C::NBUF) {
-          buf = 0;
-          round_parity ^= 1;
+          for (int kk = 0; kk < KD_TILE / 16; ++kk)
+            mma_ts_split(dO, aP + kk * 8, vlo + koff_mnmajor(kk), hi, idesc_o, kk > 0 ? 1u : acc0);
+          mma_commit(smem_u32(&bar_pv_done[i]));
+          if (c.z & CMD_RELEASE) {
+            mma_commit(smem_u32(&bar_v_empty[vstage]));
+            if (++vstage == C::VST) { vstage = 0; vparity ^= 1; }
+          }
+          // hand the buffer back to the S issuer, ordered after the MMAs above
+          tc_fence_before_sync();
+          mbar_arrive(smem_u32(&bar_pv_issued[buf]));
+          tr.ev(11);
+          if (++buf == C::NBUF) {
+            buf = 0;
+            round_parity ^= 1;
+          }
         }
       }
     }
@@ -349,8 +403,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const float c = a.scale_log2;
 
     const uint32_t qd = tile_valid ? a.desc[(size_t)b * a.Tpad + qi] : 0u;
-    float m = -INFINITY, l = 0.f;
-    int nact = 0;
     bool ok = true;
 
     // Key descriptors of PARTIAL tiles are fetched one unit ahead into registers, so their
@@ -376,12 +428,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     };
     uint32_t cmd_next = n_own > 0 ? wcmd[0] : 0u;
     if (n_own > 0) prefetch_kd(cmd_next);
+    // state that runs on across the heads of this CTA
+    int buf_off = 0;            // (units of the heads done so far) mod NBUF: rotation of the buffers
+    uint32_t sfull_par = 0;     // bit j: parity of the next phase of this tile's score barrier on buffer j
+    int pv_seen = 0;            // P V products of this query tile issued so far (phases of bar_pv_done[i])
 
+    for (int hh = 0; hh < nh && ok; ++hh) {
+    const int h = h0 + hh;
+    float m = -INFINITY, l = 0.f;
+    int nact = 0;
     for (int k = 0; k < n_own; ++k) {
       const uint32_t cmd = cmd_next;
       const uint32_t cls = wcmd_class(cmd);
       const int kt = wcmd_kt(cmd);
-      const int buf = wcmd_buf(cmd);
+      int buf = wcmd_buf(cmd) + buf_off;
+      if (buf >= C::NBUF) buf -= C::NBUF;
       const uint32_t tS = tbase + lane_base + buf * 128;
       tr.ev(20);
       uint32_t tb[12];
@@ -393,14 +454,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int j = 0; j < 12; ++j) tb[j] = tb_pre[j];
         __syncwarp();
       }
-      if (k + 1 < n_own) {
-        cmd_next = wcmd[k + 1];
+      if (k + 1 < n_own || hh + 1 < nh) {   // the next head walks the same list again
+        cmd_next = wcmd[k + 1 < n_own ? k + 1 : 0];
         prefetch_kd(cmd_next);
       }
       tr.ev(21);
-      ok = mbar_wait(smem_u32(&bar_s_full[2 * buf + i]), wcmd_parity(cmd), &abortf, a.status, W_F_SFULL);
+      ok = mbar_wait(smem_u32(&bar_s_full[2 * buf + i]), (sfull_par >> buf) & 1u, &abortf, a.status, W_F_SFULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      sfull_par ^= 1u << buf;
       tc_fence_after_sync();
       tr.ev(22);
 
@@ -486,7 +548,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (nact > 0) {
         // O_i may be touched only after the previous P V product of this query tile has completed;
         // the wait is taken for every unit so that no phase of the barrier goes unobserved
-        ok = mbar_wait(smem_u32(&bar_pv_done[i]), (nact - 1) & 1, &abortf, a.status, W_F_PVDONE);
+        ok = mbar_wait(smem_u32(&bar_pv_done[i]), (pv_seen - 1) & 1, &abortf, a.status, W_F_PVDONE);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
       }
@@ -510,11 +572,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_arrive(smem_u32(&bar_p_full[buf]));
       tr.ev(25);
       ++nact;
+      ++pv_seen;
     }
+    if (!ok) break;
+    buf_off += U % C::NBUF;
+    if (buf_off >= C::NBUF) buf_off -= C::NBUF;
 
-    // epilogue: normalise, convert, store O and LSE
-    if (ok && nact > 0) {
-      ok = mbar_wait(smem_u32(&bar_pv_done[i]), (nact - 1) & 1, &abortf, a.status, W_F_PVDONE);
+    // epilogue of this head: normalise, convert, store O and LSE
+    if (nact > 0) {
+      ok = mbar_wait(smem_u32(&bar_pv_done[i]), (pv_seen - 1) & 1, &abortf, a.status, W_F_PVDONE);
       ok = __all_sync(0xffffffffu, ok);
     }
     tr.ev(30);
@@ -535,9 +601,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
+        if (cb == HD / 32 - 1 && nact > 0) {
+          // O_i has been read out: the next head's first product may overwrite it
+          tc_fence_before_sync();
+          mbar_arrive(smem_u32(&bar_o_free[i]));
+        }
         if (tile_valid && qi < a.T) store_row32<kBf16>(orow + cb * 32, r, inv_l);
       }
     }
+    }  // heads
   }
 
   tr.ev(31);
@@ -557,6 +629,7 @@ static int launch_fwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
   FwdArgs a;
   a.B = p.B; a.H = p.H; a.T = p.T; a.NT = L.NT; a.NP = L.NP; a.Tpad = L.NT * KD_TILE;
   a.scale_log2 = p.sm_scale * 1.4426950408889634f;
+  a.G = heads_per_cta(p.B, p.H, L.NP);
   a.desc = pv.desc; a.fwd_cnt = pv.fwd_cnt; a.fwd_list = pv.fwd_list; a.status = pv.status;
   a.order = pv.order; a.trace = trace_buffer(); a.tilebits = pv.tilebits;
   a.o = p.o.ptr; a.o_sb = p.o.stride_b; a.o_sh = p.o.stride_h; a.o_st = p.o.stride_t;
@@ -564,7 +637,7 @@ static int launch_fwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
   auto kern = attn_fwd_kernel<HD, kBf16>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_ALLOC);
   if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "fwd smem attribute: %s", cudaGetErrorString(e));
-  dim3 grid(p.H, p.B, L.NP);
+  dim3 grid((p.H + a.G - 1) / a.G, p.B, L.NP);
   kern<<<grid, 384, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "attn_fwd_kernel launch: %s", cudaGetErrorString(e));
