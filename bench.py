@@ -218,8 +218,8 @@ def run_ours(args, cfg):
 
     B, H, L, D = cfg["B"], cfg["H"], cfg["L"], cfg["D"]
     dtype = torch.bfloat16 if cfg["dtype"] == "bf16" else torch.float16
-    seed = 1234 + rank
-    ins, sid, pre, lens = make_metadata(cfg, seed)
+    seed = 1234 + rank                       # Q, K, V, dO differ per rank
+    ins, sid, pre, lens = make_metadata(cfg, 1234)   # same section layout on every rank: equal work per GPU
     tt = lambda a, dt: None if a is None else torch.as_tensor(a, dtype=dt, device=dev)
     meta = dict(in_span=tt(ins, torch.bool), span_id=tt(sid, torch.int64), is_prefix=tt(pre, torch.bool),
                 lens=tt(lens, torch.int32))
@@ -360,7 +360,7 @@ def run_ours(args, cfg):
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu_baseline and not args.kernels_only:
-            tf, sample, _, _ = time_cpu_oracle(cfg, seed, 15.0)
+            tf, sample, _, _ = time_cpu_oracle(cfg, 1234, 15.0)
             cpu = {"value": tf, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port", "sample": sample}
         per_gpu = value / world
         line = {
