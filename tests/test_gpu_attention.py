@@ -240,3 +240,22 @@ def test_full_size_config1_causal_sampled_heads():
     for (b, h) in [(0, 0), (7, 15)]:
         sl = lambda x: x[b:b + 1, h:h + 1].cpu()
         compare(sl(q), sl(k), sl(v), sl(do), mask, tuple(x[b:b + 1, h:h + 1].contiguous() for x in got))
+
+
+def test_host_pipeline_matches_direct_call():
+    from kerneldev_b200 import flash_attention
+    from kerneldev_b200.host_io import HostPipeline
+    B, H, T, D = 6, 2, 256, 64
+    ins, sid, pre, lens = ao.batch_metadata(3, B, T, prefix=(8, 40), context=(64, 120), n_spans=(1, 4), span_len=(8, 30))
+    meta = dict(in_span=_t(ins, torch.bool), span_id=_t(sid, torch.int64), is_prefix=_t(pre, torch.bool), lens=_t(lens, torch.int32))
+    hq, hk, hv, hdo = (x.pin_memory() for x in rand_inputs(B, H, T, D, torch.bfloat16, seed=77))
+    outs = [torch.empty_like(hq).pin_memory() for _ in range(4)]
+    pipe = HostPipeline(DEV, chunks=4)
+    for _ in range(2):   # second run reuses the staging buffers
+        pipe.run(hq, hk, hv, hdo, *outs, causal=True, **meta)
+        torch.cuda.synchronize()
+    q, k, v = (x.to(DEV).requires_grad_() for x in (hq, hk, hv))
+    o = flash_attention(q, k, v, causal=True, **meta)
+    o.backward(hdo.to(DEV))
+    for got, ref in zip(outs, (o, q.grad, k.grad, v.grad)):
+        assert torch.equal(got, ref.cpu())
