@@ -251,7 +251,7 @@ def run_ours(args, cfg):
             dq, dk = _hadamard_call(dq, signs, True), _hadamard_call(dk, signs, True)
         return o, lse
 
-    launches_per_step = 3 + (4 if signs is not None else 0)
+    launches_per_step = 4 + (4 if signs is not None else 0)   # forward, delta, dQ, dK/dV (+ Hadamard passes)
 
     def barrier():
         if world > 1:

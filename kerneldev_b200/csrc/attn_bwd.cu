@@ -5,7 +5,7 @@
 // (_flash_attn_bwd_dq, original_kernel.py:1173-1336; _flash_attn_bwd_dkdv, :1339-1525), but
 // walk only the non-empty tiles of the plan and apply the rule only on PARTIAL tiles.
 // delta = rowsum(O * dO) (the reference's _flash_attn_bwd_precompute, :629-710) is produced
-// by the dQ kernel's prologue and consumed by the dK/dV kernel, which therefore runs second.
+// by a small bandwidth-bound kernel ahead of the other two.
 //
 // Shared structure (384 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warps 4-7 and
 // 8-11 = two compute warpgroups. The backward needs no row reductions, so the 128 columns of a
@@ -17,6 +17,7 @@
 // The tensor pipe executes in issue order, so M1(u + NBUF) may overwrite the buffer M2(u) read.
 // M1 and M2 are issued by two different single threads (warps 3 and 1): each shares its scheduler
 // with two compute warps, and splitting the work keeps either one off the critical path.
+#include <algorithm>
 #include <mutex>
 
 #include "attn_common.cuh"
@@ -77,6 +78,42 @@ enum : uint32_t {
   W_K_FIXFULL = 0x301, W_K_RINGEMPTY = 0x302, W_K_RINGFULL = 0x303, W_K_PFULL = 0x304, W_K_SFULL = 0x305,
   W_K_ACCFULL = 0x306, W_K_M2ISSUED = 0x307,
 };
+
+// =========================================================================================
+// delta kernel: delta[b, h, t] = sum_d O[b, h, t, d] * dO[b, h, t, d] in fp32 (the reference's
+// _flash_attn_bwd_precompute, original_kernel.py:629-710). HD/8 threads share a row, 16 bytes of
+// each tensor per thread, so a warp reads whole 128-byte lines; bound by HBM bandwidth.
+// =========================================================================================
+template <int HD, bool kBf16>
+__global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const BwdArgs a) {
+  constexpr int TPR = HD / 8;   // threads per row
+  constexpr int RPB = 256 / TPR;   // rows per block and iteration
+  const size_t rows = (size_t)a.B * a.H * a.T;
+  const int sub = threadIdx.x % TPR;
+  // the loop bound is the same for every thread of the block: the shuffles below need full warps
+  for (size_t base = (size_t)blockIdx.x * RPB; base < rows; base += (size_t)gridDim.x * RPB) {
+    const size_t r = base + threadIdx.x / TPR;
+    const bool live = r < rows;
+    float acc = 0.f;
+    if (live) {
+      const int t = static_cast<int>(r % a.T);
+      const int h = static_cast<int>((r / a.T) % a.H);
+      const int b = static_cast<int>(r / ((size_t)a.T * a.H));
+      const uint4 ov = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(a.o) + (size_t)b * a.o_sb + (size_t)h * a.o_sh + (size_t)t * a.o_st + sub * 8);
+      const uint4 dv = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(a.d_o) + (size_t)b * a.do_sb + (size_t)h * a.do_sh + (size_t)t * a.do_st + sub * 8);
+      const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w}, dw[4] = {dv.x, dv.y, dv.z, dv.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 x = unpack2<kBf16>(ow[k]), y = unpack2<kBf16>(dw[k]);
+        acc = fmaf(x.x, y.x, acc);
+        acc = fmaf(x.y, y.y, acc);
+      }
+    }
+#pragma unroll
+    for (int d = TPR / 2; d >= 1; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+    if (live && sub == 0) a.delta[r] = acc;
+  }
+}
 
 // =========================================================================================
 // dQ kernel: one CTA per (b, h, query tile); streams = key halves of the current key tile.
@@ -264,24 +301,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const float c = a.scale_log2;
     const size_t bh = (size_t)b * a.H + h;
 
-    // delta = rowsum(O * dO) for this thread's query row
-    float delta = 0.f;
-    if (q_valid) {
-      const uint4* orow = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(a.o) + (size_t)b * a.o_sb + (size_t)h * a.o_sh + (size_t)qi * a.o_st);
-      const uint4* drow = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(a.d_o) + (size_t)b * a.do_sb + (size_t)h * a.do_sh + (size_t)qi * a.do_st);
-#pragma unroll
-      for (int j = 0; j < HD / 8; ++j) {
-        const uint4 ov = orow[j], dv = drow[j];
-        const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w}, dw[4] = {dv.x, dv.y, dv.z, dv.w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const float2 x = unpack2<kBf16>(ow[k]), y = unpack2<kBf16>(dw[k]);
-          delta = fmaf(x.x, y.x, delta);
-          delta = fmaf(x.y, y.y, delta);
-        }
-      }
-      if (i == 0) a.delta[bh * a.T + qi] = delta;
-    }
+    const float delta = q_valid ? a.delta[bh * a.T + qi] : 0.f;
     const float neg_lse = q_valid ? -a.lse[bh * a.T + qi] : 0.f;
     const uint32_t qd = a.desc[(size_t)b * a.Tpad + qi];
     bool ok = true;
@@ -751,7 +771,13 @@ static int launch_bwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
   if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "bwd smem attribute: %s", cudaGetErrorString(e));
   dim3 grid(p.H, p.B, L.NT);
   const int phases = (p.bwd_phases & 3) ? (p.bwd_phases & 3) : 3;
-  if (phases & 1) kq<<<grid, 384, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
+  if (phases & 1) {
+    const size_t rows = (size_t)p.B * p.H * p.T;
+    const int rows_per_block = 256 / (HD / 8);
+    const int blocks = static_cast<int>(std::min<size_t>((rows + rows_per_block - 1) / rows_per_block, size_t(148) * 32));
+    attn_bwd_delta_kernel<HD, kBf16><<<blocks, 256, 0, stream>>>(a);
+    kq<<<grid, 384, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
+  }
   if (phases & 2) kk<<<grid, 384, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "attn_bwd kernels launch: %s", cudaGetErrorString(e));

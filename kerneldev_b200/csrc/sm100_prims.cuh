@@ -342,15 +342,21 @@ __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
 // optional in-kernel timeline (compiled in only with -DKD_TRACE; used to find the critical path)
 // ---------------------------------------------------------------------------------------
 #ifdef KD_TRACE
+#ifndef KD_TRACE_SLOTS
+#define KD_TRACE_SLOTS 256
+#endif
+#ifndef KD_TRACE_MASK
+#define KD_TRACE_MASK 0xFFFFFFFFFFFFFFFFull   // bit id: record event id (ids below 64)
+#endif
 struct Tracer {
   unsigned long long* p;
   int n;
   __device__ __forceinline__ void init(unsigned long long* base, bool on, int slot) {
-    p = (on && base) ? base + (size_t)slot * 256 : nullptr;
+    p = (on && base) ? base + (size_t)slot * KD_TRACE_SLOTS : nullptr;
     n = 0;
   }
   __device__ __forceinline__ void ev(uint32_t id) {
-    if (p && n < 255) {
+    if (((KD_TRACE_MASK >> (id & 63u)) & 1ull) && p && n < KD_TRACE_SLOTS - 1) {
       p[1 + n] = (static_cast<unsigned long long>(id) << 48) | (static_cast<unsigned long long>(clock64()) & 0xFFFFFFFFFFFFull);
       ++n;
       p[0] = n;
