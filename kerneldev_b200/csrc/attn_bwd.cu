@@ -7,16 +7,20 @@
 // delta = rowsum(O * dO) (the reference's _flash_attn_bwd_precompute, :629-710) is produced
 // by a small bandwidth-bound kernel ahead of the other two.
 //
-// Shared structure (384 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warps 4-7 and
-// 8-11 = two compute warpgroups. The backward needs no row reductions, so the 128 columns of a
-// score tile are split into two 64-column halves, one per warpgroup. A "unit" u = 2*entry + half;
-// it owns TMEM buffer u % NBUF (64 columns of scores + 64 of dP) and the issuer runs NBUF units
-// ahead, so that a warpgroup finishing unit u finds its next unit's scores already in TMEM:
+// Shared structure (640 threads): warp 0 = TMA producer, warps 1-3 = MMA issuers, warps 4-19 =
+// four compute warpgroups. The backward needs no row reductions, so a 128-column score tile is
+// split by columns: a "unit" u = 2*entry + half is one 64-column half, and two warpgroups share a
+// unit, 32 columns each, so that sixteen warps (four per scheduler) hide one another's
+// tensor-memory, barrier and special-function latencies. A unit owns TMEM buffer u % NBUF
+// (64 columns of scores + 64 of dP) and the issuers run NBUF units ahead, so that a warpgroup
+// finishing unit u finds its next unit's scores already in TMEM:
 //   M1(u): S_u, dP_u  (smem x smem -> TMEM, N = 64)      compute(u): P_u / dS_u -> TMEM (16 bit)
 //   M2(u): accumulators += (P_u | dS_u) x smem operand   (A from TMEM);   then M1(u + NBUF)
+// Each warpgroup writes its 16 packed columns over the start of the 32 fp32 columns it has just
+// read, so the 16-bit operand of a unit sits at columns [0,16) and [32,48) of the buffer.
 // The tensor pipe executes in issue order, so M1(u + NBUF) may overwrite the buffer M2(u) read.
-// M1 and M2 are issued by two different single threads (warps 3 and 1): each shares its scheduler
-// with two compute warps, and splitting the work keeps either one off the critical path.
+// M1 and M2 are issued by different single threads (warps 3 and 2 for M1, warp 1 for M2), so
+// that none of them is on the critical path of the other.
 #include <algorithm>
 #include <mutex>
 
@@ -60,8 +64,8 @@ struct BwdCfg {
   static constexpr int SMEM_FIX = 0;                               // two resident tiles
   static constexpr int SMEM_RING = SMEM_FIX + 2 * TILE_BYTES;      // STAGES x two streamed tiles
   static constexpr int SMEM_STAGE = SMEM_RING + STAGES * 2 * TILE_BYTES;  // per-warp staging
-  static constexpr int STAGE_WORDS = 3 * 64;                       // 64 x {-lse, delta, descriptor}
-  static constexpr int SMEM_ACT = SMEM_STAGE + 8 * STAGE_WORDS * 4;  // compacted entry list
+  static constexpr int STAGE_WORDS = 3 * 32;                       // 32 x {-lse, delta, descriptor}
+  static constexpr int SMEM_ACT = SMEM_STAGE + 16 * STAGE_WORDS * 4;  // compacted entry list
   static constexpr int SMEM_TOTAL = SMEM_ACT + 128 * 2;
   static constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;
   // TMEM columns
@@ -120,7 +124,7 @@ __global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const BwdArgs a) {
 //   M1(i): S_i = Q K_i^T, dP_i = dO V_i^T      M2(i): dQ += dS_i K_i
 // =========================================================================================
 template <int HD, bool kBf16>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(640, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                    const BwdArgs a) {
@@ -140,6 +144,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   __shared__ AbortFlag abortf;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  cta_trace(a.trace, 1);
   const int h = blockIdx.x, b = blockIdx.y;
   const int qt = a.order[((size_t)b * 3 + 1) * a.NT + blockIdx.z];   // longest lists first
   const int pair = qt >> 1, ip = qt & 1;
@@ -153,7 +158,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     for (int i = 0; i < C::NBUF; ++i) {
       mbar_init(smem_u32(&bar_s_full[i]), 2);     // one commit from each of the two M1 issuers
-      mbar_init(smem_u32(&bar_p_full[i]), 128);
+      mbar_init(smem_u32(&bar_p_full[i]), 256);   // the two warpgroups that share the unit
       mbar_init(smem_u32(&bar_m2_issued[i]), 1);
     }
     mbar_init(smem_u32(&bar_acc_full), 1);
@@ -187,6 +192,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 3 || warp == 1 || warp == 4 || warp == 8),
           blockIdx.z * 4 + (warp == 3 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));
   tr.ev(1);
+  cta_trace(a.trace, 2);
 
   if (warp < 4) {
     reg_dealloc<KD_REGS_ISSUE>();
@@ -275,10 +281,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tr.ev(10);
         tc_fence_after_sync();
         const uint32_t kb = loRingMN + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
-        const uint32_t aS = tbase + buf * 128;   // dS_u sits on top of S_u
+        const uint32_t aS = tbase + buf * 128;   // dS_u sits on top of S_u: keys 0-31 at columns [0,16), keys 32-63 at [32,48)
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // 64 keys of this unit, 16 per MMA
-          mma_ts_split(tAcc, aS + kk * 8, kb + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
+          mma_ts_split(tAcc, aS + (kk >> 1) * 32 + (kk & 1) * 8, kb + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
         if (i == 1) mma_commit(smem_u32(&bar_ring_empty[stage]));
         tc_fence_before_sync();
         mbar_arrive(smem_u32(&bar_m2_issued[buf]));
@@ -289,9 +295,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (ok) mma_commit(smem_u32(&bar_acc_full));
     }
   } else {
-    reg_alloc<KD_REGS_COMPUTE>();
+    reg_alloc<KD_REGS_COMPUTE_BWD>();
     // ------------------------------ compute warpgroups ------------------------------
-    const int i = (warp - 4) >> 2;   // stream: key half of each key tile
+    const int g = (warp - 4) >> 2;   // warpgroup
+    const int i = g >> 1;            // stream: key half (64 keys) of each key tile
+    const int sub = g & 1;           // 32-key slice of that half
     const int wq = warp & 3;
     const int row = wq * 32 + lane;
     const int qi = qt * KD_TILE + row;
@@ -300,27 +308,23 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     uint32_t* kd_buf = sStage + (size_t)(warp - 4) * C::STAGE_WORDS;
     const float c = a.scale_log2;
     const size_t bh = (size_t)b * a.H + h;
-
     const float delta = q_valid ? a.delta[bh * a.T + qi] : 0.f;
     const float neg_lse = q_valid ? -a.lse[bh * a.T + qi] : 0.f;
     const uint32_t qd = a.desc[(size_t)b * a.Tpad + qi];
+    const int tbw = 2 * i + sub;     // this slice's word in the 128-bit class masks of a key tile
     bool ok = true;
 
     // key descriptors of PARTIAL tiles are fetched one entry ahead into registers
-    uint32_t kd_pre[2] = {0u, 0u};
-    uint32_t tb_pre[6] = {0u, 0u, 0u, 0u, 0u, 0u};   // key-side class masks of this half: is_prefix[2], context[2], in_span[2]
+    uint32_t kd_pre = 0u;
+    uint32_t tb_pre[3] = {0u, 0u, 0u};   // key-side class masks of this slice: is_prefix, context, in_span
     auto prefetch_kd = [&](int e) {
       if (e < na && (sAct[e] >> 8) == KD_TILE_PARTIAL) {
-        const uint32_t* src = a.desc + (size_t)b * a.Tpad + (size_t)(sAct[e] & 0xFFu) * KD_TILE + i * 64;
-        kd_pre[0] = src[lane];
-        kd_pre[1] = src[32 + lane];
-        const uint2* tbp = reinterpret_cast<const uint2*>(a.tilebits + ((size_t)b * a.NT + (sAct[e] & 0xFFu)) * 32);
-#pragma unroll
-        for (int j = 0; j < 3; ++j) {
-          const uint2 v = tbp[2 * j + i];   // words 2i, 2i+1 of masks TB_PRE, TB_CTX, TB_INS
-          tb_pre[2 * j] = v.x;
-          tb_pre[2 * j + 1] = v.y;
-        }
+        const uint32_t ktile = sAct[e] & 0xFFu;
+        kd_pre = a.desc[(size_t)b * a.Tpad + (size_t)ktile * KD_TILE + i * 64 + sub * 32 + lane];
+        const uint32_t* tbp = a.tilebits + ((size_t)b * a.NT + ktile) * 32;
+        tb_pre[0] = tbp[4 * TB_PRE + tbw];
+        tb_pre[1] = tbp[4 * TB_CTX + tbw];
+        tb_pre[2] = tbp[4 * TB_INS + tbw];
       }
     };
     prefetch_kd(0);
@@ -329,27 +333,26 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const uint32_t ent = sAct[e];
       const uint32_t cls = ent >> 8;
       const int kt = ent & 0xFF;
-      const int j0 = kt * KD_TILE + i * 64;  // first key of this stream
-      uint32_t mk[2] = {0xFFFFFFFFu, 0xFFFFFFFFu};   // visibility of this unit's 64 keys for this query row
+      const int j0 = kt * KD_TILE + i * 64 + sub * 32;  // first key of this slice
+      uint32_t mk = 0xFFFFFFFFu;   // visibility of this slice's 32 keys for this query row
       if (cls == KD_TILE_PARTIAL) {
         __syncwarp();
-        kd_buf[lane] = kd_pre[0];
-        kd_buf[32 + lane] = kd_pre[1];
+        kd_buf[lane] = kd_pre;
         __syncwarp();
-        query_row_mask<2>(qd, qi, j0, tb_pre + 0, tb_pre + 2, tb_pre + 4, mk);
-        if ((tb_pre[4] | tb_pre[5]) != 0u && __any_sync(0xffffffffu, (qd & TD_SIDPOS) != 0u)) {
+        query_row_mask<1>(qd, qi, j0, tb_pre + 0, tb_pre + 1, tb_pre + 2, &mk);
+        if (tb_pre[2] != 0u && __any_sync(0xffffffffu, (qd & TD_SIDPOS) != 0u)) {
           const uint32_t key = span_key_of_query(qd);
 #pragma unroll
-          for (int j = 0; j < 64; j += 4) {
+          for (int j = 0; j < 32; j += 4) {
             const uint4 k4 = *reinterpret_cast<const uint4*>(kd_buf + j);
-            mk[j >> 5] |= (span_match_key(key, k4.x) << ((j + 0) & 31)) | (span_match_key(key, k4.y) << ((j + 1) & 31)) |
-                          (span_match_key(key, k4.z) << ((j + 2) & 31)) | (span_match_key(key, k4.w) << ((j + 3) & 31));
+            mk |= (span_match_key(key, k4.x) << (j + 0)) | (span_match_key(key, k4.y) << (j + 1)) |
+                  (span_match_key(key, k4.z) << (j + 2)) | (span_match_key(key, k4.w) << (j + 3));
           }
         }
       }
       prefetch_kd(e + 1);
       const int u = 2 * e + i, buf = u % C::NBUF;
-      const uint32_t tS = tbase + lane_base + buf * 128, tP = tS + 64;
+      const uint32_t tS = tbase + lane_base + buf * 128 + sub * 32, tP = tS + 64;
       tr.ev(21);
       ok = mbar_wait(smem_u32(&bar_s_full[buf]), (u / C::NBUF) & 1, &abortf, a.status, W_Q_SFULL);
       ok = __all_sync(0xffffffffu, ok);
@@ -357,57 +360,58 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_after_sync();
       tr.ev(22);
 
-      uint32_t pk[32];
-#pragma unroll
-      for (int cb = 0; cb < 2; ++cb) {
+      uint32_t pk[16];
+      {
         uint32_t rs[32], rp[32];
-        tmem_ld32(tS + cb * 32, rs);
-        tmem_ld32(tP + cb * 32, rp);
+        tmem_ld32(tS, rs);
+        tmem_ld32(tP, rp);
         tmem_wait_ld();
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
           float pv[4];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) pv[u] = fast_exp2(fmaf(__uint_as_float(rs[j + u]), c, neg_lse));
+          for (int u2 = 0; u2 < 4; ++u2) pv[u2] = fast_exp2(fmaf(__uint_as_float(rs[j + u2]), c, neg_lse));
           if (cls == KD_TILE_PARTIAL) {
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-              if ((mk[cb] & (1u << (j + u))) == 0u) pv[u] = 0.f;
+            for (int u2 = 0; u2 < 4; ++u2)
+              if ((mk & (1u << (j + u2))) == 0u) pv[u2] = 0.f;
           }
           float ds[4];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) ds[u] = pv[u] * (__uint_as_float(rp[j + u]) - delta);
-          pk[cb * 16 + j / 2] = pack2<kBf16>(ds[0], ds[1]);
-          pk[cb * 16 + j / 2 + 1] = pack2<kBf16>(ds[2], ds[3]);
+          for (int u2 = 0; u2 < 4; ++u2) ds[u2] = pv[u2] * (__uint_as_float(rp[j + u2]) - delta);
+          pk[j / 2] = pack2<kBf16>(ds[0], ds[1]);
+          pk[j / 2 + 1] = pack2<kBf16>(ds[2], ds[3]);
         }
       }
       tr.ev(24);
-      tmem_st32(tS, pk);   // dS_u as 16-bit A operand on top of S_u (this thread's own row)
+      tmem_st16(tS, pk);   // dS of this slice as 16-bit A operand over the scores it was made from (this thread's own row)
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&bar_p_full[buf]));
       tr.ev(25);
     }
 
-    // epilogue: this warpgroup stores columns [i*HD/2, (i+1)*HD/2) of dQ
+    // epilogue: warpgroup g stores columns [g*HD/4, (g+1)*HD/4) of dQ
     if (ok && na > 0) {
       ok = mbar_wait(smem_u32(&bar_acc_full), 0, &abortf, a.status, W_Q_ACCFULL);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
       tc_fence_after_sync();
-      uint16_t* drow = reinterpret_cast<uint16_t*>(a.dq) + (size_t)b * a.dq_sb + (size_t)h * a.dq_sh + (size_t)qi * a.dq_st + i * (HD / 2);
+      constexpr int EC = HD / 4;
+      uint16_t* drow = reinterpret_cast<uint16_t*>(a.dq) + (size_t)b * a.dq_sb + (size_t)h * a.dq_sh + (size_t)qi * a.dq_st + g * EC;
+      uint32_t r[EC];
+      if (na > 0) {
+        if constexpr (EC == 16) tmem_ld16(tbase + lane_base + C::TM_ACC0 + g * EC, r);
+        else tmem_ld32(tbase + lane_base + C::TM_ACC0 + g * EC, r);
+        tmem_wait_ld();
+      } else {
 #pragma unroll
-      for (int cb = 0; cb < HD / 64; ++cb) {
-        uint32_t r[32];
-        if (na > 0) {
-          tmem_ld32(tbase + lane_base + C::TM_ACC0 + i * (HD / 2) + cb * 32, r);
-          tmem_wait_ld();
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = 0u;
-        }
-        if (q_valid) store_row32<kBf16>(drow + cb * 32, r, a.sm_scale);
+        for (int j = 0; j < EC; ++j) r[j] = 0u;
+      }
+      if (q_valid) {
+        if constexpr (EC == 16) store_row16<kBf16>(drow, r, a.sm_scale);
+        else store_row32<kBf16>(drow, r, a.sm_scale);
       }
     }
   }
@@ -416,6 +420,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tbase, 512);
+  cta_trace(a.trace, 3);
 }
 
 // =========================================================================================
@@ -423,7 +428,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 //   M1(i): S^T_i = K Q_i^T, dP^T_i = V dO_i^T     M2(i): dV += P^T_i dO_i,  dK += dS^T_i Q_i
 // =========================================================================================
 template <int HD, bool kBf16>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(640, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                      const BwdArgs a) {
@@ -442,6 +447,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   __shared__ AbortFlag abortf;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  cta_trace(a.trace, 1);
   const int h = blockIdx.x, b = blockIdx.y;
   const int kt = a.order[((size_t)b * 3 + 2) * a.NT + blockIdx.z];   // longest lists first
   const int n = a.bwd_cnt[b * a.NT + kt];
@@ -455,7 +461,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
     for (int i = 0; i < C::NBUF; ++i) {
       mbar_init(smem_u32(&bar_s_full[i]), 2);     // one commit from each of the two M1 issuers
-      mbar_init(smem_u32(&bar_p_full[i]), 128);
+      mbar_init(smem_u32(&bar_p_full[i]), 256);   // the two warpgroups that share the unit
       mbar_init(smem_u32(&bar_m2_issued[i]), 1);
     }
     mbar_init(smem_u32(&bar_acc_full), 1);
@@ -478,6 +484,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 3 || warp == 1 || warp == 4 || warp == 8),
           blockIdx.z * 4 + (warp == 3 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));
   tr.ev(1);
+  cta_trace(a.trace, 2);
 
   if (warp < 4) {
     reg_dealloc<KD_REGS_ISSUE>();
@@ -569,12 +576,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const uint32_t qb = loRingMN + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
         const uint32_t dob = qb + (C::TILE_BYTES >> 4);
         const uint32_t aS = tbase + buf * 128, aP = aS + 64;
+        // 16-bit operands: queries 0-31 of the unit at columns [0,16) of their buffer half, queries 32-63 at [32,48)
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // dV += P^T_u dO_u   (P^T_u on top of S^T_u)
-          mma_ts_split(tDV, aS + kk * 8, dob + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
+          mma_ts_split(tDV, aS + (kk >> 1) * 32 + (kk & 1) * 8, dob + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // dK += dS^T_u Q_u   (dS^T_u on top of dP^T_u)
-          mma_ts_split(tDK, aP + kk * 8, qb + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
+          mma_ts_split(tDK, aP + (kk >> 1) * 32 + (kk & 1) * 8, qb + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
         if (i == 1) mma_commit(smem_u32(&bar_ring_empty[stage]));
         tc_fence_before_sync();
         mbar_arrive(smem_u32(&bar_m2_issued[buf]));
@@ -585,49 +593,44 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if (ok) mma_commit(smem_u32(&bar_acc_full));
     }
   } else {
-    reg_alloc<KD_REGS_COMPUTE>();
+    reg_alloc<KD_REGS_COMPUTE_BWD>();
     // ------------------------------ compute warpgroups ------------------------------
-    const int i = (warp - 4) >> 2;   // stream: query half of each query tile
+    const int g = (warp - 4) >> 2;   // warpgroup
+    const int i = g >> 1;            // stream: query half (64 queries) of each query tile
+    const int sub = g & 1;           // 32-query slice of that half
     const int wq = warp & 3;
     const int row = wq * 32 + lane;
     const int kj = kt * KD_TILE + row;   // this thread's key
     const bool k_valid = kj < a.T;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
-    uint32_t* st_buf = sStage + (size_t)(warp - 4) * C::STAGE_WORDS;  // [64 -lse][64 delta][64 desc]
+    uint32_t* st_buf = sStage + (size_t)(warp - 4) * C::STAGE_WORDS;  // [32 -lse][32 delta][32 desc]
     const float c = a.scale_log2;
     const size_t bh = (size_t)b * a.H + h;
     const uint32_t kdesc = a.desc[(size_t)b * a.Tpad + kj];
+    const int tbw = 2 * i + sub;     // this slice's word in the 128-bit class masks of a query tile
     bool ok = true;
 
-    // -LSE, delta and the descriptors of the next entry's 64 queries are fetched one entry ahead
+    // -LSE, delta and the descriptor of the next entry's 32 queries are fetched one entry ahead
     // into registers and handed to the warp through its shared-memory staging buffer
-    float pre_lse[2] = {0.f, 0.f}, pre_delta[2] = {0.f, 0.f};
-    uint32_t pre_desc[2] = {0u, 0u};
-    // query-side class masks of the next unit: sees-prefix[2], sees-context[2], sees-in_span[2], context[2], same-span armed[2]
-    uint32_t tb_pre[10];
-#pragma unroll
-    for (int j = 0; j < 10; ++j) tb_pre[j] = 0u;
+    float pre_lse = 0.f, pre_delta = 0.f;
+    uint32_t pre_desc = 0u;
+    // query-side class masks of the next unit: sees-prefix, sees-context, sees-in_span, context, same-span armed
+    uint32_t tb_pre[5] = {0u, 0u, 0u, 0u, 0u};
     auto prefetch = [&](int e) {
       if (e < n) {
         if ((list[e] >> 8) == KD_TILE_PARTIAL) {
-          const uint2* tbp = reinterpret_cast<const uint2*>(a.tilebits + ((size_t)b * a.NT + (list[e] & 0xFFu)) * 32);
-          const int which[5] = {TB_SEES_PRE, TB_SEES_CTX, TB_SEES_INS, TB_CTX, TB_SIDPOS};
-#pragma unroll
-          for (int j = 0; j < 5; ++j) {
-            const uint2 v = tbp[2 * which[j] + i];
-            tb_pre[2 * j] = v.x;
-            tb_pre[2 * j + 1] = v.y;
-          }
+          const uint32_t* tbp = a.tilebits + ((size_t)b * a.NT + (list[e] & 0xFFu)) * 32;
+          tb_pre[0] = tbp[4 * TB_SEES_PRE + tbw];
+          tb_pre[1] = tbp[4 * TB_SEES_CTX + tbw];
+          tb_pre[2] = tbp[4 * TB_SEES_INS + tbw];
+          tb_pre[3] = tbp[4 * TB_CTX + tbw];
+          tb_pre[4] = tbp[4 * TB_SIDPOS + tbw];
         }
-        const int q0 = (list[e] & 0xFF) * KD_TILE + i * 64;
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          const int q = q0 + r * 32 + lane;
-          const bool v = q < a.T;
-          pre_lse[r] = v ? -a.lse[bh * a.T + q] : 0.f;
-          pre_delta[r] = v ? a.delta[bh * a.T + q] : 0.f;
-          pre_desc[r] = a.desc[(size_t)b * a.Tpad + q];
-        }
+        const int q = (list[e] & 0xFF) * KD_TILE + i * 64 + sub * 32 + lane;
+        const bool v = q < a.T;
+        pre_lse = v ? -a.lse[bh * a.T + q] : 0.f;
+        pre_delta = v ? a.delta[bh * a.T + q] : 0.f;
+        pre_desc = a.desc[(size_t)b * a.Tpad + q];
       }
     };
     prefetch(0);
@@ -636,32 +639,29 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const uint32_t ent = list[e];
       const uint32_t cls = ent >> 8;
       const int qt = ent & 0xFF;
-      const int i0 = qt * KD_TILE + i * 64;  // first query of this stream
+      const int i0 = qt * KD_TILE + i * 64 + sub * 32;  // first query of this slice
       tr.ev(20);
       __syncwarp();
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        st_buf[r * 32 + lane] = __float_as_uint(pre_lse[r]);
-        st_buf[64 + r * 32 + lane] = __float_as_uint(pre_delta[r]);
-        st_buf[128 + r * 32 + lane] = pre_desc[r];
-      }
+      st_buf[lane] = __float_as_uint(pre_lse);
+      st_buf[32 + lane] = __float_as_uint(pre_delta);
+      st_buf[64 + lane] = pre_desc;
       __syncwarp();
-      uint32_t mk[2] = {0xFFFFFFFFu, 0xFFFFFFFFu};   // visibility of this key for the unit's 64 queries
+      uint32_t mk = 0xFFFFFFFFu;   // visibility of this key for the slice's 32 queries
       if (cls == KD_TILE_PARTIAL) {
-        key_row_mask<2>(kdesc, kj, i0, tb_pre + 0, tb_pre + 2, tb_pre + 4, tb_pre + 6, mk);
-        if ((tb_pre[8] | tb_pre[9]) != 0u && __any_sync(0xffffffffu, (kdesc & TD_INS) != 0u)) {
+        key_row_mask<1>(kdesc, kj, i0, tb_pre + 0, tb_pre + 1, tb_pre + 2, tb_pre + 3, &mk);
+        if (tb_pre[4] != 0u && __any_sync(0xffffffffu, (kdesc & TD_INS) != 0u)) {
           const uint32_t key = span_key_of_key(kdesc);
 #pragma unroll
-          for (int j = 0; j < 64; j += 4) {
-            const uint4 q4 = *reinterpret_cast<const uint4*>(st_buf + 128 + j);
-            mk[j >> 5] |= (span_match_query(key, q4.x) << ((j + 0) & 31)) | (span_match_query(key, q4.y) << ((j + 1) & 31)) |
-                          (span_match_query(key, q4.z) << ((j + 2) & 31)) | (span_match_query(key, q4.w) << ((j + 3) & 31));
+          for (int j = 0; j < 32; j += 4) {
+            const uint4 q4 = *reinterpret_cast<const uint4*>(st_buf + 64 + j);
+            mk |= (span_match_query(key, q4.x) << (j + 0)) | (span_match_query(key, q4.y) << (j + 1)) |
+                  (span_match_query(key, q4.z) << (j + 2)) | (span_match_query(key, q4.w) << (j + 3));
           }
         }
       }
       prefetch(e + 1);
       const int u = 2 * e + i, buf = u % C::NBUF;
-      const uint32_t tS = tbase + lane_base + buf * 128, tP = tS + 64;
+      const uint32_t tS = tbase + lane_base + buf * 128 + sub * 32, tP = tS + 64;
       tr.ev(21);
       ok = mbar_wait(smem_u32(&bar_s_full[buf]), (u / C::NBUF) & 1, &abortf, a.status, W_K_SFULL);
       ok = __all_sync(0xffffffffu, ok);
@@ -669,18 +669,16 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tc_fence_after_sync();
       tr.ev(22);
 
-      uint32_t pk_p[32], pk_ds[32];
-#pragma unroll
-      for (int cb = 0; cb < 2; ++cb) {
+      uint32_t pk_p[16], pk_ds[16];
+      {
         uint32_t rs[32], rp[32];
-        tmem_ld32(tS + cb * 32, rs);
-        tmem_ld32(tP + cb * 32, rp);
+        tmem_ld32(tS, rs);
+        tmem_ld32(tP, rp);
         tmem_wait_ld();
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const int j = g * 4;
-          const float4 l4 = *reinterpret_cast<const float4*>(st_buf + cb * 32 + j);        // -LSE of 4 queries
-          const float4 d4 = *reinterpret_cast<const float4*>(st_buf + 64 + cb * 32 + j);   // delta of 4 queries
+        for (int j = 0; j < 32; j += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(st_buf + j);        // -LSE of 4 queries
+          const float4 d4 = *reinterpret_cast<const float4*>(st_buf + 32 + j);   // delta of 4 queries
           const float lw[4] = {l4.x, l4.y, l4.z, l4.w}, dw[4] = {d4.x, d4.y, d4.z, d4.w};
           float pv[4], ds[4];
 #pragma unroll
@@ -688,26 +686,26 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           if (cls == KD_TILE_PARTIAL) {
 #pragma unroll
             for (int u2 = 0; u2 < 4; ++u2)
-              if ((mk[cb] & (1u << (j + u2))) == 0u) pv[u2] = 0.f;
+              if ((mk & (1u << (j + u2))) == 0u) pv[u2] = 0.f;
           }
 #pragma unroll
           for (int u2 = 0; u2 < 4; ++u2) ds[u2] = pv[u2] * (__uint_as_float(rp[j + u2]) - dw[u2]);
-          pk_p[cb * 16 + j / 2] = pack2<kBf16>(pv[0], pv[1]);
-          pk_p[cb * 16 + j / 2 + 1] = pack2<kBf16>(pv[2], pv[3]);
-          pk_ds[cb * 16 + j / 2] = pack2<kBf16>(ds[0], ds[1]);
-          pk_ds[cb * 16 + j / 2 + 1] = pack2<kBf16>(ds[2], ds[3]);
+          pk_p[j / 2] = pack2<kBf16>(pv[0], pv[1]);
+          pk_p[j / 2 + 1] = pack2<kBf16>(pv[2], pv[3]);
+          pk_ds[j / 2] = pack2<kBf16>(ds[0], ds[1]);
+          pk_ds[j / 2 + 1] = pack2<kBf16>(ds[2], ds[3]);
         }
       }
       tr.ev(24);
-      tmem_st32(tS, pk_p);    // P^T_u on top of S^T_u
-      tmem_st32(tP, pk_ds);   // dS^T_u on top of dP^T_u
+      tmem_st16(tS, pk_p);    // P^T of this slice over the scores it was made from
+      tmem_st16(tP, pk_ds);   // dS^T of this slice over its dP^T
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&bar_p_full[buf]));
       tr.ev(25);
     }
 
-    // epilogue: this warpgroup stores columns [i*HD/2, (i+1)*HD/2) of dK and dV
+    // epilogue: warpgroup g stores columns [g*HD/4, (g+1)*HD/4) of dK and dV
     if (ok && n > 0) {
       ok = mbar_wait(smem_u32(&bar_acc_full), 0, &abortf, a.status, W_K_ACCFULL);
       ok = __all_sync(0xffffffffu, ok);
@@ -715,22 +713,30 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     tr.ev(30);
     if (ok) {
       tc_fence_after_sync();
-      uint16_t* krow = reinterpret_cast<uint16_t*>(a.dk) + (size_t)b * a.dk_sb + (size_t)h * a.dk_sh + (size_t)kj * a.dk_st + i * (HD / 2);
-      uint16_t* vrow = reinterpret_cast<uint16_t*>(a.dv) + (size_t)b * a.dv_sb + (size_t)h * a.dv_sh + (size_t)kj * a.dv_st + i * (HD / 2);
-#pragma unroll
-      for (int cb = 0; cb < HD / 64; ++cb) {
-        uint32_t rk[32], rv[32];
-        if (n > 0) {
-          tmem_ld32(tbase + lane_base + C::TM_ACC0 + i * (HD / 2) + cb * 32, rk);
-          tmem_ld32(tbase + lane_base + C::TM_ACC1 + i * (HD / 2) + cb * 32, rv);
-          tmem_wait_ld();
+      constexpr int EC = HD / 4;
+      uint16_t* krow = reinterpret_cast<uint16_t*>(a.dk) + (size_t)b * a.dk_sb + (size_t)h * a.dk_sh + (size_t)kj * a.dk_st + g * EC;
+      uint16_t* vrow = reinterpret_cast<uint16_t*>(a.dv) + (size_t)b * a.dv_sb + (size_t)h * a.dv_sh + (size_t)kj * a.dv_st + g * EC;
+      uint32_t rk[EC], rv[EC];
+      if (n > 0) {
+        if constexpr (EC == 16) {
+          tmem_ld16(tbase + lane_base + C::TM_ACC0 + g * EC, rk);
+          tmem_ld16(tbase + lane_base + C::TM_ACC1 + g * EC, rv);
         } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) { rk[j] = 0u; rv[j] = 0u; }
+          tmem_ld32(tbase + lane_base + C::TM_ACC0 + g * EC, rk);
+          tmem_ld32(tbase + lane_base + C::TM_ACC1 + g * EC, rv);
         }
-        if (k_valid) {
-          store_row32<kBf16>(krow + cb * 32, rk, a.sm_scale);
-          store_row32<kBf16>(vrow + cb * 32, rv, 1.0f);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int j = 0; j < EC; ++j) { rk[j] = 0u; rv[j] = 0u; }
+      }
+      if (k_valid) {
+        if constexpr (EC == 16) {
+          store_row16<kBf16>(krow, rk, a.sm_scale);
+          store_row16<kBf16>(vrow, rv, 1.0f);
+        } else {
+          store_row32<kBf16>(krow, rk, a.sm_scale);
+          store_row32<kBf16>(vrow, rv, 1.0f);
         }
       }
     }
@@ -740,6 +746,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tbase, 512);
+  cta_trace(a.trace, 3);
 }
 
 template <int HD, bool kBf16>
@@ -776,9 +783,9 @@ static int launch_bwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
     const int rows_per_block = 256 / (HD / 8);
     const int blocks = static_cast<int>(std::min<size_t>((rows + rows_per_block - 1) / rows_per_block, size_t(148) * 32));
     attn_bwd_delta_kernel<HD, kBf16><<<blocks, 256, 0, stream>>>(a);
-    kq<<<grid, 384, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
+    kq<<<grid, 640, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
   }
-  if (phases & 2) kk<<<grid, 384, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
+  if (phases & 2) kk<<<grid, 640, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "attn_bwd kernels launch: %s", cudaGetErrorString(e));
   return 0;

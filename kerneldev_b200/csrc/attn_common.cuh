@@ -16,6 +16,11 @@
 #ifndef KD_REGS_COMPUTE
 #define KD_REGS_COMPUTE 224
 #endif
+// The backward kernels run sixteen compute warps (640 threads, 96 registers each at launch):
+// 4*32*(96 - ISSUE) released registers cover 16*32*(COMPUTE_BWD - 96).
+#ifndef KD_REGS_COMPUTE_BWD
+#define KD_REGS_COMPUTE_BWD 104
+#endif
 
 namespace kd {
 
@@ -66,6 +71,19 @@ template <bool kBf16>
 __device__ __forceinline__ void store_row32(uint16_t* dst, const uint32_t (&r)[32], float f) {
 #pragma unroll
   for (int j = 0; j < 32; j += 8) {
+    uint4 v;
+    v.x = pack2<kBf16>(__uint_as_float(r[j + 0]) * f, __uint_as_float(r[j + 1]) * f);
+    v.y = pack2<kBf16>(__uint_as_float(r[j + 2]) * f, __uint_as_float(r[j + 3]) * f);
+    v.z = pack2<kBf16>(__uint_as_float(r[j + 4]) * f, __uint_as_float(r[j + 5]) * f);
+    v.w = pack2<kBf16>(__uint_as_float(r[j + 6]) * f, __uint_as_float(r[j + 7]) * f);
+    *reinterpret_cast<uint4*>(dst + j) = v;
+  }
+}
+
+template <bool kBf16>
+__device__ __forceinline__ void store_row16(uint16_t* dst, const uint32_t (&r)[16], float f) {
+#pragma unroll
+  for (int j = 0; j < 16; j += 8) {
     uint4 v;
     v.x = pack2<kBf16>(__uint_as_float(r[j + 0]) * f, __uint_as_float(r[j + 1]) * f);
     v.y = pack2<kBf16>(__uint_as_float(r[j + 2]) * f, __uint_as_float(r[j + 3]) * f);

@@ -363,11 +363,24 @@ struct Tracer {
     }
   }
 };
+// per-CTA record behind the per-role timelines: {SM id, globaltimer at three points of the kernel}
+#ifndef KD_TRACE_CTA_BASE
+#define KD_TRACE_CTA_BASE (256 * KD_TRACE_SLOTS)
+#endif
+__device__ __forceinline__ void cta_trace(unsigned long long* base, int slot) {
+  if (base && threadIdx.x == 0) {
+    const size_t cta = blockIdx.x + (size_t)gridDim.x * (blockIdx.y + (size_t)gridDim.y * blockIdx.z);
+    unsigned long long* p = base + KD_TRACE_CTA_BASE + cta * 4;
+    if (slot == 1) { uint32_t sm; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm)); p[0] = sm; }
+    p[slot] = globaltimer_ns();
+  }
+}
 #else
 struct Tracer {
   __device__ __forceinline__ void init(unsigned long long*, bool, int) {}
   __device__ __forceinline__ void ev(uint32_t) {}
 };
+__device__ __forceinline__ void cta_trace(unsigned long long*, int) {}
 #endif
 
 template <uint32_t kRegs>
