@@ -30,6 +30,7 @@ namespace kd {
 
 struct BwdArgs {
   int B, H, T, NT, NP, Tpad;
+  int G;             // heads per CTA
   float scale_log2;  // sm_scale * log2(e)
   float sm_scale;
   const uint32_t* desc;
@@ -59,10 +60,14 @@ template <int HD>
 struct BwdCfg {
   static constexpr int KBLK = HD / 64;
   static constexpr int TILE_BYTES = KD_TILE * HD * 2;
-  static constexpr int NBUF = (HD == 64) ? 3 : 2;     // score / dP buffers in TMEM
+#ifndef KD_BWD_NBUF
+#define KD_BWD_NBUF 3
+#endif
+  static constexpr int NBUF = (HD == 64) ? KD_BWD_NBUF : 2;     // score / dP buffers in TMEM
   static constexpr int STAGES = NBUF;                 // ring of (tile, tile) pairs
-  static constexpr int SMEM_FIX = 0;                               // two resident tiles
-  static constexpr int SMEM_RING = SMEM_FIX + 2 * TILE_BYTES;      // STAGES x two streamed tiles
+  static constexpr int NFIX = (HD == 64) ? 2 : 1;     // buffers for the per-head resident tile pair
+  static constexpr int SMEM_FIX = 0;                               // NFIX x two resident tiles
+  static constexpr int SMEM_RING = SMEM_FIX + NFIX * 2 * TILE_BYTES;  // STAGES x two streamed tiles
   static constexpr int SMEM_STAGE = SMEM_RING + STAGES * 2 * TILE_BYTES;  // per-warp staging
   static constexpr int STAGE_WORDS = 3 * 32;                       // 32 x {-lse, delta, descriptor}
   static constexpr int SMEM_ACT = SMEM_STAGE + 16 * STAGE_WORDS * 4;  // compacted entry list
@@ -78,9 +83,9 @@ struct BwdCfg {
 
 enum : uint32_t {
   W_Q_FIXFULL = 0x201, W_Q_RINGEMPTY = 0x202, W_Q_RINGFULL = 0x203, W_Q_PFULL = 0x204, W_Q_SFULL = 0x205,
-  W_Q_ACCFULL = 0x206, W_Q_M2ISSUED = 0x207,
+  W_Q_ACCFULL = 0x206, W_Q_M2ISSUED = 0x207, W_Q_FIXEMPTY = 0x208, W_Q_ACCFREE = 0x209,
   W_K_FIXFULL = 0x301, W_K_RINGEMPTY = 0x302, W_K_RINGFULL = 0x303, W_K_PFULL = 0x304, W_K_SFULL = 0x305,
-  W_K_ACCFULL = 0x306, W_K_M2ISSUED = 0x307,
+  W_K_ACCFULL = 0x306, W_K_M2ISSUED = 0x307, W_K_FIXEMPTY = 0x308, W_K_ACCFREE = 0x309,
 };
 
 // =========================================================================================
@@ -120,8 +125,11 @@ __global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const BwdArgs a) {
 }
 
 // =========================================================================================
-// dQ kernel: one CTA per (b, h, query tile); streams = key halves of the current key tile.
-//   M1(i): S_i = Q K_i^T, dP_i = dO V_i^T      M2(i): dQ += dS_i K_i
+// dQ kernel: one CTA per (b, group of heads, query tile); streams = key halves of the current key
+// tile.   M1(i): S_i = Q K_i^T, dP_i = dO V_i^T      M2(i): dQ += dS_i K_i
+// The heads of the group are handled one after the other: they share the work list, the barriers
+// and the TMEM allocation, and the producer and the issuers run on into the next head while the
+// compute warps finish the current one, so the pipeline fill and drain are paid once per CTA.
 // =========================================================================================
 template <int HD, bool kBf16>
 __global__ void __launch_bounds__(640, 1)
@@ -131,27 +139,30 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   using C = BwdCfg<HD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const uint32_t sQ = smem_u32(smem + C::SMEM_FIX);
-  const uint32_t sDO = sQ + C::TILE_BYTES;
+  const uint32_t sFix = smem_u32(smem + C::SMEM_FIX);    // buffer f: Q at +0, dO at +TILE_BYTES
   const uint32_t sRing = smem_u32(smem + C::SMEM_RING);  // stage s: K at +0, V at +TILE_BYTES
   uint32_t* sStage = reinterpret_cast<uint32_t*>(smem + C::SMEM_STAGE);
   uint16_t* sAct = reinterpret_cast<uint16_t*>(smem + C::SMEM_ACT);
 
-  __shared__ __align__(8) uint64_t bar_fix_full, bar_ring_full[C::STAGES], bar_ring_empty[C::STAGES],
-      bar_s_full[C::NBUF], bar_p_full[C::NBUF], bar_m2_issued[C::NBUF], bar_acc_full;
+  __shared__ __align__(8) uint64_t bar_fix_full[C::NFIX], bar_fix_empty[C::NFIX], bar_ring_full[C::STAGES],
+      bar_ring_empty[C::STAGES], bar_s_full[C::NBUF], bar_p_full[C::NBUF], bar_m2_issued[C::NBUF], bar_acc_full, bar_acc_free;
   __shared__ uint32_t tmem_base_s;
   __shared__ int n_act_s;
   __shared__ AbortFlag abortf;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   cta_trace(a.trace, 1);
-  const int h = blockIdx.x, b = blockIdx.y;
+  const int h0 = blockIdx.x * a.G, b = blockIdx.y;
+  const int nh = min(a.G, a.H - h0);   // this CTA handles heads h0 .. h0 + nh - 1
   const int qt = a.order[((size_t)b * 3 + 1) * a.NT + blockIdx.z];   // longest lists first
   const int pair = qt >> 1, ip = qt & 1;
 
   if (tid == 0) {
     abortf.v = 0;
-    mbar_init(smem_u32(&bar_fix_full), 1);
+    for (int f = 0; f < C::NFIX; ++f) {
+      mbar_init(smem_u32(&bar_fix_full[f]), 1);
+      mbar_init(smem_u32(&bar_fix_empty[f]), 2);  // both M1 issuers are done with the head's Q and dO
+    }
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(smem_u32(&bar_ring_full[s]), 1);
       mbar_init(smem_u32(&bar_ring_empty[s]), 1);
@@ -162,6 +173,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_init(smem_u32(&bar_m2_issued[i]), 1);
     }
     mbar_init(smem_u32(&bar_acc_full), 1);
+    mbar_init(smem_u32(&bar_acc_free), 512);      // every compute thread has read its part of dQ
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -189,8 +201,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t tbase = tmem_base_s;
   const int na = n_act_s;
   Tracer tr;
-  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 3 || warp == 1 || warp == 4 || warp == 8),
-          blockIdx.z * 4 + (warp == 3 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));
+  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 3 || warp == 1 || warp == 4 || warp == 12),
+          blockIdx.z * 4 + (warp == 3 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));   // issuers and one warp of each stream
   tr.ev(1);
   cta_trace(a.trace, 2);
 
@@ -202,67 +214,79 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
       tma_prefetch_desc(&tmDO);
-      mbar_arrive_expect_tx(smem_u32(&bar_fix_full), 2 * C::TILE_BYTES);
-      for (int kb = 0; kb < C::KBLK; ++kb) {
-        tma_load_4d(sQ + kb * 16384, &tmQ, smem_u32(&bar_fix_full), kb * 64, qt * KD_TILE, h, b);
-        tma_load_4d(sDO + kb * 16384, &tmDO, smem_u32(&bar_fix_full), kb * 64, qt * KD_TILE, h, b);
-      }
-      int issued = 0;
-      for (int e = 0; e < na; ++e) {
-        const int s = e % C::STAGES;
-        const uint32_t ph = (e / C::STAGES) & 1;
-        const int kt = sAct[e] & 0xFF;
-        if (!mbar_wait(smem_u32(&bar_ring_empty[s]), ph ^ 1, &abortf, a.status, W_Q_RINGEMPTY)) break;
-        mbar_arrive_expect_tx(smem_u32(&bar_ring_full[s]), 2 * C::TILE_BYTES);
-        const uint32_t dst = sRing + s * 2 * C::TILE_BYTES;
-        for (int kb = 0; kb < C::KBLK; ++kb) {
-          tma_load_4d(dst + kb * 16384, &tmK, smem_u32(&bar_ring_full[s]), kb * 64, kt * KD_TILE, h, b);
-          tma_load_4d(dst + C::TILE_BYTES + kb * 16384, &tmV, smem_u32(&bar_ring_full[s]), kb * 64, kt * KD_TILE, h, b);
+      int issued = 0, fix_issued = 0;   // ring entries / resident pairs requested so far, over all heads
+      bool ok = true;
+      for (int hh = 0; hh < nh && ok; ++hh) {
+        const int h = h0 + hh, fb = hh % C::NFIX;
+        if (hh >= C::NFIX) {   // the buffer's previous head must have been consumed by both M1 issuers
+          ok = mbar_wait(smem_u32(&bar_fix_empty[fb]), (hh / C::NFIX - 1) & 1, &abortf, a.status, W_Q_FIXEMPTY);
+          if (!ok) break;
         }
-        issued = e + 1;
+        mbar_arrive_expect_tx(smem_u32(&bar_fix_full[fb]), 2 * C::TILE_BYTES);
+        for (int kb = 0; kb < C::KBLK; ++kb) {
+          tma_load_4d(sFix + fb * 2 * C::TILE_BYTES + kb * 16384, &tmQ, smem_u32(&bar_fix_full[fb]), kb * 64, qt * KD_TILE, h, b);
+          tma_load_4d(sFix + fb * 2 * C::TILE_BYTES + C::TILE_BYTES + kb * 16384, &tmDO, smem_u32(&bar_fix_full[fb]), kb * 64, qt * KD_TILE, h, b);
+        }
+        fix_issued = hh + 1;
+        for (int e = 0; e < na; ++e) {
+          const int s = issued % C::STAGES;
+          const uint32_t ph = (issued / C::STAGES) & 1;
+          const int kt = sAct[e] & 0xFF;
+          ok = mbar_wait(smem_u32(&bar_ring_empty[s]), ph ^ 1, &abortf, a.status, W_Q_RINGEMPTY);
+          if (!ok) break;
+          mbar_arrive_expect_tx(smem_u32(&bar_ring_full[s]), 2 * C::TILE_BYTES);
+          const uint32_t dst = sRing + s * 2 * C::TILE_BYTES;
+          for (int kb = 0; kb < C::KBLK; ++kb) {
+            tma_load_4d(dst + kb * 16384, &tmK, smem_u32(&bar_ring_full[s]), kb * 64, kt * KD_TILE, h, b);
+            tma_load_4d(dst + C::TILE_BYTES + kb * 16384, &tmV, smem_u32(&bar_ring_full[s]), kb * 64, kt * KD_TILE, h, b);
+          }
+          ++issued;
+        }
       }
-      if (abortf.v != 0) {
+      if (abortf.v != 0) {   // let the copies in flight land before the CTA exits
         for (int e = max(0, issued - C::STAGES); e < issued; ++e)
           for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_ring_full[e % C::STAGES]), (e / C::STAGES) & 1); ++spin) {}
-        for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_fix_full), 0); ++spin) {}
+        for (int f = max(0, fix_issued - C::NFIX); f < fix_issued; ++f)
+          for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_fix_full[f % C::NFIX]), (f / C::NFIX) & 1); ++spin) {}
       }
     } else if ((warp == 3 || warp == 2) && lane == 0 && na > 0) {
       // ------------------------------ M1 issuers: warp 3: S_u = Q K_u^T; warp 2: dP_u = dO V_u^T ------------------------------
       const bool dp_part = (warp == 2);
       const uint32_t idesc_m1 = make_idesc_f16(kBf16, 0, 0, KD_TILE, 64);   // N = 64 keys
       const uint32_t hi = desc_hi_sw128();
-      const uint32_t loQ = desc_lo_kmajor(sQ), loDO = desc_lo_kmajor(sDO), loRingK = desc_lo_kmajor(sRing);
+      const uint32_t loRingK = desc_lo_kmajor(sRing);
       const int U = 2 * na;
-      bool ok = mbar_wait(smem_u32(&bar_fix_full), 0, &abortf, a.status, W_Q_FIXFULL);
-      int buf = 0, round = 0, stage = 0;
+      bool ok = true;
+      int buf = 0, round = 0, stage = 0;   // run on across the heads
       uint32_t ring_parity = 0;
-      for (int u = 0; u < U && ok; ++u) {
-        const int i = u & 1;
-        if (round > 0) {   // buffer free once M2 of its previous unit has been issued
-          ok = mbar_wait(smem_u32(&bar_m2_issued[buf]), (round - 1) & 1, &abortf, a.status, W_Q_M2ISSUED);
-          if (!ok) break;
-        }
-        if (i == 0) {      // first unit of a new entry: its K and V tiles must have landed
-          ok = mbar_wait(smem_u32(&bar_ring_full[stage]), ring_parity, &abortf, a.status, W_Q_RINGFULL);
-          if (!ok) break;
-        }
-        tc_fence_after_sync();
-        const uint32_t kb = loRingK + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);  // key rows 64i..
-        const uint32_t vb = kb + (C::TILE_BYTES >> 4);
-        const uint32_t dS = tbase + buf * 128, dP = dS + 64;
-        if (!dp_part) {
+      for (int hh = 0; hh < nh && ok; ++hh) {
+        const int fb = hh % C::NFIX;
+        ok = mbar_wait(smem_u32(&bar_fix_full[fb]), (hh / C::NFIX) & 1, &abortf, a.status, W_Q_FIXFULL);
+        if (!ok) break;
+        const uint32_t loA = desc_lo_kmajor(sFix + fb * 2 * C::TILE_BYTES + (dp_part ? C::TILE_BYTES : 0));   // dO or Q
+        for (int u = 0; u < U && ok; ++u) {
+          const int i = u & 1;
+          if (round > 0) {   // buffer free once M2 of its previous unit has been issued
+            ok = mbar_wait(smem_u32(&bar_m2_issued[buf]), (round - 1) & 1, &abortf, a.status, W_Q_M2ISSUED);
+            if (!ok) break;
+          }
+          if (i == 0) {      // first unit of a new entry: its K and V tiles must have landed
+            ok = mbar_wait(smem_u32(&bar_ring_full[stage]), ring_parity, &abortf, a.status, W_Q_RINGFULL);
+            if (!ok) break;
+          }
+          tc_fence_after_sync();
+          // key rows 64i.. of K (scores) or V (dP)
+          const uint32_t bdesc = loRingK + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4) + (dp_part ? (C::TILE_BYTES >> 4) : 0);
+          const uint32_t dst = tbase + buf * 128 + (dp_part ? 64 : 0);
 #pragma unroll
           for (int kk = 0; kk < HD / 16; ++kk)
-            mma_ss_split(dS, loQ + koff_kmajor(kk), kb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
-        } else {
-#pragma unroll
-          for (int kk = 0; kk < HD / 16; ++kk)
-            mma_ss_split(dP, loDO + koff_kmajor(kk), vb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
+            mma_ss_split(dst, loA + koff_kmajor(kk), bdesc + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
+          mma_commit(smem_u32(&bar_s_full[buf]));
+          tr.ev(15);
+          if (++buf == C::NBUF) { buf = 0; ++round; }
+          if (i == 1 && ++stage == C::STAGES) { stage = 0; ring_parity ^= 1; }
         }
-        mma_commit(smem_u32(&bar_s_full[buf]));
-        tr.ev(15);
-        if (++buf == C::NBUF) { buf = 0; ++round; }
-        if (i == 1 && ++stage == C::STAGES) { stage = 0; ring_parity ^= 1; }
+        if (ok) mma_commit(smem_u32(&bar_fix_empty[fb]));   // this issuer's products of the head no longer read Q / dO
       }
     } else if (warp == 1 && lane == 0 && na > 0) {
       // ------------------------------ M2 issuer: dQ += dS_u K_u ------------------------------
@@ -274,25 +298,31 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       bool ok = true;
       int buf = 0, stage = 0;
       uint32_t round_parity = 0;
-      for (int u = 0; u < U && ok; ++u) {
-        const int i = u & 1;
-        ok = mbar_wait(smem_u32(&bar_p_full[buf]), round_parity, &abortf, a.status, W_Q_PFULL);
-        if (!ok) break;
-        tr.ev(10);
-        tc_fence_after_sync();
-        const uint32_t kb = loRingMN + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
-        const uint32_t aS = tbase + buf * 128;   // dS_u sits on top of S_u: keys 0-31 at columns [0,16), keys 32-63 at [32,48)
+      for (int hh = 0; hh < nh && ok; ++hh) {
+        if (hh > 0) {   // the previous head's dQ must have been read out of the accumulator
+          ok = mbar_wait(smem_u32(&bar_acc_free), (hh - 1) & 1, &abortf, a.status, W_Q_ACCFREE);
+          if (!ok) break;
+        }
+        for (int u = 0; u < U && ok; ++u) {
+          const int i = u & 1;
+          ok = mbar_wait(smem_u32(&bar_p_full[buf]), round_parity, &abortf, a.status, W_Q_PFULL);
+          if (!ok) break;
+          tr.ev(10);
+          tc_fence_after_sync();
+          const uint32_t kb = loRingMN + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
+          const uint32_t aS = tbase + buf * 128;   // dS_u sits on top of S_u: keys 0-31 at columns [0,16), keys 32-63 at [32,48)
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)  // 64 keys of this unit, 16 per MMA
-          mma_ts_split(tAcc, aS + (kk >> 1) * 32 + (kk & 1) * 8, kb + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
-        if (i == 1) mma_commit(smem_u32(&bar_ring_empty[stage]));
-        tc_fence_before_sync();
-        mbar_arrive(smem_u32(&bar_m2_issued[buf]));
-        tr.ev(11);
-        if (++buf == C::NBUF) { buf = 0; round_parity ^= 1; }
-        if (i == 1 && ++stage == C::STAGES) stage = 0;
+          for (int kk = 0; kk < 4; ++kk)  // 64 keys of this unit, 16 per MMA
+            mma_ts_split(tAcc, aS + (kk >> 1) * 32 + (kk & 1) * 8, kb + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
+          if (i == 1) mma_commit(smem_u32(&bar_ring_empty[stage]));
+          tc_fence_before_sync();
+          mbar_arrive(smem_u32(&bar_m2_issued[buf]));
+          tr.ev(11);
+          if (++buf == C::NBUF) { buf = 0; round_parity ^= 1; }
+          if (i == 1 && ++stage == C::STAGES) stage = 0;
+        }
+        if (ok) mma_commit(smem_u32(&bar_acc_full));
       }
-      if (ok) mma_commit(smem_u32(&bar_acc_full));
     }
   } else {
     reg_alloc<KD_REGS_COMPUTE_BWD>();
@@ -307,9 +337,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
     uint32_t* kd_buf = sStage + (size_t)(warp - 4) * C::STAGE_WORDS;
     const float c = a.scale_log2;
-    const size_t bh = (size_t)b * a.H + h;
-    const float delta = q_valid ? a.delta[bh * a.T + qi] : 0.f;
-    const float neg_lse = q_valid ? -a.lse[bh * a.T + qi] : 0.f;
     const uint32_t qd = a.desc[(size_t)b * a.Tpad + qi];
     const int tbw = 2 * i + sub;     // this slice's word in the 128-bit class masks of a key tile
     bool ok = true;
@@ -318,7 +345,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     uint32_t kd_pre = 0u;
     uint32_t tb_pre[3] = {0u, 0u, 0u};   // key-side class masks of this slice: is_prefix, context, in_span
     auto prefetch_kd = [&](int e) {
-      if (e < na && (sAct[e] >> 8) == KD_TILE_PARTIAL) {
+      if ((sAct[e] >> 8) == KD_TILE_PARTIAL) {
         const uint32_t ktile = sAct[e] & 0xFFu;
         kd_pre = a.desc[(size_t)b * a.Tpad + (size_t)ktile * KD_TILE + i * 64 + sub * 32 + lane];
         const uint32_t* tbp = a.tilebits + ((size_t)b * a.NT + ktile) * 32;
@@ -327,76 +354,90 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tb_pre[2] = tbp[4 * TB_INS + tbw];
       }
     };
-    prefetch_kd(0);
+    if (na > 0) prefetch_kd(0);
+    // per-row scalars of the next head are fetched while the current head is processed
+    float nxt_delta = q_valid ? a.delta[((size_t)b * a.H + h0) * a.T + qi] : 0.f;
+    float nxt_lse = q_valid ? a.lse[((size_t)b * a.H + h0) * a.T + qi] : 0.f;
+    int ug = i;   // this stream's next unit, counted over all heads
 
-    for (int e = 0; e < na; ++e) {
-      const uint32_t ent = sAct[e];
-      const uint32_t cls = ent >> 8;
-      const int kt = ent & 0xFF;
-      const int j0 = kt * KD_TILE + i * 64 + sub * 32;  // first key of this slice
-      uint32_t mk = 0xFFFFFFFFu;   // visibility of this slice's 32 keys for this query row
-      if (cls == KD_TILE_PARTIAL) {
-        __syncwarp();
-        kd_buf[lane] = kd_pre;
-        __syncwarp();
-        query_row_mask<1>(qd, qi, j0, tb_pre + 0, tb_pre + 1, tb_pre + 2, &mk);
-        if (tb_pre[2] != 0u && __any_sync(0xffffffffu, (qd & TD_SIDPOS) != 0u)) {
-          const uint32_t key = span_key_of_query(qd);
+    for (int hh = 0; hh < nh && ok; ++hh) {
+      const int h = h0 + hh;
+      const float delta = nxt_delta, neg_lse = -nxt_lse;
+      if (hh + 1 < nh && q_valid) {
+        nxt_delta = a.delta[((size_t)b * a.H + h + 1) * a.T + qi];
+        nxt_lse = a.lse[((size_t)b * a.H + h + 1) * a.T + qi];
+      }
+      for (int e = 0; e < na; ++e, ug += 2) {
+        const uint32_t ent = sAct[e];
+        const uint32_t cls = ent >> 8;
+        const int kt = ent & 0xFF;
+        const int j0 = kt * KD_TILE + i * 64 + sub * 32;  // first key of this slice
+        uint32_t mk = 0xFFFFFFFFu;   // visibility of this slice's 32 keys for this query row
+        if (cls == KD_TILE_PARTIAL) {
+          __syncwarp();
+          kd_buf[lane] = kd_pre;
+          __syncwarp();
+          query_row_mask<1>(qd, qi, j0, tb_pre + 0, tb_pre + 1, tb_pre + 2, &mk);
+          if (tb_pre[2] != 0u && __any_sync(0xffffffffu, (qd & TD_SIDPOS) != 0u)) {
+            const uint32_t key = span_key_of_query(qd);
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            const uint4 k4 = *reinterpret_cast<const uint4*>(kd_buf + j);
-            mk |= (span_match_key(key, k4.x) << (j + 0)) | (span_match_key(key, k4.y) << (j + 1)) |
-                  (span_match_key(key, k4.z) << (j + 2)) | (span_match_key(key, k4.w) << (j + 3));
+            for (int j = 0; j < 32; j += 4) {
+              const uint4 k4 = *reinterpret_cast<const uint4*>(kd_buf + j);
+              mk |= (span_match_key(key, k4.x) << (j + 0)) | (span_match_key(key, k4.y) << (j + 1)) |
+                    (span_match_key(key, k4.z) << (j + 2)) | (span_match_key(key, k4.w) << (j + 3));
+            }
           }
         }
+        if (e + 1 < na) prefetch_kd(e + 1);
+        else if (hh + 1 < nh) prefetch_kd(0);   // the next head walks the same list again
+        const int buf = ug % C::NBUF;
+        const uint32_t tS = tbase + lane_base + buf * 128 + sub * 32, tP = tS + 64;
+        tr.ev(21);
+        ok = mbar_wait(smem_u32(&bar_s_full[buf]), (ug / C::NBUF) & 1, &abortf, a.status, W_Q_SFULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+        tr.ev(22);
+
+        uint32_t pk[16];
+        {
+          uint32_t rs[32], rp[32];
+          tmem_ld32(tS, rs);
+          tmem_ld32(tP, rp);
+          tmem_wait_ld();
+          if (cls != KD_TILE_PARTIAL) {   // warp-uniform: the common case carries no mask code at all
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              const float p0 = fast_exp2(fmaf(__uint_as_float(rs[j]), c, neg_lse));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(rs[j + 1]), c, neg_lse));
+              pk[j / 2] = pack2<kBf16>(p0 * (__uint_as_float(rp[j]) - delta), p1 * (__uint_as_float(rp[j + 1]) - delta));
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              float p0 = fast_exp2(fmaf(__uint_as_float(rs[j]), c, neg_lse));
+              float p1 = fast_exp2(fmaf(__uint_as_float(rs[j + 1]), c, neg_lse));
+              if ((mk & (1u << j)) == 0u) p0 = 0.f;
+              if ((mk & (2u << j)) == 0u) p1 = 0.f;
+              pk[j / 2] = pack2<kBf16>(p0 * (__uint_as_float(rp[j]) - delta), p1 * (__uint_as_float(rp[j + 1]) - delta));
+            }
+          }
+        }
+        tr.ev(24);
+        tmem_st16(tS, pk);   // dS of this slice as 16-bit A operand over the scores it was made from (this thread's own row)
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(&bar_p_full[buf]));
+        tr.ev(25);
       }
-      prefetch_kd(e + 1);
-      const int u = 2 * e + i, buf = u % C::NBUF;
-      const uint32_t tS = tbase + lane_base + buf * 128 + sub * 32, tP = tS + 64;
-      tr.ev(21);
-      ok = mbar_wait(smem_u32(&bar_s_full[buf]), (u / C::NBUF) & 1, &abortf, a.status, W_Q_SFULL);
-      ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      tc_fence_after_sync();
-      tr.ev(22);
 
-      uint32_t pk[16];
-      {
-        uint32_t rs[32], rp[32];
-        tmem_ld32(tS, rs);
-        tmem_ld32(tP, rp);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          float pv[4];
-#pragma unroll
-          for (int u2 = 0; u2 < 4; ++u2) pv[u2] = fast_exp2(fmaf(__uint_as_float(rs[j + u2]), c, neg_lse));
-          if (cls == KD_TILE_PARTIAL) {
-#pragma unroll
-            for (int u2 = 0; u2 < 4; ++u2)
-              if ((mk & (1u << (j + u2))) == 0u) pv[u2] = 0.f;
-          }
-          float ds[4];
-#pragma unroll
-          for (int u2 = 0; u2 < 4; ++u2) ds[u2] = pv[u2] * (__uint_as_float(rp[j + u2]) - delta);
-          pk[j / 2] = pack2<kBf16>(ds[0], ds[1]);
-          pk[j / 2 + 1] = pack2<kBf16>(ds[2], ds[3]);
-        }
+      // epilogue of this head: warpgroup g stores columns [g*HD/4, (g+1)*HD/4) of dQ
+      if (na > 0) {
+        ok = mbar_wait(smem_u32(&bar_acc_full), hh & 1, &abortf, a.status, W_Q_ACCFULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
       }
-      tr.ev(24);
-      tmem_st16(tS, pk);   // dS of this slice as 16-bit A operand over the scores it was made from (this thread's own row)
-      tmem_wait_st();
-      tc_fence_before_sync();
-      mbar_arrive(smem_u32(&bar_p_full[buf]));
-      tr.ev(25);
-    }
-
-    // epilogue: warpgroup g stores columns [g*HD/4, (g+1)*HD/4) of dQ
-    if (ok && na > 0) {
-      ok = mbar_wait(smem_u32(&bar_acc_full), 0, &abortf, a.status, W_Q_ACCFULL);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok) {
       tc_fence_after_sync();
       constexpr int EC = HD / 4;
       uint16_t* drow = reinterpret_cast<uint16_t*>(a.dq) + (size_t)b * a.dq_sb + (size_t)h * a.dq_sh + (size_t)qi * a.dq_st + g * EC;
@@ -405,6 +446,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if constexpr (EC == 16) tmem_ld16(tbase + lane_base + C::TM_ACC0 + g * EC, r);
         else tmem_ld32(tbase + lane_base + C::TM_ACC0 + g * EC, r);
         tmem_wait_ld();
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(&bar_acc_free));   // the next head's first product may overwrite the accumulator
       } else {
 #pragma unroll
         for (int j = 0; j < EC; ++j) r[j] = 0u;
@@ -424,8 +467,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 }
 
 // =========================================================================================
-// dK/dV kernel: one CTA per (b, h, key tile); streams = query halves of the current query tile.
-//   M1(i): S^T_i = K Q_i^T, dP^T_i = V dO_i^T     M2(i): dV += P^T_i dO_i,  dK += dS^T_i Q_i
+// dK/dV kernel: one CTA per (b, group of heads, key tile); streams = query halves of the current
+// query tile.   M1(i): S^T_i = K Q_i^T, dP^T_i = V dO_i^T     M2(i): dV += P^T_i dO_i,  dK += dS^T_i Q_i
+// Heads are handled one after the other as in the dQ kernel.
 // =========================================================================================
 template <int HD, bool kBf16>
 __global__ void __launch_bounds__(640, 1)
@@ -435,26 +479,29 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   using C = BwdCfg<HD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const uint32_t sK = smem_u32(smem + C::SMEM_FIX);
-  const uint32_t sV = sK + C::TILE_BYTES;
+  const uint32_t sFix = smem_u32(smem + C::SMEM_FIX);    // buffer f: K at +0, V at +TILE_BYTES
   const uint32_t sRing = smem_u32(smem + C::SMEM_RING);  // stage s: Q at +0, dO at +TILE_BYTES
   uint32_t* sStage = reinterpret_cast<uint32_t*>(smem + C::SMEM_STAGE);
   uint16_t* sList = reinterpret_cast<uint16_t*>(smem + C::SMEM_ACT);
 
-  __shared__ __align__(8) uint64_t bar_fix_full, bar_ring_full[C::STAGES], bar_ring_empty[C::STAGES],
-      bar_s_full[C::NBUF], bar_p_full[C::NBUF], bar_m2_issued[C::NBUF], bar_acc_full;
+  __shared__ __align__(8) uint64_t bar_fix_full[C::NFIX], bar_fix_empty[C::NFIX], bar_ring_full[C::STAGES],
+      bar_ring_empty[C::STAGES], bar_s_full[C::NBUF], bar_p_full[C::NBUF], bar_m2_issued[C::NBUF], bar_acc_full, bar_acc_free;
   __shared__ uint32_t tmem_base_s;
   __shared__ AbortFlag abortf;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   cta_trace(a.trace, 1);
-  const int h = blockIdx.x, b = blockIdx.y;
+  const int h0 = blockIdx.x * a.G, b = blockIdx.y;
+  const int nh = min(a.G, a.H - h0);   // this CTA handles heads h0 .. h0 + nh - 1
   const int kt = a.order[((size_t)b * 3 + 2) * a.NT + blockIdx.z];   // longest lists first
   const int n = a.bwd_cnt[b * a.NT + kt];
 
   if (tid == 0) {
     abortf.v = 0;
-    mbar_init(smem_u32(&bar_fix_full), 1);
+    for (int f = 0; f < C::NFIX; ++f) {
+      mbar_init(smem_u32(&bar_fix_full[f]), 1);
+      mbar_init(smem_u32(&bar_fix_empty[f]), 2);  // both M1 issuers are done with the head's K and V
+    }
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(smem_u32(&bar_ring_full[s]), 1);
       mbar_init(smem_u32(&bar_ring_empty[s]), 1);
@@ -465,6 +512,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       mbar_init(smem_u32(&bar_m2_issued[i]), 1);
     }
     mbar_init(smem_u32(&bar_acc_full), 1);
+    mbar_init(smem_u32(&bar_acc_free), 512);      // every compute thread has read its part of dK and dV
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -481,8 +529,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t tbase = tmem_base_s;
   const uint16_t* list = sList;
   Tracer tr;
-  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 3 || warp == 1 || warp == 4 || warp == 8),
-          blockIdx.z * 4 + (warp == 3 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));
+  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 3 || warp == 1 || warp == 4 || warp == 12),
+          blockIdx.z * 4 + (warp == 3 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));   // issuers and one warp of each stream
   tr.ev(1);
   cta_trace(a.trace, 2);
 
@@ -494,68 +542,80 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
       tma_prefetch_desc(&tmDO);
-      mbar_arrive_expect_tx(smem_u32(&bar_fix_full), 2 * C::TILE_BYTES);
-      for (int kb = 0; kb < C::KBLK; ++kb) {
-        tma_load_4d(sK + kb * 16384, &tmK, smem_u32(&bar_fix_full), kb * 64, kt * KD_TILE, h, b);
-        tma_load_4d(sV + kb * 16384, &tmV, smem_u32(&bar_fix_full), kb * 64, kt * KD_TILE, h, b);
-      }
-      int issued = 0;
-      for (int e = 0; e < n; ++e) {
-        const int s = e % C::STAGES;
-        const uint32_t ph = (e / C::STAGES) & 1;
-        const int qt = list[e] & 0xFF;
-        if (!mbar_wait(smem_u32(&bar_ring_empty[s]), ph ^ 1, &abortf, a.status, W_K_RINGEMPTY)) break;
-        tr.ev(40);
-        mbar_arrive_expect_tx(smem_u32(&bar_ring_full[s]), 2 * C::TILE_BYTES);
-        const uint32_t dst = sRing + s * 2 * C::TILE_BYTES;
-        for (int kb = 0; kb < C::KBLK; ++kb) {
-          tma_load_4d(dst + kb * 16384, &tmQ, smem_u32(&bar_ring_full[s]), kb * 64, qt * KD_TILE, h, b);
-          tma_load_4d(dst + C::TILE_BYTES + kb * 16384, &tmDO, smem_u32(&bar_ring_full[s]), kb * 64, qt * KD_TILE, h, b);
+      int issued = 0, fix_issued = 0;   // ring entries / resident pairs requested so far, over all heads
+      bool ok = true;
+      for (int hh = 0; hh < nh && ok; ++hh) {
+        const int h = h0 + hh, fb = hh % C::NFIX;
+        if (hh >= C::NFIX) {
+          ok = mbar_wait(smem_u32(&bar_fix_empty[fb]), (hh / C::NFIX - 1) & 1, &abortf, a.status, W_K_FIXEMPTY);
+          if (!ok) break;
         }
-        issued = e + 1;
+        mbar_arrive_expect_tx(smem_u32(&bar_fix_full[fb]), 2 * C::TILE_BYTES);
+        for (int kb = 0; kb < C::KBLK; ++kb) {
+          tma_load_4d(sFix + fb * 2 * C::TILE_BYTES + kb * 16384, &tmK, smem_u32(&bar_fix_full[fb]), kb * 64, kt * KD_TILE, h, b);
+          tma_load_4d(sFix + fb * 2 * C::TILE_BYTES + C::TILE_BYTES + kb * 16384, &tmV, smem_u32(&bar_fix_full[fb]), kb * 64, kt * KD_TILE, h, b);
+        }
+        fix_issued = hh + 1;
+        for (int e = 0; e < n; ++e) {
+          const int s = issued % C::STAGES;
+          const uint32_t ph = (issued / C::STAGES) & 1;
+          const int qt = list[e] & 0xFF;
+          ok = mbar_wait(smem_u32(&bar_ring_empty[s]), ph ^ 1, &abortf, a.status, W_K_RINGEMPTY);
+          if (!ok) break;
+          tr.ev(40);
+          mbar_arrive_expect_tx(smem_u32(&bar_ring_full[s]), 2 * C::TILE_BYTES);
+          const uint32_t dst = sRing + s * 2 * C::TILE_BYTES;
+          for (int kb = 0; kb < C::KBLK; ++kb) {
+            tma_load_4d(dst + kb * 16384, &tmQ, smem_u32(&bar_ring_full[s]), kb * 64, qt * KD_TILE, h, b);
+            tma_load_4d(dst + C::TILE_BYTES + kb * 16384, &tmDO, smem_u32(&bar_ring_full[s]), kb * 64, qt * KD_TILE, h, b);
+          }
+          ++issued;
+        }
       }
-      if (abortf.v != 0) {
+      if (abortf.v != 0) {   // let the copies in flight land before the CTA exits
         for (int e = max(0, issued - C::STAGES); e < issued; ++e)
           for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_ring_full[e % C::STAGES]), (e / C::STAGES) & 1); ++spin) {}
-        for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_fix_full), 0); ++spin) {}
+        for (int f = max(0, fix_issued - C::NFIX); f < fix_issued; ++f)
+          for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&bar_fix_full[f % C::NFIX]), (f / C::NFIX) & 1); ++spin) {}
       }
     } else if ((warp == 3 || warp == 2) && lane == 0 && n > 0) {
       // ------------------------------ M1 issuers: warp 3: S^T_u = K Q_u^T; warp 2: dP^T_u = V dO_u^T ------------------------------
       const bool dp_part = (warp == 2);
       const uint32_t idesc_m1 = make_idesc_f16(kBf16, 0, 0, KD_TILE, 64);   // N = 64 queries
       const uint32_t hi = desc_hi_sw128();
-      const uint32_t loK = desc_lo_kmajor(sK), loV = desc_lo_kmajor(sV), loRingK = desc_lo_kmajor(sRing);
+      const uint32_t loRingK = desc_lo_kmajor(sRing);
       const int U = 2 * n;
-      bool ok = mbar_wait(smem_u32(&bar_fix_full), 0, &abortf, a.status, W_K_FIXFULL);
-      int buf = 0, round = 0, stage = 0;
+      bool ok = true;
+      int buf = 0, round = 0, stage = 0;   // run on across the heads
       uint32_t ring_parity = 0;
-      for (int u = 0; u < U && ok; ++u) {
-        const int i = u & 1;
-        if (round > 0) {   // buffer free once M2 of its previous unit has been issued
-          ok = mbar_wait(smem_u32(&bar_m2_issued[buf]), (round - 1) & 1, &abortf, a.status, W_K_M2ISSUED);
-          if (!ok) break;
-        }
-        if (i == 0) {      // first unit of a new entry: its Q and dO tiles must have landed
-          ok = mbar_wait(smem_u32(&bar_ring_full[stage]), ring_parity, &abortf, a.status, W_K_RINGFULL);
-          if (!ok) break;
-        }
-        tc_fence_after_sync();
-        const uint32_t qb = loRingK + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);  // query rows 64i..
-        const uint32_t dob = qb + (C::TILE_BYTES >> 4);
-        const uint32_t dS = tbase + buf * 128, dP = dS + 64;
-        if (!dp_part) {
+      for (int hh = 0; hh < nh && ok; ++hh) {
+        const int fb = hh % C::NFIX;
+        ok = mbar_wait(smem_u32(&bar_fix_full[fb]), (hh / C::NFIX) & 1, &abortf, a.status, W_K_FIXFULL);
+        if (!ok) break;
+        const uint32_t loA = desc_lo_kmajor(sFix + fb * 2 * C::TILE_BYTES + (dp_part ? C::TILE_BYTES : 0));   // V or K
+        for (int u = 0; u < U && ok; ++u) {
+          const int i = u & 1;
+          if (round > 0) {   // buffer free once M2 of its previous unit has been issued
+            ok = mbar_wait(smem_u32(&bar_m2_issued[buf]), (round - 1) & 1, &abortf, a.status, W_K_M2ISSUED);
+            if (!ok) break;
+          }
+          if (i == 0) {      // first unit of a new entry: its Q and dO tiles must have landed
+            ok = mbar_wait(smem_u32(&bar_ring_full[stage]), ring_parity, &abortf, a.status, W_K_RINGFULL);
+            if (!ok) break;
+          }
+          tc_fence_after_sync();
+          // query rows 64i.. of Q (scores) or dO (dP)
+          const uint32_t bdesc = loRingK + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4) + (dp_part ? (C::TILE_BYTES >> 4) : 0);
+          const uint32_t dst = tbase + buf * 128 + (dp_part ? 64 : 0);
 #pragma unroll
           for (int kk = 0; kk < HD / 16; ++kk)
-            mma_ss_split(dS, loK + koff_kmajor(kk), qb + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
-        } else {
-#pragma unroll
-          for (int kk = 0; kk < HD / 16; ++kk)
-            mma_ss_split(dP, loV + koff_kmajor(kk), dob + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
+            mma_ss_split(dst, loA + koff_kmajor(kk), bdesc + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
+          mma_commit(smem_u32(&bar_s_full[buf]));
+          tr.ev(15);
+          if (++buf == C::NBUF) { buf = 0; ++round; }
+          if (i == 1 && ++stage == C::STAGES) { stage = 0; ring_parity ^= 1; }
         }
-        mma_commit(smem_u32(&bar_s_full[buf]));
-        tr.ev(15);
-        if (++buf == C::NBUF) { buf = 0; ++round; }
-        if (i == 1 && ++stage == C::STAGES) { stage = 0; ring_parity ^= 1; }
+        if (ok) mma_commit(smem_u32(&bar_fix_empty[fb]));   // this issuer's products of the head no longer read K / V
       }
     } else if (warp == 1 && lane == 0 && n > 0) {
       // ------------------------------ M2 issuer: dV += P^T_u dO_u, dK += dS^T_u Q_u ------------------------------
@@ -567,30 +627,36 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       bool ok = true;
       int buf = 0, stage = 0;
       uint32_t round_parity = 0;
-      for (int u = 0; u < U && ok; ++u) {
-        const int i = u & 1;
-        ok = mbar_wait(smem_u32(&bar_p_full[buf]), round_parity, &abortf, a.status, W_K_PFULL);
-        if (!ok) break;
-        tr.ev(10);
-        tc_fence_after_sync();
-        const uint32_t qb = loRingMN + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
-        const uint32_t dob = qb + (C::TILE_BYTES >> 4);
-        const uint32_t aS = tbase + buf * 128, aP = aS + 64;
-        // 16-bit operands: queries 0-31 of the unit at columns [0,16) of their buffer half, queries 32-63 at [32,48)
+      for (int hh = 0; hh < nh && ok; ++hh) {
+        if (hh > 0) {   // the previous head's dK and dV must have been read out of the accumulators
+          ok = mbar_wait(smem_u32(&bar_acc_free), (hh - 1) & 1, &abortf, a.status, W_K_ACCFREE);
+          if (!ok) break;
+        }
+        for (int u = 0; u < U && ok; ++u) {
+          const int i = u & 1;
+          ok = mbar_wait(smem_u32(&bar_p_full[buf]), round_parity, &abortf, a.status, W_K_PFULL);
+          if (!ok) break;
+          tr.ev(10);
+          tc_fence_after_sync();
+          const uint32_t qb = loRingMN + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
+          const uint32_t dob = qb + (C::TILE_BYTES >> 4);
+          const uint32_t aS = tbase + buf * 128, aP = aS + 64;
+          // 16-bit operands: queries 0-31 of the unit at columns [0,16) of their buffer half, queries 32-63 at [32,48)
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)  // dV += P^T_u dO_u   (P^T_u on top of S^T_u)
-          mma_ts_split(tDV, aS + (kk >> 1) * 32 + (kk & 1) * 8, dob + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < 4; ++kk)  // dV += P^T_u dO_u   (P^T_u on top of S^T_u)
+            mma_ts_split(tDV, aS + (kk >> 1) * 32 + (kk & 1) * 8, dob + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)  // dK += dS^T_u Q_u   (dS^T_u on top of dP^T_u)
-          mma_ts_split(tDK, aP + (kk >> 1) * 32 + (kk & 1) * 8, qb + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
-        if (i == 1) mma_commit(smem_u32(&bar_ring_empty[stage]));
-        tc_fence_before_sync();
-        mbar_arrive(smem_u32(&bar_m2_issued[buf]));
-        tr.ev(11);
-        if (++buf == C::NBUF) { buf = 0; round_parity ^= 1; }
-        if (i == 1 && ++stage == C::STAGES) stage = 0;
+          for (int kk = 0; kk < 4; ++kk)  // dK += dS^T_u Q_u   (dS^T_u on top of dP^T_u)
+            mma_ts_split(tDK, aP + (kk >> 1) * 32 + (kk & 1) * 8, qb + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
+          if (i == 1) mma_commit(smem_u32(&bar_ring_empty[stage]));
+          tc_fence_before_sync();
+          mbar_arrive(smem_u32(&bar_m2_issued[buf]));
+          tr.ev(11);
+          if (++buf == C::NBUF) { buf = 0; round_parity ^= 1; }
+          if (i == 1 && ++stage == C::STAGES) stage = 0;
+        }
+        if (ok) mma_commit(smem_u32(&bar_acc_full));
       }
-      if (ok) mma_commit(smem_u32(&bar_acc_full));
     }
   } else {
     reg_alloc<KD_REGS_COMPUTE_BWD>();
@@ -603,115 +669,136 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const int kj = kt * KD_TILE + row;   // this thread's key
     const bool k_valid = kj < a.T;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
-    uint32_t* st_buf = sStage + (size_t)(warp - 4) * C::STAGE_WORDS;  // [32 -lse][32 delta][32 desc]
+    uint32_t* st_buf = sStage + (size_t)(warp - 4) * C::STAGE_WORDS;  // [32 lse][32 delta][32 desc]
     const float c = a.scale_log2;
-    const size_t bh = (size_t)b * a.H + h;
     const uint32_t kdesc = a.desc[(size_t)b * a.Tpad + kj];
     const int tbw = 2 * i + sub;     // this slice's word in the 128-bit class masks of a query tile
     bool ok = true;
 
-    // -LSE, delta and the descriptor of the next entry's 32 queries are fetched one entry ahead
+    // LSE, delta and the descriptor of the next unit's 32 queries are fetched one unit ahead
     // into registers and handed to the warp through its shared-memory staging buffer
     float pre_lse = 0.f, pre_delta = 0.f;
     uint32_t pre_desc = 0u;
     // query-side class masks of the next unit: sees-prefix, sees-context, sees-in_span, context, same-span armed
     uint32_t tb_pre[5] = {0u, 0u, 0u, 0u, 0u};
-    auto prefetch = [&](int e) {
-      if (e < n) {
-        if ((list[e] >> 8) == KD_TILE_PARTIAL) {
-          const uint32_t* tbp = a.tilebits + ((size_t)b * a.NT + (list[e] & 0xFFu)) * 32;
-          tb_pre[0] = tbp[4 * TB_SEES_PRE + tbw];
-          tb_pre[1] = tbp[4 * TB_SEES_CTX + tbw];
-          tb_pre[2] = tbp[4 * TB_SEES_INS + tbw];
-          tb_pre[3] = tbp[4 * TB_CTX + tbw];
-          tb_pre[4] = tbp[4 * TB_SIDPOS + tbw];
-        }
-        const int q = (list[e] & 0xFF) * KD_TILE + i * 64 + sub * 32 + lane;
-        const bool v = q < a.T;
-        pre_lse = v ? -a.lse[bh * a.T + q] : 0.f;
-        pre_delta = v ? a.delta[bh * a.T + q] : 0.f;
-        pre_desc = a.desc[(size_t)b * a.Tpad + q];
+    auto prefetch = [&](int e, int h) {
+      if ((list[e] >> 8) == KD_TILE_PARTIAL) {
+        const uint32_t* tbp = a.tilebits + ((size_t)b * a.NT + (list[e] & 0xFFu)) * 32;
+        tb_pre[0] = tbp[4 * TB_SEES_PRE + tbw];
+        tb_pre[1] = tbp[4 * TB_SEES_CTX + tbw];
+        tb_pre[2] = tbp[4 * TB_SEES_INS + tbw];
+        tb_pre[3] = tbp[4 * TB_CTX + tbw];
+        tb_pre[4] = tbp[4 * TB_SIDPOS + tbw];
       }
+      const int q = (list[e] & 0xFF) * KD_TILE + i * 64 + sub * 32 + lane;
+      const bool v = q < a.T;
+      const size_t bh = (size_t)b * a.H + h;
+      pre_lse = v ? a.lse[bh * a.T + q] : 0.f;   // negated where it is used: a negation here would wait for the load
+      pre_delta = v ? a.delta[bh * a.T + q] : 0.f;
+      pre_desc = a.desc[(size_t)b * a.Tpad + q];
     };
-    prefetch(0);
+    if (n > 0) prefetch(0, h0);
+    int ug = i;   // this stream's next unit, counted over all heads
 
-    for (int e = 0; e < n; ++e) {
-      const uint32_t ent = list[e];
-      const uint32_t cls = ent >> 8;
-      const int qt = ent & 0xFF;
-      const int i0 = qt * KD_TILE + i * 64 + sub * 32;  // first query of this slice
-      tr.ev(20);
-      __syncwarp();
-      st_buf[lane] = __float_as_uint(pre_lse);
-      st_buf[32 + lane] = __float_as_uint(pre_delta);
-      st_buf[64 + lane] = pre_desc;
-      __syncwarp();
-      uint32_t mk = 0xFFFFFFFFu;   // visibility of this key for the slice's 32 queries
-      if (cls == KD_TILE_PARTIAL) {
-        key_row_mask<1>(kdesc, kj, i0, tb_pre + 0, tb_pre + 1, tb_pre + 2, tb_pre + 3, &mk);
-        if (tb_pre[4] != 0u && __any_sync(0xffffffffu, (kdesc & TD_INS) != 0u)) {
-          const uint32_t key = span_key_of_key(kdesc);
+    for (int hh = 0; hh < nh && ok; ++hh) {
+      const int h = h0 + hh;
+      for (int e = 0; e < n; ++e, ug += 2) {
+        const uint32_t ent = list[e];
+        const uint32_t cls = ent >> 8;
+        const int qt = ent & 0xFF;
+        const int i0 = qt * KD_TILE + i * 64 + sub * 32;  // first query of this slice
+        tr.ev(20);
+        __syncwarp();
+        st_buf[lane] = __float_as_uint(pre_lse);
+        st_buf[32 + lane] = __float_as_uint(pre_delta);
+        st_buf[64 + lane] = pre_desc;
+        __syncwarp();
+        tr.ev(41);
+        uint32_t mk = 0xFFFFFFFFu;   // visibility of this key for the slice's 32 queries
+        if (cls == KD_TILE_PARTIAL) {
+          key_row_mask<1>(kdesc, kj, i0, tb_pre + 0, tb_pre + 1, tb_pre + 2, tb_pre + 3, &mk);
+          if (tb_pre[4] != 0u && __any_sync(0xffffffffu, (kdesc & TD_INS) != 0u)) {
+            const uint32_t key = span_key_of_key(kdesc);
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            const uint4 q4 = *reinterpret_cast<const uint4*>(st_buf + 64 + j);
-            mk |= (span_match_query(key, q4.x) << (j + 0)) | (span_match_query(key, q4.y) << (j + 1)) |
-                  (span_match_query(key, q4.z) << (j + 2)) | (span_match_query(key, q4.w) << (j + 3));
+            for (int j = 0; j < 32; j += 4) {
+              const uint4 q4 = *reinterpret_cast<const uint4*>(st_buf + 64 + j);
+              mk |= (span_match_query(key, q4.x) << (j + 0)) | (span_match_query(key, q4.y) << (j + 1)) |
+                    (span_match_query(key, q4.z) << (j + 2)) | (span_match_query(key, q4.w) << (j + 3));
+            }
           }
         }
+        tr.ev(42);
+        if (e + 1 < n) prefetch(e + 1, h);
+        else if (hh + 1 < nh) prefetch(0, h + 1);   // the next head walks the same list again
+        const int buf = ug % C::NBUF;
+        const uint32_t tS = tbase + lane_base + buf * 128 + sub * 32, tP = tS + 64;
+        tr.ev(21);
+        ok = mbar_wait(smem_u32(&bar_s_full[buf]), (ug / C::NBUF) & 1, &abortf, a.status, W_K_SFULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+        tr.ev(22);
+
+        uint32_t pk_p[16], pk_ds[16];
+        {
+          uint32_t rs[32], rp[32];
+          tmem_ld32(tS, rs);
+          tmem_ld32(tP, rp);
+          tmem_wait_ld();
+          if (cls != KD_TILE_PARTIAL) {   // warp-uniform: the common case carries no mask code at all
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const float4 l4 = *reinterpret_cast<const float4*>(st_buf + j);        // LSE of 4 queries
+              const float4 d4 = *reinterpret_cast<const float4*>(st_buf + 32 + j);   // delta of 4 queries
+              const float lw[4] = {l4.x, l4.y, l4.z, l4.w}, dw[4] = {d4.x, d4.y, d4.z, d4.w};
+              float pv[4], ds[4];
+#pragma unroll
+              for (int u2 = 0; u2 < 4; ++u2) pv[u2] = fast_exp2(fmaf(__uint_as_float(rs[j + u2]), c, -lw[u2]));
+#pragma unroll
+              for (int u2 = 0; u2 < 4; ++u2) ds[u2] = pv[u2] * (__uint_as_float(rp[j + u2]) - dw[u2]);
+              pk_p[j / 2] = pack2<kBf16>(pv[0], pv[1]);
+              pk_p[j / 2 + 1] = pack2<kBf16>(pv[2], pv[3]);
+              pk_ds[j / 2] = pack2<kBf16>(ds[0], ds[1]);
+              pk_ds[j / 2 + 1] = pack2<kBf16>(ds[2], ds[3]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const float4 l4 = *reinterpret_cast<const float4*>(st_buf + j);
+              const float4 d4 = *reinterpret_cast<const float4*>(st_buf + 32 + j);
+              const float lw[4] = {l4.x, l4.y, l4.z, l4.w}, dw[4] = {d4.x, d4.y, d4.z, d4.w};
+              float pv[4], ds[4];
+#pragma unroll
+              for (int u2 = 0; u2 < 4; ++u2) {
+                pv[u2] = fast_exp2(fmaf(__uint_as_float(rs[j + u2]), c, -lw[u2]));
+                if ((mk & (1u << (j + u2))) == 0u) pv[u2] = 0.f;
+              }
+#pragma unroll
+              for (int u2 = 0; u2 < 4; ++u2) ds[u2] = pv[u2] * (__uint_as_float(rp[j + u2]) - dw[u2]);
+              pk_p[j / 2] = pack2<kBf16>(pv[0], pv[1]);
+              pk_p[j / 2 + 1] = pack2<kBf16>(pv[2], pv[3]);
+              pk_ds[j / 2] = pack2<kBf16>(ds[0], ds[1]);
+              pk_ds[j / 2 + 1] = pack2<kBf16>(ds[2], ds[3]);
+            }
+          }
+        }
+        tr.ev(24);
+        tmem_st16(tS, pk_p);    // P^T of this slice over the scores it was made from
+        tmem_st16(tP, pk_ds);   // dS^T of this slice over its dP^T
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(&bar_p_full[buf]));
+        tr.ev(25);
       }
-      prefetch(e + 1);
-      const int u = 2 * e + i, buf = u % C::NBUF;
-      const uint32_t tS = tbase + lane_base + buf * 128 + sub * 32, tP = tS + 64;
-      tr.ev(21);
-      ok = mbar_wait(smem_u32(&bar_s_full[buf]), (u / C::NBUF) & 1, &abortf, a.status, W_K_SFULL);
-      ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      tc_fence_after_sync();
-      tr.ev(22);
 
-      uint32_t pk_p[16], pk_ds[16];
-      {
-        uint32_t rs[32], rp[32];
-        tmem_ld32(tS, rs);
-        tmem_ld32(tP, rp);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(st_buf + j);        // -LSE of 4 queries
-          const float4 d4 = *reinterpret_cast<const float4*>(st_buf + 32 + j);   // delta of 4 queries
-          const float lw[4] = {l4.x, l4.y, l4.z, l4.w}, dw[4] = {d4.x, d4.y, d4.z, d4.w};
-          float pv[4], ds[4];
-#pragma unroll
-          for (int u2 = 0; u2 < 4; ++u2) pv[u2] = fast_exp2(fmaf(__uint_as_float(rs[j + u2]), c, lw[u2]));
-          if (cls == KD_TILE_PARTIAL) {
-#pragma unroll
-            for (int u2 = 0; u2 < 4; ++u2)
-              if ((mk & (1u << (j + u2))) == 0u) pv[u2] = 0.f;
-          }
-#pragma unroll
-          for (int u2 = 0; u2 < 4; ++u2) ds[u2] = pv[u2] * (__uint_as_float(rp[j + u2]) - dw[u2]);
-          pk_p[j / 2] = pack2<kBf16>(pv[0], pv[1]);
-          pk_p[j / 2 + 1] = pack2<kBf16>(pv[2], pv[3]);
-          pk_ds[j / 2] = pack2<kBf16>(ds[0], ds[1]);
-          pk_ds[j / 2 + 1] = pack2<kBf16>(ds[2], ds[3]);
-        }
+      // epilogue of this head: warpgroup g stores columns [g*HD/4, (g+1)*HD/4) of dK and dV
+      if (n > 0) {
+        ok = mbar_wait(smem_u32(&bar_acc_full), hh & 1, &abortf, a.status, W_K_ACCFULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
       }
-      tr.ev(24);
-      tmem_st16(tS, pk_p);    // P^T of this slice over the scores it was made from
-      tmem_st16(tP, pk_ds);   // dS^T of this slice over its dP^T
-      tmem_wait_st();
-      tc_fence_before_sync();
-      mbar_arrive(smem_u32(&bar_p_full[buf]));
-      tr.ev(25);
-    }
-
-    // epilogue: warpgroup g stores columns [g*HD/4, (g+1)*HD/4) of dK and dV
-    if (ok && n > 0) {
-      ok = mbar_wait(smem_u32(&bar_acc_full), 0, &abortf, a.status, W_K_ACCFULL);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    tr.ev(30);
-    if (ok) {
+      tr.ev(30);
       tc_fence_after_sync();
       constexpr int EC = HD / 4;
       uint16_t* krow = reinterpret_cast<uint16_t*>(a.dk) + (size_t)b * a.dk_sb + (size_t)h * a.dk_sh + (size_t)kj * a.dk_st + g * EC;
@@ -726,6 +813,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           tmem_ld32(tbase + lane_base + C::TM_ACC1 + g * EC, rv);
         }
         tmem_wait_ld();
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(&bar_acc_free));   // the next head's first products may overwrite the accumulators
       } else {
 #pragma unroll
         for (int j = 0; j < EC; ++j) { rk[j] = 0u; rv[j] = 0u; }
@@ -762,6 +851,7 @@ static int launch_bwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
   a.B = p.B; a.H = p.H; a.T = p.T; a.NT = L.NT; a.NP = L.NP; a.Tpad = L.NT * KD_TILE;
   a.scale_log2 = p.sm_scale * 1.4426950408889634f;
   a.sm_scale = p.sm_scale;
+  a.G = heads_per_cta(p.B, p.H, L.NT, "KD_HEADS_PER_CTA_BWD");
   a.desc = pv.desc; a.fwd_cnt = pv.fwd_cnt; a.fwd_list = pv.fwd_list;
   a.bwd_cnt = pv.bwd_cnt; a.bwd_list = pv.bwd_list; a.status = pv.status; a.order = pv.order; a.tilebits = pv.tilebits;
   a.o = p.o.ptr; a.o_sb = p.o.stride_b; a.o_sh = p.o.stride_h; a.o_st = p.o.stride_t;
@@ -776,7 +866,7 @@ static int launch_bwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
   cudaError_t e = cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_ALLOC);
   if (e == cudaSuccess) e = cudaFuncSetAttribute(kk, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_ALLOC);
   if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "bwd smem attribute: %s", cudaGetErrorString(e));
-  dim3 grid(p.H, p.B, L.NT);
+  dim3 grid((p.H + a.G - 1) / a.G, p.B, L.NT);
   const int phases = (p.bwd_phases & 3) ? (p.bwd_phases & 3) : 3;
   if (phases & 1) {
     const size_t rows = (size_t)p.B * p.H * p.T;

@@ -95,7 +95,7 @@ __device__ __forceinline__ void store_row16(uint16_t* dst, const uint32_t (&r)[1
 
 // Heads a CTA handles one after the other (they share the plan's work list, so the list staging,
 // the TMEM allocation and the pipeline fill are paid once): as many as keeps about 8 CTAs per SM.
-inline int heads_per_cta(int B, int H, int items_per_batch) {
+inline int heads_per_cta(int B, int H, int items_per_batch, const char* env_name = "KD_HEADS_PER_CTA") {
   static int sm_count = 0;
   if (sm_count == 0) {
     int dev = 0;
@@ -107,7 +107,7 @@ inline int heads_per_cta(int B, int H, int items_per_batch) {
   if (g < 1) g = 1;
   if (g > 8) g = 8;
   if (g > H) g = H;
-  if (const char* env = getenv("KD_HEADS_PER_CTA")) {   // tuning aid
+  if (const char* env = getenv(env_name)) {   // tuning aid
     const int v = atoi(env);
     if (v >= 1 && v <= H) g = v;
   }

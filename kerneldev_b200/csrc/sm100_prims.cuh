@@ -89,20 +89,32 @@ struct AbortFlag {
 // Waits for the phase with the given parity. Returns true when the phase completed.
 // On time-out (or when another role already aborted) returns false after recording
 // KD_DEV_TIMEOUT|site in *status (first writer wins) and raising the CTA abort flag.
+// try_wait that lets the hardware suspend the thread for up to `ns` nanoseconds while the phase is
+// pending: a waiting thread then takes no issue slots from the warps that share its scheduler
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, AbortFlag* abort_flag,
                                           uint32_t* status, uint32_t site) {
   if (mbar_try_wait(bar, parity)) return true;
-  uint64_t t0 = globaltimer_ns();
-  uint32_t spins = 0;
+  const uint64_t t0 = globaltimer_ns();
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (((++spins) & 63u) == 0u) {
-      if (abort_flag->v != 0u) return false;
-      if (globaltimer_ns() - t0 > KD_WAIT_LIMIT_NS) {
-        abort_flag->v = 1u;
-        atomicCAS(status, KD_DEV_OK, KD_DEV_TIMEOUT | site);
-        return false;
-      }
+    if (mbar_try_wait_suspend(bar, parity, 20000u)) return true;
+    if (abort_flag->v != 0u) return false;
+    if (globaltimer_ns() - t0 > KD_WAIT_LIMIT_NS) {
+      abort_flag->v = 1u;
+      atomicCAS(status, KD_DEV_OK, KD_DEV_TIMEOUT | site);
+      return false;
     }
   }
 }
