@@ -344,9 +344,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // key descriptors of PARTIAL tiles are fetched one entry ahead into registers
     uint32_t kd_pre = 0u;
     uint32_t tb_pre[3] = {0u, 0u, 0u};   // key-side class masks of this slice: is_prefix, context, in_span
-    auto prefetch_kd = [&](int e) {
-      if ((sAct[e] >> 8) == KD_TILE_PARTIAL) {
-        const uint32_t ktile = sAct[e] & 0xFFu;
+    auto prefetch_kd = [&](uint32_t entry) {
+      if ((entry >> 8) == KD_TILE_PARTIAL) {
+        const uint32_t ktile = entry & 0xFFu;
         kd_pre = a.desc[(size_t)b * a.Tpad + (size_t)ktile * KD_TILE + i * 64 + sub * 32 + lane];
         const uint32_t* tbp = a.tilebits + ((size_t)b * a.NT + ktile) * 32;
         tb_pre[0] = tbp[4 * TB_PRE + tbw];
@@ -354,11 +354,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tb_pre[2] = tbp[4 * TB_INS + tbw];
       }
     };
-    if (na > 0) prefetch_kd(0);
+    uint32_t ent_next = na > 0 ? sAct[0] : 0u;
+    if (na > 0) prefetch_kd(ent_next);
     // per-row scalars of the next head are fetched while the current head is processed
     float nxt_delta = q_valid ? a.delta[((size_t)b * a.H + h0) * a.T + qi] : 0.f;
     float nxt_lse = q_valid ? a.lse[((size_t)b * a.H + h0) * a.T + qi] : 0.f;
-    int ug = i;   // this stream's next unit, counted over all heads
+    // this stream's next unit, counted over all heads, as (unit / NBUF, unit % NBUF)
+    int buf = i % C::NBUF;
+    uint32_t rnd = i / C::NBUF;
+    const uint32_t sfull0 = smem_u32(&bar_s_full[0]), pfull0 = smem_u32(&bar_p_full[0]);
+    const uint32_t tcol = tbase + lane_base + sub * 32;   // this slice's columns inside a buffer
 
     for (int hh = 0; hh < nh && ok; ++hh) {
       const int h = h0 + hh;
@@ -367,13 +372,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         nxt_delta = a.delta[((size_t)b * a.H + h + 1) * a.T + qi];
         nxt_lse = a.lse[((size_t)b * a.H + h + 1) * a.T + qi];
       }
-      for (int e = 0; e < na; ++e, ug += 2) {
-        const uint32_t ent = sAct[e];
+      for (int e = 0; e < na; ++e) {
+        const uint32_t ent = ent_next;
         const uint32_t cls = ent >> 8;
-        const int kt = ent & 0xFF;
-        const int j0 = kt * KD_TILE + i * 64 + sub * 32;  // first key of this slice
         uint32_t mk = 0xFFFFFFFFu;   // visibility of this slice's 32 keys for this query row
         if (cls == KD_TILE_PARTIAL) {
+          const int j0 = (ent & 0xFF) * KD_TILE + i * 64 + sub * 32;  // first key of this slice
           __syncwarp();
           kd_buf[lane] = kd_pre;
           __syncwarp();
@@ -388,12 +392,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             }
           }
         }
-        if (e + 1 < na) prefetch_kd(e + 1);
-        else if (hh + 1 < nh) prefetch_kd(0);   // the next head walks the same list again
-        const int buf = ug % C::NBUF;
-        const uint32_t tS = tbase + lane_base + buf * 128 + sub * 32, tP = tS + 64;
+        // the next entry: of this head or, at the end of the list, the first one again for the next head
+        if (e + 1 < na || hh + 1 < nh) {
+          ent_next = sAct[e + 1 < na ? e + 1 : 0];
+          prefetch_kd(ent_next);
+        }
+        const uint32_t tS = tcol + buf * 128, tP = tS + 64;
         tr.ev(21);
-        ok = mbar_wait(smem_u32(&bar_s_full[buf]), (ug / C::NBUF) & 1, &abortf, a.status, W_Q_SFULL);
+        ok = mbar_wait(sfull0 + buf * 8, rnd & 1u, &abortf, a.status, W_Q_SFULL);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
@@ -427,8 +433,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tmem_st16(tS, pk);   // dS of this slice as 16-bit A operand over the scores it was made from (this thread's own row)
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(smem_u32(&bar_p_full[buf]));
+        mbar_arrive(pfull0 + buf * 8);
         tr.ev(25);
+        buf += 2;
+        if (buf >= C::NBUF) { buf -= C::NBUF; ++rnd; }
       }
       if (!ok) break;
 
@@ -681,32 +689,36 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     uint32_t pre_desc = 0u;
     // query-side class masks of the next unit: sees-prefix, sees-context, sees-in_span, context, same-span armed
     uint32_t tb_pre[5] = {0u, 0u, 0u, 0u, 0u};
-    auto prefetch = [&](int e, int h) {
-      if ((list[e] >> 8) == KD_TILE_PARTIAL) {
-        const uint32_t* tbp = a.tilebits + ((size_t)b * a.NT + (list[e] & 0xFFu)) * 32;
+    auto prefetch = [&](uint32_t entry, int h) {
+      if ((entry >> 8) == KD_TILE_PARTIAL) {
+        const uint32_t* tbp = a.tilebits + ((size_t)b * a.NT + (entry & 0xFFu)) * 32;
         tb_pre[0] = tbp[4 * TB_SEES_PRE + tbw];
         tb_pre[1] = tbp[4 * TB_SEES_CTX + tbw];
         tb_pre[2] = tbp[4 * TB_SEES_INS + tbw];
         tb_pre[3] = tbp[4 * TB_CTX + tbw];
         tb_pre[4] = tbp[4 * TB_SIDPOS + tbw];
       }
-      const int q = (list[e] & 0xFF) * KD_TILE + i * 64 + sub * 32 + lane;
-      const bool v = q < a.T;
-      const size_t bh = (size_t)b * a.H + h;
-      pre_lse = v ? a.lse[bh * a.T + q] : 0.f;   // negated where it is used: a negation here would wait for the load
-      pre_delta = v ? a.delta[bh * a.T + q] : 0.f;
+      // a query at or beyond the sequence length reads the last row's scalars: its descriptor is 0,
+      // so the tile is PARTIAL and the mask removes it
+      const int q = (entry & 0xFF) * KD_TILE + i * 64 + sub * 32 + lane;
+      const size_t r = ((size_t)b * a.H + h) * a.T + min(q, a.T - 1);
+      pre_lse = a.lse[r];   // negated where it is used: a negation here would wait for the load
+      pre_delta = a.delta[r];
       pre_desc = a.desc[(size_t)b * a.Tpad + q];
     };
-    if (n > 0) prefetch(0, h0);
-    int ug = i;   // this stream's next unit, counted over all heads
+    uint32_t ent_next = n > 0 ? list[0] : 0u;
+    if (n > 0) prefetch(ent_next, h0);
+    // this stream's next unit, counted over all heads, as (unit / NBUF, unit % NBUF)
+    int buf = i % C::NBUF;
+    uint32_t rnd = i / C::NBUF;
+    const uint32_t sfull0 = smem_u32(&bar_s_full[0]), pfull0 = smem_u32(&bar_p_full[0]);
+    const uint32_t tcol = tbase + lane_base + sub * 32;   // this slice's columns inside a buffer
 
     for (int hh = 0; hh < nh && ok; ++hh) {
       const int h = h0 + hh;
-      for (int e = 0; e < n; ++e, ug += 2) {
-        const uint32_t ent = list[e];
+      for (int e = 0; e < n; ++e) {
+        const uint32_t ent = ent_next;
         const uint32_t cls = ent >> 8;
-        const int qt = ent & 0xFF;
-        const int i0 = qt * KD_TILE + i * 64 + sub * 32;  // first query of this slice
         tr.ev(20);
         __syncwarp();
         st_buf[lane] = __float_as_uint(pre_lse);
@@ -716,6 +728,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tr.ev(41);
         uint32_t mk = 0xFFFFFFFFu;   // visibility of this key for the slice's 32 queries
         if (cls == KD_TILE_PARTIAL) {
+          const int i0 = (ent & 0xFF) * KD_TILE + i * 64 + sub * 32;  // first query of this slice
           key_row_mask<1>(kdesc, kj, i0, tb_pre + 0, tb_pre + 1, tb_pre + 2, tb_pre + 3, &mk);
           if (tb_pre[4] != 0u && __any_sync(0xffffffffu, (kdesc & TD_INS) != 0u)) {
             const uint32_t key = span_key_of_key(kdesc);
@@ -728,12 +741,17 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           }
         }
         tr.ev(42);
-        if (e + 1 < n) prefetch(e + 1, h);
-        else if (hh + 1 < nh) prefetch(0, h + 1);   // the next head walks the same list again
-        const int buf = ug % C::NBUF;
-        const uint32_t tS = tbase + lane_base + buf * 128 + sub * 32, tP = tS + 64;
+        // the next entry: of this head or, at the end of the list, the first one again for the next head
+        if (e + 1 < n) {
+          ent_next = list[e + 1];
+          prefetch(ent_next, h);
+        } else if (hh + 1 < nh) {
+          ent_next = list[0];
+          prefetch(ent_next, h + 1);
+        }
+        const uint32_t tS = tcol + buf * 128, tP = tS + 64;
         tr.ev(21);
-        ok = mbar_wait(smem_u32(&bar_s_full[buf]), (ug / C::NBUF) & 1, &abortf, a.status, W_K_SFULL);
+        ok = mbar_wait(sfull0 + buf * 8, rnd & 1u, &abortf, a.status, W_K_SFULL);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
@@ -787,8 +805,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tmem_st16(tP, pk_ds);   // dS^T of this slice over its dP^T
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(smem_u32(&bar_p_full[buf]));
+        mbar_arrive(pfull0 + buf * 8);
         tr.ev(25);
+        buf += 2;
+        if (buf >= C::NBUF) { buf -= C::NBUF; ++rnd; }
       }
       if (!ok) break;
 
