@@ -328,7 +328,7 @@ def run_ours(args, cfg):
     d2h = sum(x.numel() * x.element_size() for x in (ho, hdq, hdk, hdv))
 
     from kerneldev_b200.host_io import HostPipeline
-    pipe = HostPipeline(dev, chunks=4)
+    pipe = HostPipeline(dev, chunks=args.e2e_chunks)
 
     def step_e2e():
         # public API on host buffers: chunks of the batch are copied in, run through flash_attention +
@@ -396,6 +396,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch size (profiling on a small case)")
     ap.add_argument("--kernels-only", action="store_true", help="skip the end-to-end and CPU legs (profiling)")
+    ap.add_argument("--e2e-chunks", type=int, default=8, help="batch chunks of the host-buffer pipeline in the end-to-end leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     cfg = dict(CONFIGS[args.config])

@@ -19,7 +19,7 @@ import torch
 from . import _capi
 
 _CACHE: "OrderedDict[tuple, AttentionPlan]" = OrderedDict()
-_CACHE_SIZE = 8
+_CACHE_SIZE = 64
 
 
 def _tensor_key(t):
