@@ -367,6 +367,29 @@ struct Tracer {
     p = (on && base) ? base + (size_t)slot * KD_TRACE_SLOTS : nullptr;
     n = 0;
   }
+  // time accumulators (KD_TRACE_ACC builds): tb() starts a section, te(k) adds its length to
+  // counter k, flush() stores the counters as the role's record
+  long long t_, acc_[8];
+  __device__ __forceinline__ void acc_init() {
+#ifdef KD_TRACE_ACC
+    for (int k = 0; k < 8; ++k) acc_[k] = 0;
+#endif
+  }
+  __device__ __forceinline__ void tb() {
+#ifdef KD_TRACE_ACC
+    if (p) t_ = clock64();
+#endif
+  }
+  __device__ __forceinline__ void te(int k) {
+#ifdef KD_TRACE_ACC
+    if (p) { const long long now = clock64(); acc_[k] += now - t_; t_ = now; }
+#endif
+  }
+  __device__ __forceinline__ void flush() {
+#ifdef KD_TRACE_ACC
+    if (p) { for (int k = 0; k < 8; ++k) p[1 + k] = static_cast<unsigned long long>(acc_[k]); p[0] = 8; }
+#endif
+  }
   __device__ __forceinline__ void ev(uint32_t id) {
     if (((KD_TRACE_MASK >> (id & 63u)) & 1ull) && p && n < KD_TRACE_SLOTS - 1) {
       p[1 + n] = (static_cast<unsigned long long>(id) << 48) | (static_cast<unsigned long long>(clock64()) & 0xFFFFFFFFFFFFull);
@@ -391,6 +414,10 @@ __device__ __forceinline__ void cta_trace(unsigned long long* base, int slot) {
 struct Tracer {
   __device__ __forceinline__ void init(unsigned long long*, bool, int) {}
   __device__ __forceinline__ void ev(uint32_t) {}
+  __device__ __forceinline__ void acc_init() {}
+  __device__ __forceinline__ void tb() {}
+  __device__ __forceinline__ void te(int) {}
+  __device__ __forceinline__ void flush() {}
 };
 __device__ __forceinline__ void cta_trace(unsigned long long*, int) {}
 #endif
