@@ -69,8 +69,15 @@ struct BwdCfg {
   static constexpr int SMEM_FIX = 0;                               // NFIX x two resident tiles
   static constexpr int SMEM_RING = SMEM_FIX + NFIX * 2 * TILE_BYTES;  // STAGES x two streamed tiles
   static constexpr int SMEM_STAGE = SMEM_RING + STAGES * 2 * TILE_BYTES;  // per-warp staging
-  static constexpr int STAGE_WORDS = 3 * 32;                       // 32 x {-lse, delta, descriptor}
-  static constexpr int SMEM_ACT = SMEM_STAGE + 16 * STAGE_WORDS * 4;  // compacted entry list
+#ifndef KD_BWD_NSUB
+#define KD_BWD_NSUB 2
+#endif
+  static constexpr int NSUB = KD_BWD_NSUB;            // warpgroups that share a 64-column unit (1 or 2)
+  static constexpr int CPT = 2 / NSUB;                // 32-column chunks per compute thread and unit
+  static constexpr int THREADS = 128 + 256 * NSUB;    // four light warps + 2 * NSUB compute warpgroups
+  static constexpr int REGS_COMPUTE = (NSUB == 2) ? KD_REGS_COMPUTE_BWD : KD_REGS_COMPUTE;
+  static constexpr int STAGE_WORDS = 3 * 32 * CPT;                 // per warp: 32*CPT x {lse, delta, descriptor}
+  static constexpr int SMEM_ACT = SMEM_STAGE + 8 * NSUB * STAGE_WORDS * 4;  // compacted entry list
   static constexpr int SMEM_TOTAL = SMEM_ACT + 128 * 2;
   static constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;
   // TMEM columns
@@ -132,7 +139,7 @@ __global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const BwdArgs a) {
 // compute warps finish the current one, so the pipeline fill and drain are paid once per CTA.
 // =========================================================================================
 template <int HD, bool kBf16>
-__global__ void __launch_bounds__(640, 1)
+__global__ void __launch_bounds__(BwdCfg<HD>::THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                    const BwdArgs a) {
@@ -169,11 +176,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     for (int i = 0; i < C::NBUF; ++i) {
       mbar_init(smem_u32(&bar_s_full[i]), 2);     // one commit from each of the two M1 issuers
-      mbar_init(smem_u32(&bar_p_full[i]), 256);   // the two warpgroups that share the unit
+      mbar_init(smem_u32(&bar_p_full[i]), 128 * C::NSUB);   // the warpgroups that share the unit
       mbar_init(smem_u32(&bar_m2_issued[i]), 1);
     }
     mbar_init(smem_u32(&bar_acc_full), 1);
-    mbar_init(smem_u32(&bar_acc_free), 512);      // every compute thread has read its part of dQ
+    mbar_init(smem_u32(&bar_acc_free), 256 * C::NSUB);      // every compute thread has read its part of dQ
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -201,7 +208,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t tbase = tmem_base_s;
   const int na = n_act_s;
   Tracer tr;
-  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 3 || warp == 1 || warp == 4 || warp == 12),
+  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 3 || warp == 1 || warp == 4 || warp == 4 + 4 * C::NSUB),
           blockIdx.z * 4 + (warp == 3 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));   // issuers and one warp of each stream
   tr.ev(1);
   cta_trace(a.trace, 2);
@@ -325,11 +332,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
     }
   } else {
-    reg_alloc<KD_REGS_COMPUTE_BWD>();
+    reg_alloc<C::REGS_COMPUTE>();
     // ------------------------------ compute warpgroups ------------------------------
+    constexpr int CPT = C::CPT;      // 32-column chunks of a unit this thread handles
     const int g = (warp - 4) >> 2;   // warpgroup
-    const int i = g >> 1;            // stream: key half (64 keys) of each key tile
-    const int sub = g & 1;           // 32-key slice of that half
+    const int i = g / C::NSUB;       // stream: key half (64 keys) of each key tile
+    const int c0 = (g % C::NSUB) * CPT;   // first 32-key chunk of that half handled here
     const int wq = warp & 3;
     const int row = wq * 32 + lane;
     const int qi = qt * KD_TILE + row;
@@ -338,20 +346,25 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     uint32_t* kd_buf = sStage + (size_t)(warp - 4) * C::STAGE_WORDS;
     const float c = a.scale_log2;
     const uint32_t qd = a.desc[(size_t)b * a.Tpad + qi];
-    const int tbw = 2 * i + sub;     // this slice's word in the 128-bit class masks of a key tile
+    const int tbw = 2 * i + c0;      // first word of this thread's chunks in the 128-bit class masks of a key tile
     bool ok = true;
 
     // key descriptors of PARTIAL tiles are fetched one entry ahead into registers
-    uint32_t kd_pre = 0u;
-    uint32_t tb_pre[3] = {0u, 0u, 0u};   // key-side class masks of this slice: is_prefix, context, in_span
+    uint32_t kd_pre[CPT];
+    uint32_t tb_pre[3][CPT];   // key-side class masks of the chunks: is_prefix, context, in_span
+#pragma unroll
+    for (int cc = 0; cc < CPT; ++cc) { kd_pre[cc] = 0u; tb_pre[0][cc] = 0u; tb_pre[1][cc] = 0u; tb_pre[2][cc] = 0u; }
     auto prefetch_kd = [&](uint32_t entry) {
       if ((entry >> 8) == KD_TILE_PARTIAL) {
         const uint32_t ktile = entry & 0xFFu;
-        kd_pre = a.desc[(size_t)b * a.Tpad + (size_t)ktile * KD_TILE + i * 64 + sub * 32 + lane];
         const uint32_t* tbp = a.tilebits + ((size_t)b * a.NT + ktile) * 32;
-        tb_pre[0] = tbp[4 * TB_PRE + tbw];
-        tb_pre[1] = tbp[4 * TB_CTX + tbw];
-        tb_pre[2] = tbp[4 * TB_INS + tbw];
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) {
+          kd_pre[cc] = a.desc[(size_t)b * a.Tpad + (size_t)ktile * KD_TILE + i * 64 + (c0 + cc) * 32 + lane];
+          tb_pre[0][cc] = tbp[4 * TB_PRE + tbw + cc];
+          tb_pre[1][cc] = tbp[4 * TB_CTX + tbw + cc];
+          tb_pre[2][cc] = tbp[4 * TB_INS + tbw + cc];
+        }
       }
     };
     uint32_t ent_next = na > 0 ? sAct[0] : 0u;
@@ -363,7 +376,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     int buf = i % C::NBUF;
     uint32_t rnd = i / C::NBUF;
     const uint32_t sfull0 = smem_u32(&bar_s_full[0]), pfull0 = smem_u32(&bar_p_full[0]);
-    const uint32_t tcol = tbase + lane_base + sub * 32;   // this slice's columns inside a buffer
+    const uint32_t tcol = tbase + lane_base + c0 * 32;   // this thread's first chunk inside a buffer
 
     for (int hh = 0; hh < nh && ok; ++hh) {
       const int h = h0 + hh;
@@ -375,20 +388,26 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       for (int e = 0; e < na; ++e) {
         const uint32_t ent = ent_next;
         const uint32_t cls = ent >> 8;
-        uint32_t mk = 0xFFFFFFFFu;   // visibility of this slice's 32 keys for this query row
+        uint32_t mk[CPT];   // visibility of the chunks' keys for this query row
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) mk[cc] = 0xFFFFFFFFu;
         if (cls == KD_TILE_PARTIAL) {
-          const int j0 = (ent & 0xFF) * KD_TILE + i * 64 + sub * 32;  // first key of this slice
+          const int j0 = (ent & 0xFF) * KD_TILE + i * 64 + c0 * 32;  // first key handled here
           __syncwarp();
-          kd_buf[lane] = kd_pre;
+#pragma unroll
+          for (int cc = 0; cc < CPT; ++cc) kd_buf[cc * 32 + lane] = kd_pre[cc];
           __syncwarp();
-          query_row_mask<1>(qd, qi, j0, tb_pre + 0, tb_pre + 1, tb_pre + 2, &mk);
-          if (tb_pre[2] != 0u && __any_sync(0xffffffffu, (qd & TD_SIDPOS) != 0u)) {
+          query_row_mask<CPT>(qd, qi, j0, tb_pre[0], tb_pre[1], tb_pre[2], mk);
+          uint32_t any_ins = 0u;
+#pragma unroll
+          for (int cc = 0; cc < CPT; ++cc) any_ins |= tb_pre[2][cc];
+          if (any_ins != 0u && __any_sync(0xffffffffu, (qd & TD_SIDPOS) != 0u)) {
             const uint32_t key = span_key_of_query(qd);
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
+            for (int j = 0; j < 32 * CPT; j += 4) {
               const uint4 k4 = *reinterpret_cast<const uint4*>(kd_buf + j);
-              mk |= (span_match_key(key, k4.x) << (j + 0)) | (span_match_key(key, k4.y) << (j + 1)) |
-                    (span_match_key(key, k4.z) << (j + 2)) | (span_match_key(key, k4.w) << (j + 3));
+              mk[j >> 5] |= (span_match_key(key, k4.x) << ((j + 0) & 31)) | (span_match_key(key, k4.y) << ((j + 1) & 31)) |
+                            (span_match_key(key, k4.z) << ((j + 2) & 31)) | (span_match_key(key, k4.w) << ((j + 3) & 31));
             }
           }
         }
@@ -405,11 +424,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tc_fence_after_sync();
         tr.ev(22);
 
-        uint32_t pk[16];
-        {
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) {
+          uint32_t pk[16];
           uint32_t rs[32], rp[32];
-          tmem_ld32(tS, rs);
-          tmem_ld32(tP, rp);
+          tmem_ld32(tS + cc * 32, rs);
+          tmem_ld32(tP + cc * 32, rp);
           tmem_wait_ld();
           if (cls != KD_TILE_PARTIAL) {   // warp-uniform: the common case carries no mask code at all
 #pragma unroll
@@ -423,14 +443,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             for (int j = 0; j < 32; j += 2) {
               float p0 = fast_exp2(fmaf(__uint_as_float(rs[j]), c, neg_lse));
               float p1 = fast_exp2(fmaf(__uint_as_float(rs[j + 1]), c, neg_lse));
-              if ((mk & (1u << j)) == 0u) p0 = 0.f;
-              if ((mk & (2u << j)) == 0u) p1 = 0.f;
+              if ((mk[cc] & (1u << j)) == 0u) p0 = 0.f;
+              if ((mk[cc] & (2u << j)) == 0u) p1 = 0.f;
               pk[j / 2] = pack2<kBf16>(p0 * (__uint_as_float(rp[j]) - delta), p1 * (__uint_as_float(rp[j + 1]) - delta));
             }
           }
+          // dS of the chunk as 16-bit A operand over the start of the scores it was made from (this thread's own row)
+          tmem_st16(tS + cc * 32, pk);
         }
         tr.ev(24);
-        tmem_st16(tS, pk);   // dS of this slice as 16-bit A operand over the scores it was made from (this thread's own row)
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(pfull0 + buf * 8);
@@ -440,29 +461,38 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       if (!ok) break;
 
-      // epilogue of this head: warpgroup g stores columns [g*HD/4, (g+1)*HD/4) of dQ
+      // epilogue of this head: warpgroup g stores EC columns of dQ from column g * EC
       if (na > 0) {
         ok = mbar_wait(smem_u32(&bar_acc_full), hh & 1, &abortf, a.status, W_Q_ACCFULL);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
       }
       tc_fence_after_sync();
-      constexpr int EC = HD / 4;
+      constexpr int EC = HD / (2 * C::NSUB);
+      constexpr int ECH = EC < 32 ? EC : 32;   // columns per TMEM load
       uint16_t* drow = reinterpret_cast<uint16_t*>(a.dq) + (size_t)b * a.dq_sb + (size_t)h * a.dq_sh + (size_t)qi * a.dq_st + g * EC;
-      uint32_t r[EC];
+      uint32_t r[EC / ECH][ECH];
       if (na > 0) {
-        if constexpr (EC == 16) tmem_ld16(tbase + lane_base + C::TM_ACC0 + g * EC, r);
-        else tmem_ld32(tbase + lane_base + C::TM_ACC0 + g * EC, r);
+#pragma unroll
+        for (int cb = 0; cb < EC / ECH; ++cb) {
+          if constexpr (ECH == 16) tmem_ld16(tbase + lane_base + C::TM_ACC0 + g * EC + cb * ECH, r[cb]);
+          else tmem_ld32(tbase + lane_base + C::TM_ACC0 + g * EC + cb * ECH, r[cb]);
+        }
         tmem_wait_ld();
         tc_fence_before_sync();
         mbar_arrive(smem_u32(&bar_acc_free));   // the next head's first product may overwrite the accumulator
       } else {
 #pragma unroll
-        for (int j = 0; j < EC; ++j) r[j] = 0u;
+        for (int cb = 0; cb < EC / ECH; ++cb)
+#pragma unroll
+          for (int j = 0; j < ECH; ++j) r[cb][j] = 0u;
       }
       if (q_valid) {
-        if constexpr (EC == 16) store_row16<kBf16>(drow, r, a.sm_scale);
-        else store_row32<kBf16>(drow, r, a.sm_scale);
+#pragma unroll
+        for (int cb = 0; cb < EC / ECH; ++cb) {
+          if constexpr (ECH == 16) store_row16<kBf16>(drow + cb * ECH, r[cb], a.sm_scale);
+          else store_row32<kBf16>(drow + cb * ECH, r[cb], a.sm_scale);
+        }
       }
     }
   }
@@ -480,7 +510,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 // Heads are handled one after the other as in the dQ kernel.
 // =========================================================================================
 template <int HD, bool kBf16>
-__global__ void __launch_bounds__(640, 1)
+__global__ void __launch_bounds__(BwdCfg<HD>::THREADS, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                      const BwdArgs a) {
@@ -516,11 +546,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
     for (int i = 0; i < C::NBUF; ++i) {
       mbar_init(smem_u32(&bar_s_full[i]), 2);     // one commit from each of the two M1 issuers
-      mbar_init(smem_u32(&bar_p_full[i]), 256);   // the two warpgroups that share the unit
+      mbar_init(smem_u32(&bar_p_full[i]), 128 * C::NSUB);   // the warpgroups that share the unit
       mbar_init(smem_u32(&bar_m2_issued[i]), 1);
     }
     mbar_init(smem_u32(&bar_acc_full), 1);
-    mbar_init(smem_u32(&bar_acc_free), 512);      // every compute thread has read its part of dK and dV
+    mbar_init(smem_u32(&bar_acc_free), 256 * C::NSUB);      // every compute thread has read its part of dK and dV
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -537,7 +567,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t tbase = tmem_base_s;
   const uint16_t* list = sList;
   Tracer tr;
-  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 3 || warp == 1 || warp == 4 || warp == 12),
+  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 3 || warp == 1 || warp == 4 || warp == 4 + 4 * C::NSUB),
           blockIdx.z * 4 + (warp == 3 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));   // issuers and one warp of each stream
   tr.ev(1);
   cta_trace(a.trace, 2);
@@ -667,44 +697,58 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
     }
   } else {
-    reg_alloc<KD_REGS_COMPUTE_BWD>();
+    reg_alloc<C::REGS_COMPUTE>();
     // ------------------------------ compute warpgroups ------------------------------
+    constexpr int CPT = C::CPT;      // 32-column chunks of a unit this thread handles
+    constexpr int QW = 32 * CPT;     // queries of a unit handled by this warp
     const int g = (warp - 4) >> 2;   // warpgroup
-    const int i = g >> 1;            // stream: query half (64 queries) of each query tile
-    const int sub = g & 1;           // 32-query slice of that half
+    const int i = g / C::NSUB;       // stream: query half (64 queries) of each query tile
+    const int c0 = (g % C::NSUB) * CPT;   // first 32-query chunk of that half handled here
     const int wq = warp & 3;
     const int row = wq * 32 + lane;
     const int kj = kt * KD_TILE + row;   // this thread's key
     const bool k_valid = kj < a.T;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
-    uint32_t* st_buf = sStage + (size_t)(warp - 4) * C::STAGE_WORDS;  // [32 lse][32 delta][32 desc]
+    uint32_t* st_buf = sStage + (size_t)(warp - 4) * C::STAGE_WORDS;  // [QW lse][QW delta][QW desc]
     const float c = a.scale_log2;
     const uint32_t kdesc = a.desc[(size_t)b * a.Tpad + kj];
-    const int tbw = 2 * i + sub;     // this slice's word in the 128-bit class masks of a query tile
+    const int tbw = 2 * i + c0;      // first word of this thread's chunks in the 128-bit class masks of a query tile
     bool ok = true;
 
-    // LSE, delta and the descriptor of the next unit's 32 queries are fetched one unit ahead
+    // LSE, delta and the descriptors of the next unit's queries are fetched one unit ahead
     // into registers and handed to the warp through its shared-memory staging buffer
-    float pre_lse = 0.f, pre_delta = 0.f;
-    uint32_t pre_desc = 0u;
+    float pre_lse[CPT], pre_delta[CPT];
+    uint32_t pre_desc[CPT];
     // query-side class masks of the next unit: sees-prefix, sees-context, sees-in_span, context, same-span armed
-    uint32_t tb_pre[5] = {0u, 0u, 0u, 0u, 0u};
+    uint32_t tb_pre[5][CPT];
+#pragma unroll
+    for (int cc = 0; cc < CPT; ++cc) {
+      pre_lse[cc] = 0.f; pre_delta[cc] = 0.f; pre_desc[cc] = 0u;
+#pragma unroll
+      for (int j = 0; j < 5; ++j) tb_pre[j][cc] = 0u;
+    }
     auto prefetch = [&](uint32_t entry, int h) {
       if ((entry >> 8) == KD_TILE_PARTIAL) {
         const uint32_t* tbp = a.tilebits + ((size_t)b * a.NT + (entry & 0xFFu)) * 32;
-        tb_pre[0] = tbp[4 * TB_SEES_PRE + tbw];
-        tb_pre[1] = tbp[4 * TB_SEES_CTX + tbw];
-        tb_pre[2] = tbp[4 * TB_SEES_INS + tbw];
-        tb_pre[3] = tbp[4 * TB_CTX + tbw];
-        tb_pre[4] = tbp[4 * TB_SIDPOS + tbw];
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) {
+          tb_pre[0][cc] = tbp[4 * TB_SEES_PRE + tbw + cc];
+          tb_pre[1][cc] = tbp[4 * TB_SEES_CTX + tbw + cc];
+          tb_pre[2][cc] = tbp[4 * TB_SEES_INS + tbw + cc];
+          tb_pre[3][cc] = tbp[4 * TB_CTX + tbw + cc];
+          tb_pre[4][cc] = tbp[4 * TB_SIDPOS + tbw + cc];
+        }
       }
       // a query at or beyond the sequence length reads the last row's scalars: its descriptor is 0,
       // so the tile is PARTIAL and the mask removes it
-      const int q = (entry & 0xFF) * KD_TILE + i * 64 + sub * 32 + lane;
-      const size_t r = ((size_t)b * a.H + h) * a.T + min(q, a.T - 1);
-      pre_lse = a.lse[r];   // negated where it is used: a negation here would wait for the load
-      pre_delta = a.delta[r];
-      pre_desc = a.desc[(size_t)b * a.Tpad + q];
+#pragma unroll
+      for (int cc = 0; cc < CPT; ++cc) {
+        const int q = (entry & 0xFF) * KD_TILE + i * 64 + (c0 + cc) * 32 + lane;
+        const size_t r = ((size_t)b * a.H + h) * a.T + min(q, a.T - 1);
+        pre_lse[cc] = a.lse[r];   // negated where it is used: a negation here would wait for the load
+        pre_delta[cc] = a.delta[r];
+        pre_desc[cc] = a.desc[(size_t)b * a.Tpad + q];
+      }
     };
     uint32_t ent_next = n > 0 ? list[0] : 0u;
     if (n > 0) prefetch(ent_next, h0);
@@ -712,7 +756,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     int buf = i % C::NBUF;
     uint32_t rnd = i / C::NBUF;
     const uint32_t sfull0 = smem_u32(&bar_s_full[0]), pfull0 = smem_u32(&bar_p_full[0]);
-    const uint32_t tcol = tbase + lane_base + sub * 32;   // this slice's columns inside a buffer
+    const uint32_t tcol = tbase + lane_base + c0 * 32;   // this thread's first chunk inside a buffer
 
     for (int hh = 0; hh < nh && ok; ++hh) {
       const int h = h0 + hh;
@@ -721,22 +765,30 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const uint32_t cls = ent >> 8;
         tr.ev(20);
         __syncwarp();
-        st_buf[lane] = __float_as_uint(pre_lse);
-        st_buf[32 + lane] = __float_as_uint(pre_delta);
-        st_buf[64 + lane] = pre_desc;
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) {
+          st_buf[cc * 32 + lane] = __float_as_uint(pre_lse[cc]);
+          st_buf[QW + cc * 32 + lane] = __float_as_uint(pre_delta[cc]);
+          st_buf[2 * QW + cc * 32 + lane] = pre_desc[cc];
+        }
         __syncwarp();
         tr.ev(41);
-        uint32_t mk = 0xFFFFFFFFu;   // visibility of this key for the slice's 32 queries
+        uint32_t mk[CPT];   // visibility of this key for the chunks' queries
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) mk[cc] = 0xFFFFFFFFu;
         if (cls == KD_TILE_PARTIAL) {
-          const int i0 = (ent & 0xFF) * KD_TILE + i * 64 + sub * 32;  // first query of this slice
-          key_row_mask<1>(kdesc, kj, i0, tb_pre + 0, tb_pre + 1, tb_pre + 2, tb_pre + 3, &mk);
-          if (tb_pre[4] != 0u && __any_sync(0xffffffffu, (kdesc & TD_INS) != 0u)) {
+          const int i0 = (ent & 0xFF) * KD_TILE + i * 64 + c0 * 32;  // first query handled here
+          key_row_mask<CPT>(kdesc, kj, i0, tb_pre[0], tb_pre[1], tb_pre[2], tb_pre[3], mk);
+          uint32_t any_armed = 0u;
+#pragma unroll
+          for (int cc = 0; cc < CPT; ++cc) any_armed |= tb_pre[4][cc];
+          if (any_armed != 0u && __any_sync(0xffffffffu, (kdesc & TD_INS) != 0u)) {
             const uint32_t key = span_key_of_key(kdesc);
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              const uint4 q4 = *reinterpret_cast<const uint4*>(st_buf + 64 + j);
-              mk |= (span_match_query(key, q4.x) << (j + 0)) | (span_match_query(key, q4.y) << (j + 1)) |
-                    (span_match_query(key, q4.z) << (j + 2)) | (span_match_query(key, q4.w) << (j + 3));
+            for (int j = 0; j < QW; j += 4) {
+              const uint4 q4 = *reinterpret_cast<const uint4*>(st_buf + 2 * QW + j);
+              mk[j >> 5] |= (span_match_query(key, q4.x) << ((j + 0) & 31)) | (span_match_query(key, q4.y) << ((j + 1) & 31)) |
+                            (span_match_query(key, q4.z) << ((j + 2) & 31)) | (span_match_query(key, q4.w) << ((j + 3) & 31));
             }
           }
         }
@@ -757,17 +809,18 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tc_fence_after_sync();
         tr.ev(22);
 
-        uint32_t pk_p[16], pk_ds[16];
-        {
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) {
+          uint32_t pk_p[16], pk_ds[16];
           uint32_t rs[32], rp[32];
-          tmem_ld32(tS, rs);
-          tmem_ld32(tP, rp);
+          tmem_ld32(tS + cc * 32, rs);
+          tmem_ld32(tP + cc * 32, rp);
           tmem_wait_ld();
           if (cls != KD_TILE_PARTIAL) {   // warp-uniform: the common case carries no mask code at all
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
-              const float4 l4 = *reinterpret_cast<const float4*>(st_buf + j);        // LSE of 4 queries
-              const float4 d4 = *reinterpret_cast<const float4*>(st_buf + 32 + j);   // delta of 4 queries
+              const float4 l4 = *reinterpret_cast<const float4*>(st_buf + cc * 32 + j);        // LSE of 4 queries
+              const float4 d4 = *reinterpret_cast<const float4*>(st_buf + QW + cc * 32 + j);   // delta of 4 queries
               const float lw[4] = {l4.x, l4.y, l4.z, l4.w}, dw[4] = {d4.x, d4.y, d4.z, d4.w};
               float pv[4], ds[4];
 #pragma unroll
@@ -782,14 +835,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           } else {
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
-              const float4 l4 = *reinterpret_cast<const float4*>(st_buf + j);
-              const float4 d4 = *reinterpret_cast<const float4*>(st_buf + 32 + j);
+              const float4 l4 = *reinterpret_cast<const float4*>(st_buf + cc * 32 + j);
+              const float4 d4 = *reinterpret_cast<const float4*>(st_buf + QW + cc * 32 + j);
               const float lw[4] = {l4.x, l4.y, l4.z, l4.w}, dw[4] = {d4.x, d4.y, d4.z, d4.w};
               float pv[4], ds[4];
 #pragma unroll
               for (int u2 = 0; u2 < 4; ++u2) {
                 pv[u2] = fast_exp2(fmaf(__uint_as_float(rs[j + u2]), c, -lw[u2]));
-                if ((mk & (1u << (j + u2))) == 0u) pv[u2] = 0.f;
+                if ((mk[cc] & (1u << (j + u2))) == 0u) pv[u2] = 0.f;
               }
 #pragma unroll
               for (int u2 = 0; u2 < 4; ++u2) ds[u2] = pv[u2] * (__uint_as_float(rp[j + u2]) - dw[u2]);
@@ -799,10 +852,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
               pk_ds[j / 2 + 1] = pack2<kBf16>(ds[2], ds[3]);
             }
           }
+          tmem_st16(tS + cc * 32, pk_p);    // P^T of the chunk over the start of the scores it was made from
+          tmem_st16(tP + cc * 32, pk_ds);   // dS^T of the chunk over the start of its dP^T
         }
         tr.ev(24);
-        tmem_st16(tS, pk_p);    // P^T of this slice over the scores it was made from
-        tmem_st16(tP, pk_ds);   // dS^T of this slice over its dP^T
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(pfull0 + buf * 8);
@@ -812,7 +865,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       if (!ok) break;
 
-      // epilogue of this head: warpgroup g stores columns [g*HD/4, (g+1)*HD/4) of dK and dV
+      // epilogue of this head: warpgroup g stores EC columns of dK and dV from column g * EC
       if (n > 0) {
         ok = mbar_wait(smem_u32(&bar_acc_full), hh & 1, &abortf, a.status, W_K_ACCFULL);
         ok = __all_sync(0xffffffffu, ok);
@@ -820,32 +873,38 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       tr.ev(30);
       tc_fence_after_sync();
-      constexpr int EC = HD / 4;
+      constexpr int EC = HD / (2 * C::NSUB);
+      constexpr int ECH = EC < 32 ? EC : 32;   // columns per TMEM load
       uint16_t* krow = reinterpret_cast<uint16_t*>(a.dk) + (size_t)b * a.dk_sb + (size_t)h * a.dk_sh + (size_t)kj * a.dk_st + g * EC;
       uint16_t* vrow = reinterpret_cast<uint16_t*>(a.dv) + (size_t)b * a.dv_sb + (size_t)h * a.dv_sh + (size_t)kj * a.dv_st + g * EC;
-      uint32_t rk[EC], rv[EC];
-      if (n > 0) {
-        if constexpr (EC == 16) {
-          tmem_ld16(tbase + lane_base + C::TM_ACC0 + g * EC, rk);
-          tmem_ld16(tbase + lane_base + C::TM_ACC1 + g * EC, rv);
-        } else {
-          tmem_ld32(tbase + lane_base + C::TM_ACC0 + g * EC, rk);
-          tmem_ld32(tbase + lane_base + C::TM_ACC1 + g * EC, rv);
-        }
-        tmem_wait_ld();
-        tc_fence_before_sync();
-        mbar_arrive(smem_u32(&bar_acc_free));   // the next head's first products may overwrite the accumulators
-      } else {
 #pragma unroll
-        for (int j = 0; j < EC; ++j) { rk[j] = 0u; rv[j] = 0u; }
-      }
-      if (k_valid) {
-        if constexpr (EC == 16) {
-          store_row16<kBf16>(krow, rk, a.sm_scale);
-          store_row16<kBf16>(vrow, rv, 1.0f);
+      for (int cb = 0; cb < EC / ECH; ++cb) {
+        uint32_t rk[ECH], rv[ECH];
+        if (n > 0) {
+          if constexpr (ECH == 16) {
+            tmem_ld16(tbase + lane_base + C::TM_ACC0 + g * EC + cb * ECH, rk);
+            tmem_ld16(tbase + lane_base + C::TM_ACC1 + g * EC + cb * ECH, rv);
+          } else {
+            tmem_ld32(tbase + lane_base + C::TM_ACC0 + g * EC + cb * ECH, rk);
+            tmem_ld32(tbase + lane_base + C::TM_ACC1 + g * EC + cb * ECH, rv);
+          }
+          tmem_wait_ld();
+          if (cb == EC / ECH - 1) {
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&bar_acc_free));   // the next head's first products may overwrite the accumulators
+          }
         } else {
-          store_row32<kBf16>(krow, rk, a.sm_scale);
-          store_row32<kBf16>(vrow, rv, 1.0f);
+#pragma unroll
+          for (int j = 0; j < ECH; ++j) { rk[j] = 0u; rv[j] = 0u; }
+        }
+        if (k_valid) {
+          if constexpr (ECH == 16) {
+            store_row16<kBf16>(krow + cb * ECH, rk, a.sm_scale);
+            store_row16<kBf16>(vrow + cb * ECH, rv, 1.0f);
+          } else {
+            store_row32<kBf16>(krow + cb * ECH, rk, a.sm_scale);
+            store_row32<kBf16>(vrow + cb * ECH, rv, 1.0f);
+          }
         }
       }
     }
@@ -893,9 +952,9 @@ static int launch_bwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
     const int rows_per_block = 256 / (HD / 8);
     const int blocks = static_cast<int>(std::min<size_t>((rows + rows_per_block - 1) / rows_per_block, size_t(148) * 32));
     attn_bwd_delta_kernel<HD, kBf16><<<blocks, 256, 0, stream>>>(a);
-    kq<<<grid, 640, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
+    kq<<<grid, C::THREADS, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
   }
-  if (phases & 2) kk<<<grid, 640, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
+  if (phases & 2) kk<<<grid, C::THREADS, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "attn_bwd kernels launch: %s", cudaGetErrorString(e));
   return 0;
