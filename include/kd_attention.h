@@ -101,9 +101,9 @@ typedef struct kd_attn_params {
   float* delta;      /* (B,H,T) contiguous fp32 scratch of the backward: rowsum(O * dO)
                         (kd_workspace_bytes gives its size) */
   const void* plan;  /* filled by kd_classify for the same (B,T) */
-  int32_t bwd_phases; /* kd_attn_bwd only. 0 or 3: both kernels; 1: the dQ kernel alone (it also
-                         writes delta); 2: the dK/dV kernel alone (reads delta of an earlier dQ
-                         pass). Lets a caller time the two kernels separately. */
+  int32_t bwd_phases; /* kd_attn_bwd only. 0 or 3: all kernels; 1: the delta kernel and the dQ
+                         kernel; 2: the dK/dV kernel alone (reads delta of an earlier pass 1).
+                         Lets a caller time the two large kernels separately. */
 } kd_attn_params;
 
 /* Size and layout of a plan for B sequences of T tokens. */

@@ -271,6 +271,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         ok = mbar_wait(smem_u32(&bar_fix_full[fb]), (hh / C::NFIX) & 1, &abortf, a.status, W_Q_FIXFULL);
         if (!ok) break;
         const uint32_t loA = desc_lo_kmajor(sFix + fb * 2 * C::TILE_BYTES + (dp_part ? C::TILE_BYTES : 0));   // dO or Q
+        uint64_t adesc[HD / 16];   // A descriptors of the head's k-steps
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) adesc[kk] = (static_cast<uint64_t>(hi) << 32) | (loA + koff_kmajor(kk));
         for (int u = 0; u < U && ok; ++u) {
           const int i = u & 1;
           if (round > 0) {   // buffer free once M2 of its previous unit has been issued
@@ -285,9 +288,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           // key rows 64i.. of K (scores) or V (dP)
           const uint32_t bdesc = loRingK + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4) + (dp_part ? (C::TILE_BYTES >> 4) : 0);
           const uint32_t dst = tbase + buf * 128 + (dp_part ? 64 : 0);
+          mma_ss_a64<false>(dst, adesc[0], bdesc, hi, idesc_m1);
 #pragma unroll
-          for (int kk = 0; kk < HD / 16; ++kk)
-            mma_ss_split(dst, loA + koff_kmajor(kk), bdesc + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
+          for (int kk = 1; kk < HD / 16; ++kk) mma_ss_a64<true>(dst, adesc[kk], bdesc + koff_kmajor(kk), hi, idesc_m1);
           mma_commit(smem_u32(&bar_s_full[buf]));
           tr.ev(15);
           if (++buf == C::NBUF) { buf = 0; ++round; }
@@ -631,6 +634,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         ok = mbar_wait(smem_u32(&bar_fix_full[fb]), (hh / C::NFIX) & 1, &abortf, a.status, W_K_FIXFULL);
         if (!ok) break;
         const uint32_t loA = desc_lo_kmajor(sFix + fb * 2 * C::TILE_BYTES + (dp_part ? C::TILE_BYTES : 0));   // V or K
+        uint64_t adesc[HD / 16];   // A descriptors of the head's k-steps
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) adesc[kk] = (static_cast<uint64_t>(hi) << 32) | (loA + koff_kmajor(kk));
         for (int u = 0; u < U && ok; ++u) {
           const int i = u & 1;
           if (round > 0) {   // buffer free once M2 of its previous unit has been issued
@@ -645,9 +651,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           // query rows 64i.. of Q (scores) or dO (dP)
           const uint32_t bdesc = loRingK + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4) + (dp_part ? (C::TILE_BYTES >> 4) : 0);
           const uint32_t dst = tbase + buf * 128 + (dp_part ? 64 : 0);
+          mma_ss_a64<false>(dst, adesc[0], bdesc, hi, idesc_m1);
 #pragma unroll
-          for (int kk = 0; kk < HD / 16; ++kk)
-            mma_ss_split(dst, loA + koff_kmajor(kk), bdesc + koff_kmajor(kk), hi, idesc_m1, kk > 0 ? 1u : 0u);
+          for (int kk = 1; kk < HD / 16; ++kk) mma_ss_a64<true>(dst, adesc[kk], bdesc + koff_kmajor(kk), hi, idesc_m1);
           mma_commit(smem_u32(&bar_s_full[buf]));
           tr.ev(15);
           if (++buf == C::NBUF) { buf = 0; ++round; }

@@ -52,6 +52,22 @@ __device__ __forceinline__ void mma_ss_split(uint32_t d_tmem, uint32_t alo, uint
       ::"r"(d_tmem), "r"(alo), "r"(blo), "r"(hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// SS product whose A descriptor is already a 64-bit value (precomputed per k-step outside the unit
+// loop) and whose accumulate flag is a compile-time constant: two instructions less per MMA for the
+// issuing thread
+template <bool kAccumulate>
+__device__ __forceinline__ void mma_ss_a64(uint32_t d_tmem, uint64_t adesc, uint32_t blo, uint32_t hi, uint32_t idesc) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 db;\n"
+      "mov.b64 db, {%2, %3};\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, db, %4, p;\n"
+      "}\n"
+      ::"r"(d_tmem), "l"(adesc), "r"(blo), "r"(hi), "r"(idesc), "n"(kAccumulate ? 1 : 0)
+      : "memory");
+}
 __device__ __forceinline__ void mma_ts_split(uint32_t d_tmem, uint32_t a_tmem, uint32_t blo, uint32_t hi,
                                              uint32_t idesc, uint32_t accumulate) {
   asm volatile(

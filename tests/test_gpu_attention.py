@@ -259,3 +259,26 @@ def test_host_pipeline_matches_direct_call():
     o.backward(hdo.to(DEV))
     for got, ref in zip(outs, (o, q.grad, k.grad, v.grad)):
         assert torch.equal(got, ref.cpu())
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_backward_phases_and_delta_scratch(D):
+    """kd_attn_bwd with bwd_phases 1 (delta + dQ) then 2 (dK/dV) equals one call with both; the
+    delta scratch holds rowsum(O * dO) (original_kernel.py:629-710)."""
+    from kerneldev_b200.original_kernel import _backward, _forward
+    from kerneldev_b200.plan import get_plan
+    B, H, T = 2, 3, 333
+    ins, sid, pre, lens = ao.batch_metadata(11, B, T, prefix=(8, 40), context=(64, 150), n_spans=(1, 4), span_len=(8, 30))
+    plan = get_plan(B, T, torch.device(DEV), _t(ins, torch.bool), _t(sid, torch.int64), _t(pre, torch.bool), _t(lens, torch.int32), True, True)
+    q, k, v, do = (x.to(DEV) for x in rand_inputs(B, H, T, D, torch.bfloat16, seed=3))
+    o, lse = _forward(q, k, v, plan, D ** -0.5)
+    ref = [x.clone() for x in _backward(q, k, v, o, lse, do, plan, D ** -0.5)]
+    bufs = (torch.zeros_like(q), torch.zeros_like(q), torch.zeros_like(q), torch.zeros((B, H, T), dtype=torch.float32, device=DEV))
+    _backward(q, k, v, o, lse, do, plan, D ** -0.5, 1, bufs)
+    torch.cuda.synchronize()
+    assert torch.equal(bufs[0], ref[0]) and not bufs[1].any() and not bufs[2].any()
+    want = (o.float() * do.float()).sum(-1)
+    assert torch.allclose(bufs[3], want, atol=1e-4, rtol=1e-5)
+    _backward(q, k, v, o, lse, do, plan, D ** -0.5, 2, bufs)
+    torch.cuda.synchronize()
+    assert torch.equal(bufs[1], ref[1]) and torch.equal(bufs[2], ref[2])
