@@ -238,6 +238,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 3 || warp == 1 || warp == 4 || warp == 8),
           blockIdx.z * 4 + (warp == 3 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));
   tr.ev(1);
+  tr.acc_init();
 
   if (warp < 4) {
     reg_dealloc<KD_REGS_ISSUE>();
@@ -312,16 +313,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         ok = mbar_wait(smem_u32(&bar_q_full[qb]), (hh / C::NQ) & 1, &abortf, a.status, W_F_QFULL);
         const uint32_t q_off = qb * (2 * C::TILE_BYTES >> 4);
         for (int u = 0; u < U && ok; ++u) {
+          tr.tb();
           const uint4 c = sCmd[2 * u];
           if (round > 0) {
             // the buffer is free once P V of the unit that used it in the previous round has been issued
             ok = mbar_wait(smem_u32(&bar_pv_issued[buf]), (round - 1) & 1, &abortf, a.status, W_F_PVISSUED);
             if (!ok) break;
           }
+          tr.te(1);
           if (c.z & CMD_WAIT) {
             ok = mbar_wait(smem_u32(&bar_k_full[kstage]), kparity, &abortf, a.status, W_F_KFULL);
             if (!ok) break;
           }
+          tr.te(2);
           tc_fence_after_sync();
           const uint32_t d = tbase + buf * 128;
           const uint32_t qlo = c.x + q_off, klo = c.y + kstage * (C::TILE_BYTES >> 4);
@@ -334,6 +338,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (++kstage == C::KST) { kstage = 0; kparity ^= 1; }
           }
           tr.ev(15);
+          tr.te(3);
           if (++buf == C::NBUF) {
             buf = 0;
             ++round;
@@ -350,9 +355,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       uint32_t round_parity = 0, vparity = 0;
       for (int hh = 0; hh < nh && ok; ++hh) {
         for (int u = 0; u < U && ok; ++u) {
+          tr.tb();
           const uint4 c = sCmd[2 * u + 1];
           ok = mbar_wait(smem_u32(&bar_p_full[buf]), round_parity, &abortf, a.status, W_F_PFULL);
           if (!ok) break;
+          tr.te(1);
           tr.ev(10);
           if (c.z & CMD_WAIT) {
             ok = mbar_wait(smem_u32(&bar_v_full[vstage]), vparity, &abortf, a.status, W_F_VFULL);
@@ -366,6 +373,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             ok = mbar_wait(smem_u32(&bar_o_free[i]), (hh - 1) & 1, &abortf, a.status, W_F_OFREE);
             if (!ok) break;
           }
+          tr.te(2);
           tc_fence_after_sync();
           const uint32_t dO = tbase + C::TM_O0 + i * HD, aP = tbase + buf * 128;
           const uint32_t vlo = c.y + vstage * (C::TILE_BYTES >> 4);
@@ -381,6 +389,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tc_fence_before_sync();
           mbar_arrive(smem_u32(&bar_pv_issued[buf]));
           tr.ev(11);
+          tr.te(3);
           if (++buf == C::NBUF) {
             buf = 0;
             round_parity ^= 1;
@@ -433,6 +442,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint32_t sfull_par = 0;     // bit j: parity of the next phase of this tile's score barrier on buffer j
     int pv_seen = 0;            // P V products of this query tile issued so far (phases of bar_pv_done[i])
 
+    tr.tb();
     for (int hh = 0; hh < nh && ok; ++hh) {
     const int h = h0 + hh;
     float m = -INFINITY, l = 0.f;
@@ -459,12 +469,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         prefetch_kd(cmd_next);
       }
       tr.ev(21);
+      tr.te(7);
       ok = mbar_wait(smem_u32(&bar_s_full[2 * buf + i]), (sfull_par >> buf) & 1u, &abortf, a.status, W_F_SFULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       sfull_par ^= 1u << buf;
       tc_fence_after_sync();
       tr.ev(22);
+      tr.te(1);
 
       float s[KD_TILE];
 #pragma unroll
@@ -476,6 +488,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       tmem_wait_ld();
       tr.ev(23);
+      tr.te(2);
       if (cls == KD_TILE_PARTIAL) {
         // The row's 128-bit visibility mask comes from the tile's class masks with a few word-wide
         // operations; only the "same span" term needs the individual key descriptors.
@@ -499,6 +512,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           if ((mk[j >> 5] & (1u << (j & 31))) == 0u) s[j] = -INFINITY;
         tr.ev(28);
       }
+      tr.te(3);
       // four independent chains for the row maximum and for the row sum: a single chain of 127
       // dependent operations would be latency-bound
       float mx4[4] = {s[0], s[1], s[2], s[3]};
@@ -536,6 +550,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       tr.ev(32);
+      tr.te(4);
       l = l * alpha + sum;
       m = m_new;
 #pragma unroll
@@ -553,6 +568,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!ok) break;
       }
       tr.ev(33);
+      tr.te(5);
       if (__any_sync(0xffffffffu, need_rescale)) {
         tc_fence_after_sync();
         const float f = need_rescale ? alpha : 1.f;
@@ -571,6 +587,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&bar_p_full[buf]));
       tr.ev(25);
+      tr.te(6);
       ++nact;
       ++pv_seen;
     }
@@ -613,6 +630,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 
   tr.ev(31);
+  tr.flush();
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tbase, 512);
