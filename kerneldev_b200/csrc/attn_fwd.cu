@@ -54,13 +54,21 @@ struct FwdCfg {
   static constexpr int SMEM_Q = 0;
   static constexpr int SMEM_K = SMEM_Q + NQ * 2 * TILE_BYTES;
   static constexpr int SMEM_V = SMEM_K + KST * TILE_BYTES;
-  static constexpr int SMEM_KDESC = SMEM_V + VST * TILE_BYTES;     // 8 warps x 128 u32
+  static constexpr int SMEM_KDESC = SMEM_V + VST * TILE_BYTES;     // per softmax warp: the descriptors of its keys (4 KB in all)
   static constexpr int SMEM_LIST = SMEM_KDESC + 8 * KD_TILE * 4;   // the pair's work list (<= 128 entries)
   static constexpr int SMEM_UNITS = SMEM_LIST + 128 * 2;           // unit list (<= 256 units)
   static constexpr int SMEM_CMD = SMEM_UNITS + 256 * 2;            // 256 x {S command, P V command} (uint4 each)
   static constexpr int SMEM_WCMD = SMEM_CMD + 256 * 2 * 16;        // 2 x 256 softmax commands (u32 each)
-  static constexpr int SMEM_TOTAL = SMEM_WCMD + 2 * 256 * 4;
+  static constexpr int SMEM_XCHG = SMEM_WCMD + 2 * 256 * 4;        // row maxima / row sums exchanged between the warpgroups of a tile
+  static constexpr int SMEM_TOTAL = SMEM_XCHG + 2 * 2 * 2 * KD_TILE * 4;   // [tile][slot][half][row]
   static constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;   // slack for 1024-byte alignment
+#ifndef KD_FWD_NSUB
+#define KD_FWD_NSUB 1
+#endif
+  static constexpr int NSUB = KD_FWD_NSUB;               // softmax warpgroups per query tile (1 or 2)
+  static constexpr int CW = KD_TILE / NSUB;              // score columns per softmax thread
+  static constexpr int THREADS = 128 + 256 * NSUB;
+  static constexpr int REGS_COMPUTE = (NSUB == 2) ? KD_REGS_COMPUTE_BWD : KD_REGS_COMPUTE;
   // TMEM columns: NBUF score buffers of 128, then O0 and O1 (HD each)
   static constexpr uint32_t TM_O0 = NBUF * 128, TM_O1 = NBUF * 128 + HD;
   static_assert(TM_O1 + HD <= 512, "TMEM budget");
@@ -82,11 +90,11 @@ __device__ __forceinline__ int wcmd_buf(uint32_t c) { return (c >> 10) & 3; }
 // wait-site codes reported in the status word
 enum : uint32_t {
   W_F_QFULL = 0x101, W_F_KEMPTY = 0x102, W_F_VEMPTY = 0x103, W_F_KFULL = 0x104, W_F_VFULL = 0x105,
-  W_F_PFULL = 0x106, W_F_SFULL = 0x107, W_F_PVDONE = 0x108, W_F_PVISSUED = 0x109, W_F_QEMPTY = 0x10A, W_F_OFREE = 0x10B,
+  W_F_PFULL = 0x106, W_F_SFULL = 0x107, W_F_PVDONE = 0x108, W_F_PVISSUED = 0x109, W_F_QEMPTY = 0x10A, W_F_OFREE = 0x10B, W_F_XCHG = 0x10C,
 };
 
 template <int HD, bool kBf16>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(FwdCfg<HD>::THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const FwdArgs a) {
   using C = FwdCfg<HD>;
@@ -103,7 +111,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   __shared__ __align__(8) uint64_t bar_q_full[C::NQ], bar_q_empty[C::NQ], bar_k_full[C::KST], bar_k_empty[C::KST],
       bar_v_full[C::VST], bar_v_empty[C::VST], bar_s_full[2 * C::NBUF], bar_p_full[C::NBUF], bar_pv_issued[C::NBUF],
-      bar_pv_done[2], bar_o_free[2];
+      bar_pv_done[2], bar_o_free[2], bar_xchg[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int n_units_s, n_own_s[2];
   __shared__ AbortFlag abortf;
@@ -135,13 +143,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // phase of the barriers it waits on, which is what makes a parity wait sound
       mbar_init(smem_u32(&bar_s_full[2 * s]), 1);
       mbar_init(smem_u32(&bar_s_full[2 * s + 1]), 1);
-      mbar_init(smem_u32(&bar_p_full[s]), 128);
+      mbar_init(smem_u32(&bar_p_full[s]), 128 * C::NSUB);
       mbar_init(smem_u32(&bar_pv_issued[s]), 1);
     }
     mbar_init(smem_u32(&bar_pv_done[0]), 1);
     mbar_init(smem_u32(&bar_pv_done[1]), 1);
-    mbar_init(smem_u32(&bar_o_free[0]), 128);
-    mbar_init(smem_u32(&bar_o_free[1]), 128);
+    mbar_init(smem_u32(&bar_xchg[0]), 256);   // both warpgroups of a tile have published their half-row value
+    mbar_init(smem_u32(&bar_xchg[1]), 256);
+    mbar_init(smem_u32(&bar_o_free[0]), 128 * C::NSUB);
+    mbar_init(smem_u32(&bar_o_free[1]), 128 * C::NSUB);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -235,7 +245,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tbase = tmem_base_s;
   const int U = n_units_s;
   Tracer tr;
-  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 3 || warp == 1 || warp == 4 || warp == 8),
+  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 3 || warp == 1 || warp == 4 || warp == 4 + 4 * C::NSUB),
           blockIdx.z * 4 + (warp == 3 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));
   tr.ev(1);
   tr.acc_init();
@@ -378,8 +388,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           const uint32_t dO = tbase + C::TM_O0 + i * HD, aP = tbase + buf * 128;
           const uint32_t vlo = c.y + vstage * (C::TILE_BYTES >> 4);
 #pragma unroll
-          for (int kk = 0; kk < KD_TILE / 16; ++kk)
-            mma_ts_split(dO, aP + kk * 8, vlo + koff_mnmajor(kk), hi, idesc_o, kk > 0 ? 1u : acc0);
+          for (int kk = 0; kk < KD_TILE / 16; ++kk) {
+            // P of 16 keys = 8 packed columns; each softmax warpgroup writes its keys at the start of its own score columns
+            const uint32_t pcol = (C::NSUB == 2) ? (kk >> 2) * 64 + (kk & 3) * 8 : kk * 8;
+            mma_ts_split(dO, aP + pcol, vlo + koff_mnmajor(kk), hi, idesc_o, kk > 0 ? 1u : acc0);
+          }
           mma_commit(smem_u32(&bar_pv_done[i]));
           if (c.z & CMD_RELEASE) {
             mma_commit(smem_u32(&bar_v_empty[vstage]));
@@ -398,17 +411,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
   } else {
-    reg_alloc<KD_REGS_COMPUTE>();
+    reg_alloc<C::REGS_COMPUTE>();
     // ------------------------------ softmax warpgroups ------------------------------
-    const int i = (warp - 4) >> 2;        // query tile of the pair
+    // NSUB warpgroups share a query tile; each thread owns one row and CW of its 128 score columns.
+    // With two warpgroups per tile the row maximum (per unit) and the row sum (per head) are
+    // exchanged through shared memory and a named barrier of the two warpgroups.
+    constexpr int NS = C::NSUB, CW = C::CW, NW = CW / 32;
+    const int g = (warp - 4) >> 2;        // warpgroup
+    const int i = g / NS;                 // query tile of the pair
+    const int sub = g % NS;               // which CW columns of a unit
     const int wq = warp & 3;              // TMEM lane quadrant of this warp
     const int row = wq * 32 + lane;       // row inside the tile
     const int qtile = 2 * pair + i;
     const int qi = qtile * KD_TILE + row;  // token index of this thread's query
     const bool tile_valid = qtile < a.NT;
-    uint32_t* kd_buf = sKdesc + (size_t)(warp - 4) * KD_TILE;   // this warp's copy of a key tile's descriptors
+    uint32_t* kd_buf = sKdesc + (size_t)(warp - 4) * CW;   // this warp's copy of its keys' descriptors
+    float* xchg = reinterpret_cast<float*>(smem + C::SMEM_XCHG) + i * (2 * 2 * KD_TILE);   // [slot][half][row]
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
-    const uint32_t tO = tbase + lane_base + (i == 0 ? C::TM_O0 : C::TM_O1);
+    const uint32_t tO = tbase + lane_base + (i == 0 ? C::TM_O0 : C::TM_O1) + sub * (HD / NS);   // this thread's share of O
     const float c = a.scale_log2;
 
     const uint32_t qd = tile_valid ? a.desc[(size_t)b * a.Tpad + qi] : 0u;
@@ -418,20 +438,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // global-memory latency overlaps the previous tile's softmax.
     const int n_own = n_own_s[i];
     const uint32_t* wcmd = sWcmd + i * 256;
-    uint32_t kd_pre[4] = {0u, 0u, 0u, 0u};
-    uint32_t tb_pre[12];   // key-side class masks of the tile: is_prefix[4], context[4], in_span[4]
+    uint32_t kd_pre[NW];
+    uint32_t tb_pre[3][NW];   // key-side class masks of this thread's columns: is_prefix, context, in_span
 #pragma unroll
-    for (int j = 0; j < 12; ++j) tb_pre[j] = 0u;
-    auto prefetch_kd = [&](uint32_t c) {
-      if (wcmd_class(c) == KD_TILE_PARTIAL) {
-        const uint32_t* src = a.desc + (size_t)b * a.Tpad + (size_t)wcmd_kt(c) * KD_TILE;
+    for (int w = 0; w < NW; ++w) { kd_pre[w] = 0u; tb_pre[0][w] = 0u; tb_pre[1][w] = 0u; tb_pre[2][w] = 0u; }
+    auto prefetch_kd = [&](uint32_t cmd) {
+      if (wcmd_class(cmd) == KD_TILE_PARTIAL) {
+        const uint32_t* src = a.desc + (size_t)b * a.Tpad + (size_t)wcmd_kt(cmd) * KD_TILE + sub * CW;
+        const uint32_t* tbp = a.tilebits + ((size_t)b * a.NT + wcmd_kt(cmd)) * 32 + sub * NW;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) kd_pre[j] = src[j * 32 + lane];
-        const uint4* tb = reinterpret_cast<const uint4*>(a.tilebits + ((size_t)b * a.NT + wcmd_kt(c)) * 32);
-#pragma unroll
-        for (int j = 0; j < 3; ++j) {
-          const uint4 v = tb[j];   // masks TB_PRE, TB_CTX, TB_INS
-          tb_pre[4 * j + 0] = v.x; tb_pre[4 * j + 1] = v.y; tb_pre[4 * j + 2] = v.z; tb_pre[4 * j + 3] = v.w;
+        for (int w = 0; w < NW; ++w) {
+          kd_pre[w] = src[w * 32 + lane];
+          tb_pre[0][w] = tbp[4 * TB_PRE + w];
+          tb_pre[1][w] = tbp[4 * TB_CTX + w];
+          tb_pre[2][w] = tbp[4 * TB_INS + w];
         }
       }
     };
@@ -441,6 +461,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     int buf_off = 0;            // (units of the heads done so far) mod NBUF: rotation of the buffers
     uint32_t sfull_par = 0;     // bit j: parity of the next phase of this tile's score barrier on buffer j
     int pv_seen = 0;            // P V products of this query tile issued so far (phases of bar_pv_done[i])
+    uint32_t xcnt = 0;          // exchanges so far: phase of bar_xchg[i] and slot (two slots, so that a fast warpgroup
+                                // cannot overwrite a value its partner has not read yet)
 
     tr.tb();
     for (int hh = 0; hh < nh && ok; ++hh) {
@@ -453,15 +475,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int kt = wcmd_kt(cmd);
       int buf = wcmd_buf(cmd) + buf_off;
       if (buf >= C::NBUF) buf -= C::NBUF;
-      const uint32_t tS = tbase + lane_base + buf * 128;
+      const uint32_t tS = tbase + lane_base + buf * 128 + sub * CW;
       tr.ev(20);
-      uint32_t tb[12];
+      uint32_t tb[3][NW];
       if (cls == KD_TILE_PARTIAL) {
         __syncwarp();
 #pragma unroll
-        for (int j = 0; j < 4; ++j) kd_buf[j * 32 + lane] = kd_pre[j];
-#pragma unroll
-        for (int j = 0; j < 12; ++j) tb[j] = tb_pre[j];
+        for (int w = 0; w < NW; ++w) {
+          kd_buf[w * 32 + lane] = kd_pre[w];
+          tb[0][w] = tb_pre[0][w]; tb[1][w] = tb_pre[1][w]; tb[2][w] = tb_pre[2][w];
+        }
         __syncwarp();
       }
       if (k + 1 < n_own || hh + 1 < nh) {   // the next head walks the same list again
@@ -478,29 +501,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tr.ev(22);
       tr.te(1);
 
-      float s[KD_TILE];
+      float sc[CW];
 #pragma unroll
-      for (int cb = 0; cb < 4; ++cb) {
+      for (int cb = 0; cb < NW; ++cb) {
         uint32_t r[32];
         tmem_ld32(tS + cb * 32, r);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) s[cb * 32 + j] = __uint_as_float(r[j]);
+        for (int j = 0; j < 32; ++j) sc[cb * 32 + j] = __uint_as_float(r[j]);
       }
       tmem_wait_ld();
       tr.ev(23);
       tr.te(2);
       if (cls == KD_TILE_PARTIAL) {
-        // The row's 128-bit visibility mask comes from the tile's class masks with a few word-wide
+        // The row's visibility mask comes from the tile's class masks with a few word-wide
         // operations; only the "same span" term needs the individual key descriptors.
-        const int j0 = kt * KD_TILE;
-        uint32_t mk[4];
-        query_row_mask<4>(qd, qi, j0, tb + 0, tb + 4, tb + 8, mk);
+        const int j0 = kt * KD_TILE + sub * CW;
+        uint32_t mk[NW];
+        query_row_mask<NW>(qd, qi, j0, tb[0], tb[1], tb[2], mk);
         tr.ev(26);
-        const bool tile_has_span_keys = (tb[8] | tb[9] | tb[10] | tb[11]) != 0u;
-        if (tile_has_span_keys && __any_sync(0xffffffffu, (qd & TD_SIDPOS) != 0u)) {
+        uint32_t any_ins = 0u;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) any_ins |= tb[2][w];
+        if (any_ins != 0u && __any_sync(0xffffffffu, (qd & TD_SIDPOS) != 0u)) {
           const uint32_t key = span_key_of_query(qd);
 #pragma unroll
-          for (int j = 0; j < KD_TILE; j += 4) {
+          for (int j = 0; j < CW; j += 4) {
             const uint4 k4 = *reinterpret_cast<const uint4*>(kd_buf + j);
             mk[j >> 5] |= (span_match_key(key, k4.x) << ((j + 0) & 31)) | (span_match_key(key, k4.y) << ((j + 1) & 31)) |
                           (span_match_key(key, k4.z) << ((j + 2) & 31)) | (span_match_key(key, k4.w) << ((j + 3) & 31));
@@ -508,22 +533,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         tr.ev(27);
 #pragma unroll
-        for (int j = 0; j < KD_TILE; ++j)
-          if ((mk[j >> 5] & (1u << (j & 31))) == 0u) s[j] = -INFINITY;
+        for (int j = 0; j < CW; ++j)
+          if ((mk[j >> 5] & (1u << (j & 31))) == 0u) sc[j] = -INFINITY;
         tr.ev(28);
       }
       tr.te(3);
-      // four independent chains for the row maximum and for the row sum: a single chain of 127
+      // four independent chains for the row maximum and for the row sum: a single chain of
       // dependent operations would be latency-bound
-      float mx4[4] = {s[0], s[1], s[2], s[3]};
+      float mx4[4] = {sc[0], sc[1], sc[2], sc[3]};
 #pragma unroll
-      for (int j = 4; j < KD_TILE; j += 4) {
-        mx4[0] = fmaxf(mx4[0], s[j + 0]);
-        mx4[1] = fmaxf(mx4[1], s[j + 1]);
-        mx4[2] = fmaxf(mx4[2], s[j + 2]);
-        mx4[3] = fmaxf(mx4[3], s[j + 3]);
+      for (int j = 4; j < CW; j += 4) {
+        mx4[0] = fmaxf(mx4[0], sc[j + 0]);
+        mx4[1] = fmaxf(mx4[1], sc[j + 1]);
+        mx4[2] = fmaxf(mx4[2], sc[j + 2]);
+        mx4[3] = fmaxf(mx4[3], sc[j + 3]);
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      if constexpr (NS == 2) {
+        // the other warpgroup of this tile holds the other half of the row
+        float* slot = xchg + (xcnt & 1u) * (2 * KD_TILE);
+        slot[sub * KD_TILE + row] = mx;
+        mbar_arrive(smem_u32(&bar_xchg[i]));
+        ok = mbar_wait(smem_u32(&bar_xchg[i]), xcnt & 1u, &abortf, a.status, W_F_XCHG);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        mx = fmaxf(mx, slot[(sub ^ 1) * KD_TILE + row]);
+        ++xcnt;
+      }
       // The running maximum is refreshed only when it would grow by more than 2^8 in the
       // exponent; until then the stale value is used consistently for P, l and O, which leaves
       // the normalised result unchanged and skips most O rescales.
@@ -534,13 +570,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const bool need_rescale = (nact > 0) && (m_new != m);
       const float neg_mc = -m_use * c;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t pk[KD_TILE / 2];
+      uint32_t pk[CW / 2];
 #pragma unroll
-      for (int j = 0; j < KD_TILE; j += 4) {
-        const float p0 = fast_exp2(fmaf(s[j], c, neg_mc));
-        const float p1 = fast_exp2(fmaf(s[j + 1], c, neg_mc));
-        const float p2 = fast_exp2(fmaf(s[j + 2], c, neg_mc));
-        const float p3 = fast_exp2(fmaf(s[j + 3], c, neg_mc));
+      for (int j = 0; j < CW; j += 4) {
+        const float p0 = fast_exp2(fmaf(sc[j], c, neg_mc));
+        const float p1 = fast_exp2(fmaf(sc[j + 1], c, neg_mc));
+        const float p2 = fast_exp2(fmaf(sc[j + 2], c, neg_mc));
+        const float p3 = fast_exp2(fmaf(sc[j + 3], c, neg_mc));
         sum4[0] += p0;
         sum4[1] += p1;
         sum4[2] += p2;
@@ -551,14 +587,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       tr.ev(32);
       tr.te(4);
-      l = l * alpha + sum;
+      l = l * alpha + sum;   // with two warpgroups per tile: the sum over this thread's columns only
       m = m_new;
 #pragma unroll
-      for (int cb = 0; cb < 2; ++cb) {
+      for (int cb = 0; cb < CW / 64; ++cb) {
         uint32_t r[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) r[j] = pk[cb * 32 + j];
-        tmem_st32(tS + cb * 32, r);   // P over the first 64 columns of this thread's own score row
+        tmem_st32(tS + cb * 32, r);   // P over the start of this thread's own score columns
       }
       if (nact > 0) {
         // O_i may be touched only after the previous P V product of this query tile has completed;
@@ -573,7 +609,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_after_sync();
         const float f = need_rescale ? alpha : 1.f;
 #pragma unroll
-        for (int cb = 0; cb < HD / 32; ++cb) {
+        for (int cb = 0; cb < HD / NS / 32; ++cb) {
           uint32_t r[32];
           tmem_ld32(tO + cb * 32, r);
           tmem_wait_ld();
@@ -595,21 +631,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     buf_off += U % C::NBUF;
     if (buf_off >= C::NBUF) buf_off -= C::NBUF;
 
-    // epilogue of this head: normalise, convert, store O and LSE
+    // epilogue of this head: normalise, convert, store this thread's share of O, and LSE
     if (nact > 0) {
       ok = mbar_wait(smem_u32(&bar_pv_done[i]), (pv_seen - 1) & 1, &abortf, a.status, W_F_PVDONE);
       ok = __all_sync(0xffffffffu, ok);
     }
     tr.ev(30);
-    if (ok && tile_valid && qi < a.T) {
+    if constexpr (NS == 2) {
+      // total row sum = the two halves' sums (both carry the same running maximum)
+      if (ok) {
+        float* slot = xchg + (xcnt & 1u) * (2 * KD_TILE);
+        slot[sub * KD_TILE + row] = l;
+        mbar_arrive(smem_u32(&bar_xchg[i]));
+        ok = mbar_wait(smem_u32(&bar_xchg[i]), xcnt & 1u, &abortf, a.status, W_F_XCHG);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) l += slot[(sub ^ 1) * KD_TILE + row];
+        ++xcnt;
+      }
+    }
+    if (ok && tile_valid && qi < a.T && sub == 0) {
       a.lse[((size_t)b * a.H + h) * a.T + qi] = (l > 0.f) ? (m * c + log2f(l)) : -INFINITY;
     }
     if (ok) {
       tc_fence_after_sync();
       const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
-      uint16_t* orow = reinterpret_cast<uint16_t*>(a.o) + (size_t)b * a.o_sb + (size_t)h * a.o_sh + (size_t)qi * a.o_st;
+      uint16_t* orow = reinterpret_cast<uint16_t*>(a.o) + (size_t)b * a.o_sb + (size_t)h * a.o_sh + (size_t)qi * a.o_st + sub * (HD / NS);
 #pragma unroll
-      for (int cb = 0; cb < HD / 32; ++cb) {
+      for (int cb = 0; cb < HD / NS / 32; ++cb) {
         uint32_t r[32];
         if (nact > 0) {
           tmem_ld32(tO + cb * 32, r);
@@ -618,8 +666,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
-        if (cb == HD / 32 - 1 && nact > 0) {
-          // O_i has been read out: the next head's first product may overwrite it
+        if (cb == HD / NS / 32 - 1 && nact > 0) {
+          // this thread's share of O_i has been read out: the next head's first product may overwrite it
           tc_fence_before_sync();
           mbar_arrive(smem_u32(&bar_o_free[i]));
         }
@@ -656,7 +704,7 @@ static int launch_fwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_ALLOC);
   if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "fwd smem attribute: %s", cudaGetErrorString(e));
   dim3 grid((p.H + a.G - 1) / a.G, p.B, L.NP);
-  kern<<<grid, 384, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, a);
+  kern<<<grid, C::THREADS, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "attn_fwd_kernel launch: %s", cudaGetErrorString(e));
   return 0;
