@@ -273,9 +273,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const uint32_t loA = desc_lo_kmajor(sFix + fb * 2 * C::TILE_BYTES + (dp_part ? C::TILE_BYTES : 0));   // dO or Q
         uint64_t adesc[HD / 16];   // A descriptors of the head's k-steps
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) adesc[kk] = (static_cast<uint64_t>(hi) << 32) | (loA + koff_kmajor(kk));
+        for (int kk = 0; kk < HD / 16; ++kk) adesc[kk] = desc64(loA + koff_kmajor(kk), hi);
         for (int u = 0; u < U && ok; ++u) {
           const int i = u & 1;
+          // operands of the unit, formed ahead of the waits
+          // key rows 64i.. of K (scores) or V (dP)
+          const uint32_t blo = loRingK + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4) + (dp_part ? (C::TILE_BYTES >> 4) : 0);
+          uint64_t bdesc[HD / 16];
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk) bdesc[kk] = desc64(blo + koff_kmajor(kk), hi);
+          const uint32_t dst = tbase + buf * 128 + (dp_part ? 64 : 0);
           if (round > 0) {   // buffer free once M2 of its previous unit has been issued
             ok = mbar_wait(smem_u32(&bar_m2_issued[buf]), (round - 1) & 1, &abortf, a.status, W_Q_M2ISSUED);
             if (!ok) break;
@@ -285,12 +292,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             if (!ok) break;
           }
           tc_fence_after_sync();
-          // key rows 64i.. of K (scores) or V (dP)
-          const uint32_t bdesc = loRingK + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4) + (dp_part ? (C::TILE_BYTES >> 4) : 0);
-          const uint32_t dst = tbase + buf * 128 + (dp_part ? 64 : 0);
-          mma_ss_a64<false>(dst, adesc[0], bdesc, hi, idesc_m1);
+          mma_ss64<false>(dst, adesc[0], bdesc[0], idesc_m1);
 #pragma unroll
-          for (int kk = 1; kk < HD / 16; ++kk) mma_ss_a64<true>(dst, adesc[kk], bdesc + koff_kmajor(kk), hi, idesc_m1);
+          for (int kk = 1; kk < HD / 16; ++kk) mma_ss64<true>(dst, adesc[kk], bdesc[kk], idesc_m1);
           mma_commit(smem_u32(&bar_s_full[buf]));
           tr.ev(15);
           if (++buf == C::NBUF) { buf = 0; ++round; }
@@ -315,15 +319,23 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         for (int u = 0; u < U && ok; ++u) {
           const int i = u & 1;
+          // operands of the unit, formed ahead of the wait
+          const uint32_t kb = loRingMN + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
+          const uint32_t aS = tbase + buf * 128;   // dS_u sits on top of S_u: keys 0-31 at columns [0,16), keys 32-63 at [32,48)
+          uint64_t bdesc[4];
+          uint32_t aop[4];
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {  // 64 keys of this unit, 16 per MMA
+            bdesc[kk] = desc64(kb + koff_mnmajor(kk), hi);
+            aop[kk] = aS + (kk >> 1) * 32 + (kk & 1) * 8;
+          }
           ok = mbar_wait(smem_u32(&bar_p_full[buf]), round_parity, &abortf, a.status, W_Q_PFULL);
           if (!ok) break;
           tr.ev(10);
           tc_fence_after_sync();
-          const uint32_t kb = loRingMN + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
-          const uint32_t aS = tbase + buf * 128;   // dS_u sits on top of S_u: keys 0-31 at columns [0,16), keys 32-63 at [32,48)
+          mma_ts64_p(tAcc, aop[0], bdesc[0], idesc_m2, u > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)  // 64 keys of this unit, 16 per MMA
-            mma_ts_split(tAcc, aS + (kk >> 1) * 32 + (kk & 1) * 8, kb + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 1; kk < 4; ++kk) mma_ts64<true>(tAcc, aop[kk], bdesc[kk], idesc_m2);
           if (i == 1) mma_commit(smem_u32(&bar_ring_empty[stage]));
           tc_fence_before_sync();
           mbar_arrive(smem_u32(&bar_m2_issued[buf]));
@@ -636,9 +648,16 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const uint32_t loA = desc_lo_kmajor(sFix + fb * 2 * C::TILE_BYTES + (dp_part ? C::TILE_BYTES : 0));   // V or K
         uint64_t adesc[HD / 16];   // A descriptors of the head's k-steps
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) adesc[kk] = (static_cast<uint64_t>(hi) << 32) | (loA + koff_kmajor(kk));
+        for (int kk = 0; kk < HD / 16; ++kk) adesc[kk] = desc64(loA + koff_kmajor(kk), hi);
         for (int u = 0; u < U && ok; ++u) {
           const int i = u & 1;
+          // operands of the unit, formed ahead of the waits
+          // query rows 64i.. of Q (scores) or dO (dP)
+          const uint32_t blo = loRingK + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4) + (dp_part ? (C::TILE_BYTES >> 4) : 0);
+          uint64_t bdesc[HD / 16];
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk) bdesc[kk] = desc64(blo + koff_kmajor(kk), hi);
+          const uint32_t dst = tbase + buf * 128 + (dp_part ? 64 : 0);
           if (round > 0) {   // buffer free once M2 of its previous unit has been issued
             ok = mbar_wait(smem_u32(&bar_m2_issued[buf]), (round - 1) & 1, &abortf, a.status, W_K_M2ISSUED);
             if (!ok) break;
@@ -648,12 +667,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             if (!ok) break;
           }
           tc_fence_after_sync();
-          // query rows 64i.. of Q (scores) or dO (dP)
-          const uint32_t bdesc = loRingK + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4) + (dp_part ? (C::TILE_BYTES >> 4) : 0);
-          const uint32_t dst = tbase + buf * 128 + (dp_part ? 64 : 0);
-          mma_ss_a64<false>(dst, adesc[0], bdesc, hi, idesc_m1);
+          mma_ss64<false>(dst, adesc[0], bdesc[0], idesc_m1);
 #pragma unroll
-          for (int kk = 1; kk < HD / 16; ++kk) mma_ss_a64<true>(dst, adesc[kk], bdesc + koff_kmajor(kk), hi, idesc_m1);
+          for (int kk = 1; kk < HD / 16; ++kk) mma_ss64<true>(dst, adesc[kk], bdesc[kk], idesc_m1);
           mma_commit(smem_u32(&bar_s_full[buf]));
           tr.ev(15);
           if (++buf == C::NBUF) { buf = 0; ++round; }
@@ -678,20 +694,31 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         for (int u = 0; u < U && ok; ++u) {
           const int i = u & 1;
+          // operands of the unit, formed ahead of the wait
+          const uint32_t qb = loRingMN + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
+          const uint32_t dob = qb + (C::TILE_BYTES >> 4);
+          const uint32_t aS = tbase + buf * 128;
+          // 16-bit operands: queries 0-31 of the unit at columns [0,16) of their buffer half, queries 32-63 at [32,48)
+          uint64_t bq[4], bdo[4];
+          uint32_t aop[4];
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            bq[kk] = desc64(qb + koff_mnmajor(kk), hi);
+            bdo[kk] = desc64(dob + koff_mnmajor(kk), hi);
+            aop[kk] = aS + (kk >> 1) * 32 + (kk & 1) * 8;
+          }
           ok = mbar_wait(smem_u32(&bar_p_full[buf]), round_parity, &abortf, a.status, W_K_PFULL);
           if (!ok) break;
           tr.ev(10);
           tc_fence_after_sync();
-          const uint32_t qb = loRingMN + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
-          const uint32_t dob = qb + (C::TILE_BYTES >> 4);
-          const uint32_t aS = tbase + buf * 128, aP = aS + 64;
-          // 16-bit operands: queries 0-31 of the unit at columns [0,16) of their buffer half, queries 32-63 at [32,48)
+          // dV += P^T_u dO_u   (P^T_u on top of S^T_u)
+          mma_ts64_p(tDV, aop[0], bdo[0], idesc_m2, u > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)  // dV += P^T_u dO_u   (P^T_u on top of S^T_u)
-            mma_ts_split(tDV, aS + (kk >> 1) * 32 + (kk & 1) * 8, dob + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 1; kk < 4; ++kk) mma_ts64<true>(tDV, aop[kk], bdo[kk], idesc_m2);
+          // dK += dS^T_u Q_u   (dS^T_u on top of dP^T_u, 64 columns further)
+          mma_ts64_p(tDK, aop[0] + 64, bq[0], idesc_m2, u > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)  // dK += dS^T_u Q_u   (dS^T_u on top of dP^T_u)
-            mma_ts_split(tDK, aP + (kk >> 1) * 32 + (kk & 1) * 8, qb + koff_mnmajor(kk), hi, idesc_m2, (u > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 1; kk < 4; ++kk) mma_ts64<true>(tDK, aop[kk] + 64, bq[kk], idesc_m2);
           if (i == 1) mma_commit(smem_u32(&bar_ring_empty[stage]));
           tc_fence_before_sync();
           mbar_arrive(smem_u32(&bar_m2_issued[buf]));

@@ -52,20 +52,42 @@ __device__ __forceinline__ void mma_ss_split(uint32_t d_tmem, uint32_t alo, uint
       ::"r"(d_tmem), "r"(alo), "r"(blo), "r"(hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// SS product whose A descriptor is already a 64-bit value (precomputed per k-step outside the unit
-// loop) and whose accumulate flag is a compile-time constant: two instructions less per MMA for the
-// issuing thread
+// MMA forms whose shared-memory descriptors are complete 64-bit values. The issuing thread forms
+// them BEFORE it waits for the barriers of a unit, so that once the barriers have fired the MMAs go
+// out back to back with no address arithmetic between them: that thread shares its scheduler with
+// busy compute warps, and every dependent instruction in its path costs it 10-20 cycles.
+__device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; }
 template <bool kAccumulate>
-__device__ __forceinline__ void mma_ss_a64(uint32_t d_tmem, uint64_t adesc, uint32_t blo, uint32_t hi, uint32_t idesc) {
+__device__ __forceinline__ void mma_ss64(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
-      ".reg .b64 db;\n"
-      "mov.b64 db, {%2, %3};\n"
-      "setp.ne.b32 p, %5, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, db, %4, p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
       "}\n"
-      ::"r"(d_tmem), "l"(adesc), "r"(blo), "r"(hi), "r"(idesc), "n"(kAccumulate ? 1 : 0)
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "n"(kAccumulate ? 1 : 0)
+      : "memory");
+}
+template <bool kAccumulate>
+__device__ __forceinline__ void mma_ts64(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "n"(kAccumulate ? 1 : 0)
+      : "memory");
+}
+// accumulate flag known only at run time (first product into an accumulator)
+__device__ __forceinline__ void mma_ts64_p(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void mma_ts_split(uint32_t d_tmem, uint32_t a_tmem, uint32_t blo, uint32_t hi,

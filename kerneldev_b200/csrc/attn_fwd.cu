@@ -325,6 +325,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int u = 0; u < U && ok; ++u) {
           tr.tb();
           const uint4 c = sCmd[2 * u];
+          // operands of the unit, formed ahead of the waits
+          const uint32_t d = tbase + buf * 128;
+          const uint32_t qlo = c.x + q_off, klo = c.y + kstage * (C::TILE_BYTES >> 4);
+          uint64_t qdesc[HD / 16], kdesc[HD / 16];
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            qdesc[kk] = desc64(qlo + koff_kmajor(kk), hi);
+            kdesc[kk] = desc64(klo + koff_kmajor(kk), hi);
+          }
           if (round > 0) {
             // the buffer is free once P V of the unit that used it in the previous round has been issued
             ok = mbar_wait(smem_u32(&bar_pv_issued[buf]), (round - 1) & 1, &abortf, a.status, W_F_PVISSUED);
@@ -337,11 +346,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
           tr.te(2);
           tc_fence_after_sync();
-          const uint32_t d = tbase + buf * 128;
-          const uint32_t qlo = c.x + q_off, klo = c.y + kstage * (C::TILE_BYTES >> 4);
+          mma_ss64<false>(d, qdesc[0], kdesc[0], idesc_s);
 #pragma unroll
-          for (int kk = 0; kk < HD / 16; ++kk)
-            mma_ss_split(d, qlo + koff_kmajor(kk), klo + koff_kmajor(kk), hi, idesc_s, kk > 0 ? 1u : 0u);
+          for (int kk = 1; kk < HD / 16; ++kk) mma_ss64<true>(d, qdesc[kk], kdesc[kk], idesc_s);
           mma_commit(smem_u32(&bar_s_full[2 * buf + ((c.z & CMD_TILE1) ? 1 : 0)]));
           if (c.z & CMD_RELEASE) {
             mma_commit(smem_u32(&bar_k_empty[kstage]));
@@ -367,6 +374,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int u = 0; u < U && ok; ++u) {
           tr.tb();
           const uint4 c = sCmd[2 * u + 1];
+          // operands of the unit, formed ahead of the waits
+          const uint32_t vlo = c.y + vstage * (C::TILE_BYTES >> 4);
+          const uint32_t aP = tbase + buf * 128;
+          uint64_t vdesc[KD_TILE / 16];
+          uint32_t pop[KD_TILE / 16];
+#pragma unroll
+          for (int kk = 0; kk < KD_TILE / 16; ++kk) {
+            vdesc[kk] = desc64(vlo + koff_mnmajor(kk), hi);
+            // P of 16 keys = 8 packed columns; each softmax warpgroup writes its keys at the start of its own score columns
+            pop[kk] = aP + ((C::NSUB == 2) ? (kk >> 2) * 64 + (kk & 3) * 8 : kk * 8);
+          }
           ok = mbar_wait(smem_u32(&bar_p_full[buf]), round_parity, &abortf, a.status, W_F_PFULL);
           if (!ok) break;
           tr.te(1);
@@ -385,14 +403,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
           tr.te(2);
           tc_fence_after_sync();
-          const uint32_t dO = tbase + C::TM_O0 + i * HD, aP = tbase + buf * 128;
-          const uint32_t vlo = c.y + vstage * (C::TILE_BYTES >> 4);
+          const uint32_t dO = tbase + C::TM_O0 + i * HD;
+          mma_ts64_p(dO, pop[0], vdesc[0], idesc_o, acc0);
 #pragma unroll
-          for (int kk = 0; kk < KD_TILE / 16; ++kk) {
-            // P of 16 keys = 8 packed columns; each softmax warpgroup writes its keys at the start of its own score columns
-            const uint32_t pcol = (C::NSUB == 2) ? (kk >> 2) * 64 + (kk & 3) * 8 : kk * 8;
-            mma_ts_split(dO, aP + pcol, vlo + koff_mnmajor(kk), hi, idesc_o, kk > 0 ? 1u : acc0);
-          }
+          for (int kk = 1; kk < KD_TILE / 16; ++kk) mma_ts64<true>(dO, pop[kk], vdesc[kk], idesc_o);
           mma_commit(smem_u32(&bar_pv_done[i]));
           if (c.z & CMD_RELEASE) {
             mma_commit(smem_u32(&bar_v_empty[vstage]));
