@@ -282,3 +282,19 @@ def test_backward_phases_and_delta_scratch(D):
     _backward(q, k, v, o, lse, do, plan, D ** -0.5, 2, bufs)
     torch.cuda.synchronize()
     assert torch.equal(bufs[1], ref[1]) and torch.equal(bufs[2], ref[2])
+
+
+@pytest.mark.parametrize("D,dtype", [(64, torch.bfloat16), (128, torch.float16)])
+@pytest.mark.parametrize("G", [2, 3, 8])
+def test_head_groups_per_cta(monkeypatch, D, dtype, G):
+    """A CTA handles G heads one after the other (the work list is shared, the pipeline runs on across
+    heads). Small problems get G = 1 by themselves, so the group size is forced here: H = 5 is not a
+    multiple of 2 or 3, a sequence is empty and one ends inside a tile."""
+    monkeypatch.setenv("KD_HEADS_PER_CTA", str(G))
+    monkeypatch.setenv("KD_HEADS_PER_CTA_BWD", str(G))
+    B, H, T = 3, 5, 520
+    ins, sid, pre = random_meta(17 + G, B, T)
+    lens = np.array([T, 0, T - 77], np.int32)
+    q, k, v, do = rand_inputs(B, H, T, D, dtype, seed=40 + G)
+    got = run_op(q, k, v, do, ins, sid, pre, lens)
+    compare(q, k, v, do, ao.dense_mask(T, ins, sid, pre, lens), got)
