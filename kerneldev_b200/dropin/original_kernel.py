@@ -1,5 +1,14 @@
 """Drop-in module: put this directory ahead of the reference checkout on ``sys.path`` and the
 reference's ``model.py`` (``from original_kernel import flash_attention``, model.py:24) binds the
-sm_100a operator instead of the Triton one."""
-from kerneldev_b200.original_kernel import (flash_attention, generate_hadamard_signs,  # noqa: F401
-                                             hadamard_transform)
+sm_100a operator instead of the Triton one.
+
+The operator is bound with ``out_layout="input"``: model.py hands over (B,H,T,D) views of (B,T,H,D)
+memory (model.py:76-78) and undoes the transpose after the call with ``.transpose(1, 2).contiguous()``
+(model.py:95), which is free when O already lies in that memory order."""
+import functools
+
+from kerneldev_b200.original_kernel import flash_attention as _flash_attention
+from kerneldev_b200.original_kernel import generate_hadamard_signs, hadamard_transform  # noqa: F401
+
+flash_attention = functools.partial(_flash_attention, out_layout="input")
+functools.update_wrapper(flash_attention, _flash_attention)

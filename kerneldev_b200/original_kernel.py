@@ -3,7 +3,7 @@
 sm_100a kernels in libkd_attention.so.
 
 ``flash_attention`` is a drop-in for ``model.MultiHeadAttention`` (model.py:83-93): same
-arguments, same return structure, O contiguous in the dtype of q, LSE in base-2 units
+arguments, same return structure, O contiguous in the dtype of q (original_kernel.py:1801), LSE in base-2 units
 (original_kernel.py:603-604), gradients for q, k and v only (the gradient of LSE is ignored,
 as at original_kernel.py:1965-1992).
 
@@ -75,11 +75,13 @@ def _params(q, k, v, o, lse, plan, sm_scale):
     return p
 
 
-def _forward(q, k, v, plan: AttentionPlan, sm_scale: float):
-    """One kd_attn_fwd call: returns (O, LSE) for inputs that passed _check_inputs."""
+def _forward(q, k, v, plan: AttentionPlan, sm_scale: float, like_input: bool = False):
+    """One kd_attn_fwd call: returns (O, LSE) for inputs that passed _check_inputs. ``like_input``: O in the
+    memory layout of q instead of contiguous."""
     q, k, v = _usable(q), _usable(k), _usable(v)
     B, H, T, D = q.shape
-    o = torch.empty((B, H, T, D), dtype=q.dtype, device=q.device)
+    # empty_like keeps the strides of a dense q, e.g. (B,T,H,D) memory seen as (B,H,T,D)
+    o = torch.empty_like(q) if like_input else torch.empty((B, H, T, D), dtype=q.dtype, device=q.device)
     lse = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
     p = _params(q, k, v, o, lse, plan, sm_scale)
     stream = torch.cuda.current_stream(q.device).cuda_stream
@@ -90,15 +92,19 @@ def _forward(q, k, v, plan: AttentionPlan, sm_scale: float):
     return o, lse
 
 
-def _backward(q, k, v, o, lse, d_o, plan: AttentionPlan, sm_scale: float, phases: int = 0, bufs=None):
+def _backward(q, k, v, o, lse, d_o, plan: AttentionPlan, sm_scale: float, phases: int = 0, bufs=None,
+              like_input: bool = False):
     """One kd_attn_bwd call: returns (dQ, dK, dV). ``phases`` selects one of the two backward
     kernels (see kd_attn_params.bwd_phases); ``bufs`` = (dq, dk, dv, delta) reuses buffers."""
     q, k, v, d_o = _usable(q), _usable(k), _usable(v), _usable(d_o)
     B, H, T, D = q.shape
     if bufs is None:
-        dq = torch.empty((B, H, T, D), dtype=q.dtype, device=q.device)
-        dk = torch.empty_like(dq)
-        dv = torch.empty_like(dq)
+        if like_input:   # each gradient in its input's layout
+            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        else:
+            dq = torch.empty((B, H, T, D), dtype=q.dtype, device=q.device)
+            dk = torch.empty_like(dq)
+            dv = torch.empty_like(dq)
         delta = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
     else:
         dq, dk, dv, delta = bufs
@@ -117,19 +123,20 @@ def _backward(q, k, v, o, lse, d_o, plan: AttentionPlan, sm_scale: float, phases
 
 class _FlashAttentionFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, plan, sm_scale):
-        o, lse = _forward(q, k, v, plan, sm_scale)
+    def forward(ctx, q, k, v, plan, sm_scale, like_input=False):
+        o, lse = _forward(q, k, v, plan, sm_scale, like_input)
         ctx.save_for_backward(q, k, v, o, lse)
         ctx.plan = plan
         ctx.sm_scale = sm_scale
+        ctx.like_input = like_input
         ctx.mark_non_differentiable(lse)
         return o, lse
 
     @staticmethod
     def backward(ctx, d_o, _d_lse):
         q, k, v, o, lse = ctx.saved_tensors
-        dq, dk, dv = _backward(q, k, v, o, lse, d_o, ctx.plan, ctx.sm_scale)
-        return dq, dk, dv, None, None
+        dq, dk, dv = _backward(q, k, v, o, lse, d_o, ctx.plan, ctx.sm_scale, like_input=ctx.like_input)
+        return dq, dk, dv, None, None, None
 
 
 def _hadamard_call(x: torch.Tensor, signs, inverse: bool) -> torch.Tensor:
@@ -197,6 +204,7 @@ def flash_attention(
     is_prefix: torch.Tensor | None = None,
     return_attention_mask: bool = False,
     hadamard_signs: torch.Tensor | None = None,
+    out_layout: str = "contiguous",
 ):
     """Self-attention with the 4-section hierarchical mask; arguments and return value as the
     reference's ``flash_attention`` (original_kernel.py:2096-2168).
@@ -210,6 +218,10 @@ def flash_attention(
     hadamard_signs (extension, default None): (heads, head_dim) +-1; Q and K are replaced by
     ``hadamard_transform(., signs)`` before the attention, which leaves Q K^T unchanged in exact
     arithmetic and spreads outliers over the head dimension.
+    out_layout (extension): "contiguous" (default, as original_kernel.py:1801 and :1920-1922) or
+    "input": O and the gradients take the memory layout of q, k, v. For the model's (B,H,T,D) views
+    of (B,T,H,D) memory (model.py:76-78) the ``transpose(1, 2).contiguous()`` after the call
+    (model.py:95) and its counterpart in the backward then copy nothing. The drop-in module uses it.
 
     Returns O, or (O, LSE) with return_lse, or (that, mask[B,H,T,T] bool) with return_attention_mask.
     """
@@ -227,7 +239,9 @@ def flash_attention(
         q = hadamard_transform(q, hadamard_signs)
         k = hadamard_transform(k, hadamard_signs)
 
-    o, lse = _FlashAttentionFn.apply(q, k, v, plan, sm_scale)
+    if out_layout not in ("contiguous", "input"):
+        raise ValueError("out_layout must be 'contiguous' or 'input'")
+    o, lse = _FlashAttentionFn.apply(q, k, v, plan, sm_scale, out_layout == "input")
 
     if return_attention_mask:
         mask = plan.dense_mask().unsqueeze(1).expand(B, H, T, T)

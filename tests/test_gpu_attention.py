@@ -137,6 +137,20 @@ def test_strided_views_like_the_model():
         outs.append((o, qs.grad, ks.grad, vs.grad))
     for a, b in zip(*outs):
         assert torch.equal(a, b)
+    # out_layout="input" (what the drop-in module binds): O lies in q's memory order, so the model's
+    # transpose(1, 2).contiguous() after the call is a no-op; values are the same
+    import sys, os
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "kerneldev_b200", "dropin"))
+    try:
+        import original_kernel as dropin
+    finally:
+        sys.path.pop(0)
+    qs, ks, vs = (x.transpose(1, 2).contiguous().transpose(1, 2).requires_grad_() for x in (q, k, v))
+    o = dropin.flash_attention(qs, ks, vs, causal=True, **meta)
+    assert o.stride() == qs.stride() and o.transpose(1, 2).is_contiguous()
+    o.backward(do.transpose(1, 2).contiguous().transpose(1, 2))
+    for a, b in zip((o, qs.grad, ks.grad, vs.grad), outs[0]):
+        assert torch.equal(a, b)
 
 
 def test_golden_fixture_from_reference_kernels():
