@@ -156,6 +156,19 @@ int kd_workspace_bytes(int32_t B, int32_t H, int32_t T, int32_t D, size_t* bytes
 int kd_hadamard(const kd_tensor* x, const kd_tensor* y, int32_t B, int32_t H, int32_t T, int32_t D,
                 int32_t dtype, const float* signs, int32_t inverse, void* stream);
 
+/* Per-token mask metadata from token ids, on the device (replaces the fallback of
+ * GPTModel.forward, model.py:203-238: two cumulative sums plus a host loop with one .nonzero() /
+ * .item() synchronisation per row).
+ *   tokens     int64 (B,T), unit stride along T, stride_b elements between rows
+ *   tok_*      ids of [SPAN], [ES], [CLS] and [MASKQ] (data_builder.py:44-51)
+ *   in_span    uint8 (B,T) contiguous out: (#[SPAN] - #[ES] in tokens[b, 0..t]) > 0
+ *   span_id    int64 (B,T) contiguous out: #[SPAN] in tokens[b, 0..t] where in_span, else 0; -1 at [MASKQ]
+ *   is_prefix  uint8 (B,T) contiguous out: t <= index of the first [CLS] of the row (none: all 0)
+ * The outputs are what kd_classify takes (bool tensors are one byte per element). */
+int kd_metadata_from_tokens(const int64_t* tokens, int64_t stride_b, int32_t B, int32_t T, int64_t tok_span,
+                            int64_t tok_es, int64_t tok_cls, int64_t tok_maskq, uint8_t* in_span,
+                            int64_t* span_id, uint8_t* is_prefix, void* stream);
+
 /* Message for the last negative return value on this host thread. */
 const char* kd_last_error(void);
 

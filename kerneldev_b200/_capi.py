@@ -23,6 +23,7 @@ LIB_PATH = Path(os.environ.get("KD_LIB_PATH") or Path(__file__).resolve().parent
 EXPORTS = (
     "kd_version", "kd_last_error", "kd_plan_layout_get", "kd_classify", "kd_mask_dense",
     "kd_attn_fwd", "kd_attn_bwd", "kd_attn_bwd_static", "kd_workspace_bytes", "kd_hadamard",
+    "kd_metadata_from_tokens",
 )
 
 
@@ -87,8 +88,10 @@ def load() -> ctypes.CDLL:
     lib.kd_workspace_bytes.argtypes = [c_int32, c_int32, c_int32, c_int32, POINTER(c_size_t)]
     lib.kd_hadamard.argtypes = [POINTER(KdTensor), POINTER(KdTensor), c_int32, c_int32, c_int32, c_int32,
                                 c_int32, c_void_p, c_int32, c_void_p]
+    lib.kd_metadata_from_tokens.argtypes = [c_void_p, c_int64, c_int32, c_int32, c_int64, c_int64, c_int64, c_int64,
+                                            c_void_p, c_void_p, c_void_p, c_void_p]
     for name in ("kd_plan_layout_get", "kd_classify", "kd_mask_dense", "kd_attn_fwd", "kd_attn_bwd", "kd_attn_bwd_static",
-                 "kd_workspace_bytes", "kd_hadamard"):
+                 "kd_workspace_bytes", "kd_hadamard", "kd_metadata_from_tokens"):
         getattr(lib, name).restype = c_int32
     _lib = lib
     return lib

@@ -216,4 +216,17 @@ int kd_hadamard(const kd_tensor* x, const kd_tensor* y, int32_t B, int32_t H, in
   return launch_hadamard(*x, *y, B, H, T, D, dtype, signs, inverse, static_cast<cudaStream_t>(stream));
 }
 
+int kd_metadata_from_tokens(const int64_t* tokens, int64_t stride_b, int32_t B, int32_t T, int64_t tok_span,
+                            int64_t tok_es, int64_t tok_cls, int64_t tok_maskq, uint8_t* in_span,
+                            int64_t* span_id, uint8_t* is_prefix, void* stream) {
+  if (B < 0 || T < 0) return set_error(KD_ERR_ARG, "bad shape B=%d T=%d", B, T);
+  if (B == 0 || T == 0) return 0;
+  if (!tokens || !in_span || !span_id || !is_prefix) return set_error(KD_ERR_ARG, "tokens / in_span / span_id / is_prefix is null");
+  if (stride_b < T) return set_error(KD_ERR_ARG, "stride_b %lld is smaller than T %d", static_cast<long long>(stride_b), T);
+  int rc = check_device();
+  if (rc) return rc;
+  return launch_metadata(tokens, stride_b, B, T, tok_span, tok_es, tok_cls, tok_maskq, in_span, span_id, is_prefix,
+                         static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -66,4 +66,8 @@ int static_delta_address(size_t rows_needed, float** out);
 int launch_hadamard(const kd_tensor& x, const kd_tensor& y, int B, int H, int T, int D, int dtype,
                     const float* signs, int inverse, cudaStream_t stream);
 
+int launch_metadata(const int64_t* tokens, int64_t stride_b, int B, int T, int64_t tok_span, int64_t tok_es,
+                    int64_t tok_cls, int64_t tok_maskq, uint8_t* in_span, int64_t* span_id, uint8_t* is_prefix,
+                    cudaStream_t stream);
+
 }  // namespace kd

@@ -223,3 +223,28 @@ def hadamard_transform(x, signs=None):
     if signs is not None:
         x = x * signs[None, :, None, :].to(x.device)
     return (x @ hadamard_matrix(D).to(x.device)) / math.sqrt(D)
+
+
+# ------------------------------------------------------------------------------------------
+# metadata from token ids
+# ------------------------------------------------------------------------------------------
+SPECIAL_TOKENS = {"[PAD]": 0, "[CLS]": 1, "[MASK]": 2, "[SPAN]": 3, "[ES]": 4, "[MASKQ]": 5}   # data_builder.py:44-51
+
+
+def metadata_from_tokens(tokens, special_tokens=None):
+    """(in_span bool, span_id int64, is_prefix bool), each (B, T), from token ids (B, T): the fallback
+    of GPTModel.forward (model.py:203-238). Both of its branches reduce to the same formulas: without
+    [SPAN] / [ES] / [MASKQ] tokens the cumulative sums are zero (model.py:216-224 vs :231-237)."""
+    st = SPECIAL_TOKENS if special_tokens is None else special_tokens
+    x = tokens.detach().cpu().numpy() if torch.is_tensor(tokens) else np.asarray(tokens)
+    c_span = np.cumsum(x == st["[SPAN]"], axis=1)
+    c_es = np.cumsum(x == st["[ES]"], axis=1)
+    in_span = (c_span - c_es) > 0                      # model.py:218
+    span_id = np.where(in_span, c_span, 0).astype(np.int64)   # :219-220
+    span_id[x == st["[MASKQ]"]] = -1                   # :223-224
+    is_prefix = np.zeros(x.shape, dtype=bool)
+    for b in range(x.shape[0]):                        # :227-231
+        pos = np.nonzero(x[b] == st["[CLS]"])[0]
+        if len(pos) > 0:
+            is_prefix[b, : pos[0] + 1] = True
+    return in_span, span_id, is_prefix

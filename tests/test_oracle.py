@@ -125,3 +125,17 @@ def test_package_generator_equals_oracle_generator():
         b = synthetic.batch_metadata(9, B, T, **synthetic.CONFIG_RANGES[cfg])
         for x, y in zip(a, b):
             assert np.array_equal(x, y) and x.dtype == y.dtype
+
+
+def test_metadata_from_tokens_matches_reference_fixture():
+    """The token -> (in_span, span_id, is_prefix) restatement against outputs of the reference's own
+    code (model.py:203-238, executed by tests/golden/make_golden_metadata.py): bit-exact, for canonical
+    rows, rows without markers, unbalanced / nested markers and a batch that takes the reference's
+    teacher-forcing branch."""
+    import os
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "metadata_from_tokens.npz"))
+    for name in "abcd":
+        ins, sid, pre = ao.metadata_from_tokens(z[f"{name}_tokens"])
+        assert np.array_equal(ins, z[f"{name}_in_span"]), name
+        assert np.array_equal(sid, z[f"{name}_span_id"]), name
+        assert np.array_equal(pre, z[f"{name}_is_prefix"]), name
