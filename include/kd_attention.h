@@ -30,6 +30,7 @@ extern "C" {
 
 #define KD_F16 0
 #define KD_BF16 1
+#define KD_F32 2   /* kd_span_mean only */
 
 #define KD_TILE 128 /* mask classification and kernel tile edge (tokens) */
 
@@ -168,6 +169,26 @@ int kd_hadamard(const kd_tensor* x, const kd_tensor* y, int32_t B, int32_t H, in
 int kd_metadata_from_tokens(const int64_t* tokens, int64_t stride_b, int32_t B, int32_t T, int64_t tok_span,
                             int64_t tok_es, int64_t tok_cls, int64_t tok_maskq, uint8_t* in_span,
                             int64_t* span_id, uint8_t* is_prefix, void* stream);
+
+/* Span means of the cocktail-party head (model.py:258-296). kd_span_index ranks the [SPAN] and [ES]
+ * markers of every row: starts / ends are int32 (B,T) with the position of the r-th marker of the
+ * row at [b][r] and -1 beyond its count; n_starts / n_ends (B) are the counts and first_mask (B) the
+ * position of the row's first [MASK] token or -1 (replaces the .nonzero() / torch.unique calls of
+ * model.py:265-277). */
+int kd_span_index(const int64_t* tokens, int64_t stride_b, int32_t B, int32_t T, int64_t tok_span, int64_t tok_es,
+                  int64_t tok_mask, int32_t* starts, int32_t* ends, int32_t* n_starts, int32_t* n_ends,
+                  int32_t* first_mask, void* stream);
+
+/* backward = 0: h[b, j, :] = mean(x[b, st_j + 1 : ed_j, :]) for the pairs j < min(n_starts, n_ends) of row b
+ * with st_j + 1 < ed_j, zero otherwise (the Python double loop of model.py:287-293);
+ *   a = x (B,T,C) with element strides a_sb, a_st and unit stride along C; out = h (B,S,C) contiguous.
+ * backward = 1: its gradient, grad_x[b, t, :] = sum over the pairs covering t of grad_h[b, j, :] / (ed_j - st_j - 1);
+ *   a = grad_h (B,S,C) contiguous; out = grad_x (B,T,C) with element strides o_sb, o_st.
+ * dtype KD_F16 / KD_BF16 / KD_F32 (sums in fp32). S is the padded span count of h (the reference uses the
+ * largest n_starts of the batch). */
+int kd_span_mean(int32_t backward, const void* a, int64_t a_sb, int64_t a_st, void* out, int64_t o_sb, int64_t o_st,
+                 int32_t B, int32_t T, int32_t C, int32_t S, int32_t dtype, const int32_t* starts,
+                 const int32_t* ends, const int32_t* n_starts, const int32_t* n_ends, void* stream);
 
 /* Message for the last negative return value on this host thread. */
 const char* kd_last_error(void);

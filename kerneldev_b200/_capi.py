@@ -11,7 +11,7 @@ from ctypes import (POINTER, Structure, c_char_p, c_float, c_int32, c_int64, c_s
                     c_void_p)
 from pathlib import Path
 
-KD_F16, KD_BF16 = 0, 1
+KD_F16, KD_BF16, KD_F32 = 0, 1, 2
 KD_TILE = 128
 KD_TILE_EMPTY, KD_TILE_FULL, KD_TILE_PARTIAL = 0, 1, 2
 KD_STATUS_TIMEOUT = 0x10000000
@@ -23,7 +23,7 @@ LIB_PATH = Path(os.environ.get("KD_LIB_PATH") or Path(__file__).resolve().parent
 EXPORTS = (
     "kd_version", "kd_last_error", "kd_plan_layout_get", "kd_classify", "kd_mask_dense",
     "kd_attn_fwd", "kd_attn_bwd", "kd_attn_bwd_static", "kd_workspace_bytes", "kd_hadamard",
-    "kd_metadata_from_tokens",
+    "kd_metadata_from_tokens", "kd_span_index", "kd_span_mean",
 )
 
 
@@ -88,10 +88,14 @@ def load() -> ctypes.CDLL:
     lib.kd_workspace_bytes.argtypes = [c_int32, c_int32, c_int32, c_int32, POINTER(c_size_t)]
     lib.kd_hadamard.argtypes = [POINTER(KdTensor), POINTER(KdTensor), c_int32, c_int32, c_int32, c_int32,
                                 c_int32, c_void_p, c_int32, c_void_p]
+    lib.kd_span_index.argtypes = [c_void_p, c_int64, c_int32, c_int32, c_int64, c_int64, c_int64, c_void_p, c_void_p,
+                                  c_void_p, c_void_p, c_void_p, c_void_p]
+    lib.kd_span_mean.argtypes = [c_int32, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int32, c_int32, c_int32,
+                                 c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
     lib.kd_metadata_from_tokens.argtypes = [c_void_p, c_int64, c_int32, c_int32, c_int64, c_int64, c_int64, c_int64,
                                             c_void_p, c_void_p, c_void_p, c_void_p]
     for name in ("kd_plan_layout_get", "kd_classify", "kd_mask_dense", "kd_attn_fwd", "kd_attn_bwd", "kd_attn_bwd_static",
-                 "kd_workspace_bytes", "kd_hadamard", "kd_metadata_from_tokens"):
+                 "kd_workspace_bytes", "kd_hadamard", "kd_metadata_from_tokens", "kd_span_index", "kd_span_mean"):
         getattr(lib, name).restype = c_int32
     _lib = lib
     return lib

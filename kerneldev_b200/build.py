@@ -18,7 +18,7 @@ LIB_DIR = PKG_DIR / "_lib"
 LIB_PATH = LIB_DIR / "libkd_attention.so"
 INCLUDE_DIR = PKG_DIR.parent / "include"
 
-SOURCES = ["capi.cu", "plan.cu", "attn_fwd.cu", "attn_bwd.cu", "hadamard.cu", "metadata.cu"]
+SOURCES = ["capi.cu", "plan.cu", "attn_fwd.cu", "attn_bwd.cu", "hadamard.cu", "metadata.cu", "cocktail.cu"]
 HEADERS = ["common.cuh", "mask_rule.cuh", "sm100_prims.cuh"]
 
 NVCC_FLAGS = [

@@ -229,4 +229,30 @@ int kd_metadata_from_tokens(const int64_t* tokens, int64_t stride_b, int32_t B, 
                          static_cast<cudaStream_t>(stream));
 }
 
+int kd_span_index(const int64_t* tokens, int64_t stride_b, int32_t B, int32_t T, int64_t tok_span, int64_t tok_es,
+                  int64_t tok_mask, int32_t* starts, int32_t* ends, int32_t* n_starts, int32_t* n_ends,
+                  int32_t* first_mask, void* stream) {
+  if (B < 0 || T < 0) return set_error(KD_ERR_ARG, "bad shape B=%d T=%d", B, T);
+  if (B == 0 || T == 0) return 0;
+  if (!tokens || !starts || !ends || !n_starts || !n_ends || !first_mask) return set_error(KD_ERR_ARG, "null pointer");
+  if (stride_b < T) return set_error(KD_ERR_ARG, "stride_b %lld is smaller than T %d", static_cast<long long>(stride_b), T);
+  int rc = check_device();
+  if (rc) return rc;
+  return launch_span_index(tokens, stride_b, B, T, tok_span, tok_es, tok_mask, starts, ends, n_starts, n_ends, first_mask,
+                           static_cast<cudaStream_t>(stream));
+}
+
+int kd_span_mean(int32_t backward, const void* a, int64_t a_sb, int64_t a_st, void* out, int64_t o_sb, int64_t o_st,
+                 int32_t B, int32_t T, int32_t C, int32_t S, int32_t dtype, const int32_t* starts,
+                 const int32_t* ends, const int32_t* n_starts, const int32_t* n_ends, void* stream) {
+  if (B < 0 || T < 0 || C < 0 || S < 0) return set_error(KD_ERR_ARG, "bad shape B=%d T=%d C=%d S=%d", B, T, C, S);
+  if (B == 0 || C == 0 || S == 0) return 0;
+  if (!a || !out || !starts || !ends || !n_starts || !n_ends) return set_error(KD_ERR_ARG, "null pointer");
+  if (dtype != KD_F16 && dtype != KD_BF16 && dtype != KD_F32) return set_error(KD_ERR_ARG, "dtype %d not supported", dtype);
+  int rc = check_device();
+  if (rc) return rc;
+  return launch_span_mean(backward != 0, a, a_sb, a_st, out, o_sb, o_st, B, T, C, S, dtype, starts, ends, n_starts, n_ends,
+                          static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -70,4 +70,11 @@ int launch_metadata(const int64_t* tokens, int64_t stride_b, int B, int T, int64
                     int64_t tok_cls, int64_t tok_maskq, uint8_t* in_span, int64_t* span_id, uint8_t* is_prefix,
                     cudaStream_t stream);
 
+int launch_span_index(const int64_t* tokens, int64_t stride_b, int B, int T, int64_t tok_span, int64_t tok_es,
+                      int64_t tok_mask, int32_t* starts, int32_t* ends, int32_t* n_starts, int32_t* n_ends,
+                      int32_t* first_mask, cudaStream_t stream);
+int launch_span_mean(bool backward, const void* a, int64_t a_sb, int64_t a_st, void* out, int64_t o_sb, int64_t o_st, int B,
+                     int T, int C, int S, int dtype, const int32_t* starts, const int32_t* ends, const int32_t* n_starts,
+                     const int32_t* n_ends, cudaStream_t stream);
+
 }  // namespace kd

@@ -248,3 +248,35 @@ def metadata_from_tokens(tokens, special_tokens=None):
         if len(pos) > 0:
             is_prefix[b, : pos[0] + 1] = True
     return in_span, span_id, is_prefix
+
+
+# ------------------------------------------------------------------------------------------
+# cocktail-party head
+# ------------------------------------------------------------------------------------------
+def cocktail_scores(x_embed, tokens, special_tokens=None):
+    """(scores (B, max_spans), h_spans (B, max_spans, D)) as model.py:262-296 computes them: the j-th [SPAN]
+    of a row is paired with its j-th [ES] (zip stops at the shorter list, :288); a pair with
+    st + 1 < ed contributes the mean of x_embed[b, st+1:ed], any other slot stays zero (:289-293);
+    h_context is the embedding at the row's first [MASK] or zero (:265-273). Differentiable torch code
+    on whatever device x_embed lives on (the tests run it on CPU)."""
+    st_ = SPECIAL_TOKENS if special_tokens is None else special_tokens
+    x = tokens.detach().cpu().numpy() if torch.is_tensor(tokens) else np.asarray(tokens)
+    B, T = x.shape
+    D = x_embed.shape[-1]
+    max_spans = int((x == st_["[SPAN]"]).sum(1).max()) if B else 0
+    h_context = x_embed.new_zeros((B, D))
+    rows_spans = []
+    for b in range(B):
+        mpos = np.nonzero(x[b] == st_["[MASK]"])[0]
+        if len(mpos) > 0:
+            h_context = h_context.index_put((torch.tensor([b]),), x_embed[b, int(mpos[0])].unsqueeze(0))
+        starts = np.nonzero(x[b] == st_["[SPAN]"])[0]
+        ends = np.nonzero(x[b] == st_["[ES]"])[0]
+        slots = [x_embed.new_zeros((D,)) for _ in range(max_spans)]
+        for j, (s0, e0) in enumerate(zip(starts, ends)):
+            if s0 + 1 < e0:
+                slots[j] = x_embed[b, int(s0) + 1:int(e0)].mean(dim=0)
+        rows_spans.append(torch.stack(slots) if max_spans else x_embed.new_zeros((0, D)))
+    h_spans = torch.stack(rows_spans) if B else x_embed.new_zeros((0, max_spans, D))
+    return torch.einsum("bd,bnd->bn", h_context, h_spans), h_spans
+

@@ -139,3 +139,24 @@ def test_metadata_from_tokens_matches_reference_fixture():
         assert np.array_equal(ins, z[f"{name}_in_span"]), name
         assert np.array_equal(sid, z[f"{name}_span_id"]), name
         assert np.array_equal(pre, z[f"{name}_is_prefix"]), name
+
+
+def test_cocktail_head_matches_reference_fixture():
+    """The span-mean head restatement against outputs of the reference's own code (model.py:258-296,
+    executed by tests/golden/make_golden_cocktail.py) on the same seeded inputs."""
+    import os
+    import sys
+    gdir = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    sys.path.insert(0, gdir)
+    try:
+        from cocktail_inputs import CASES, cocktail_rows, embeddings
+    finally:
+        sys.path.pop(0)
+    z = np.load(os.path.join(gdir, "cocktail_head.npz"))
+    for name, (seed, B, T, D) in CASES.items():
+        x, e = cocktail_rows(seed, B, T), embeddings(seed, B, T, D)
+        assert int(x.sum()) == int(z[f"{name}_tokens_sum"])      # the inputs are the generator's
+        scores, h_spans = ao.cocktail_scores(e, x)
+        assert tuple(h_spans.shape) == z[f"{name}_h_spans"].shape
+        np.testing.assert_allclose(h_spans.numpy(), z[f"{name}_h_spans"], rtol=1e-6, atol=1e-6)
+        np.testing.assert_allclose(scores.numpy(), z[f"{name}_scores"], rtol=1e-5, atol=1e-5)
