@@ -312,3 +312,39 @@ def test_head_groups_per_cta(monkeypatch, D, dtype, G):
     q, k, v, do = rand_inputs(B, H, T, D, dtype, seed=40 + G)
     got = run_op(q, k, v, do, ins, sid, pre, lens)
     compare(q, k, v, do, ao.dense_mask(T, ins, sid, pre, lens), got)
+
+
+@pytest.mark.parametrize("D,dtype", [(64, torch.bfloat16), (128, torch.float16)])
+def test_max_sequence_length_sampled_rows(D, dtype):
+    """T = 16384 (the largest supported: 128 tiles per row, work lists of up to 128 entries): O and dQ of
+    sampled query rows against dense fp32 math, dK / dV through exact linearity in dO."""
+    from kerneldev_b200 import flash_attention, synthetic
+    B, H, T = 1, 2, 16384
+    ins, sid, pre, lens = synthetic.batch_metadata(7, B, T, prefix=(100, 400), context=(4000, 9000), n_spans=(20, 60), span_len=(16, 128))
+    meta = dict(in_span=_t(ins, torch.bool), span_id=_t(sid, torch.int64), is_prefix=_t(pre, torch.bool), lens=_t(lens, torch.int32))
+    g = torch.Generator(device=DEV).manual_seed(1)
+    q, k, v, do = (torch.randn((B, H, T, D), generator=g, device=DEV, dtype=dtype) for _ in range(4))
+    for x in (q, k, v):
+        x.requires_grad_()
+    o = flash_attention(q, k, v, **meta)
+    o.backward(do)
+    mask = torch.as_tensor(ao.dense_mask(T, ins, sid, pre, lens))[0]
+    rows = torch.tensor(sorted(set([0, 1, 127, 128, 5000, 9000, 12000, int(lens[0]) - 1, T - 1] + list(np.random.default_rng(0).integers(0, T, 24)))))
+    qf, kf, vf, dof = (x.detach().float().cpu() for x in (q, k, v, do))
+    sc = D ** -0.5
+    for h in range(H):
+        s = ((qf[0, h, rows] @ kf[0, h].T) * sc).masked_fill(~mask[rows], float("-inf"))
+        m = s.max(-1, keepdim=True).values
+        m = torch.where(torch.isinf(m), torch.zeros_like(m), m)
+        p = torch.exp(s - m)
+        l = p.sum(-1, keepdim=True)
+        P = torch.where(l > 0, p / l.clamp_min(1e-30), torch.zeros(1))
+        o_ref = P @ vf[0, h]
+        dq_ref = (P * (dof[0, h, rows] @ vf[0, h].T - (o_ref * dof[0, h, rows]).sum(-1, keepdim=True))) @ kf[0, h] * sc
+        assert_close("O", o.detach()[0, h, rows], o_ref)
+        assert_close("dQ", q.grad[0, h, rows], dq_ref)
+    q2, k2, v2 = (x.detach().clone().requires_grad_() for x in (q, k, v))
+    flash_attention(q2, k2, v2, **meta).backward(do * 2)
+    assert torch.isfinite(k.grad).all() and torch.isfinite(v.grad).all()
+    assert torch.allclose(v2.grad.float(), 2 * v.grad.float(), rtol=0, atol=1e-3)
+    assert torch.allclose(k2.grad.float(), 2 * k.grad.float(), rtol=0, atol=2e-3)
