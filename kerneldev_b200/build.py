@@ -19,7 +19,7 @@ LIB_PATH = LIB_DIR / "libkd_attention.so"
 INCLUDE_DIR = PKG_DIR.parent / "include"
 
 SOURCES = ["capi.cu", "plan.cu", "attn_fwd.cu", "attn_bwd.cu", "hadamard.cu", "metadata.cu", "cocktail.cu"]
-HEADERS = ["common.cuh", "mask_rule.cuh", "sm100_prims.cuh"]
+HEADERS = sorted(p.name for p in (Path(__file__).resolve().parent / "csrc").glob("*.cuh"))
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
