@@ -134,8 +134,10 @@ __device__ __forceinline__ void store_row16(uint16_t* dst, const uint32_t (&r)[1
 // Heads a CTA handles one after the other (they share the plan's work list, so the list staging,
 // the TMEM allocation and the pipeline fill are paid once): as many as keeps about per_sm CTAs per SM,
 // at most g_max (the longest-first dispatch order keeps the SMs balanced with that few). Measured
-// best: backward 3 per SM, up to 8 heads; forward (a CTA already holds two query tiles) 2 per SM, up to 4.
-inline int heads_per_cta(int B, int H, int items_per_batch, const char* env_name = "KD_HEADS_PER_CTA", int per_sm = 3,
+// best over batches 4-16 of config 2 and configs 1 and 3: backward 6 per SM, up to 8 heads; forward (a
+// CTA already holds two query tiles) 3 per SM, up to 4. Fewer CTAs than that lose more to imbalance
+// between sequences of different section lengths than the shared pipeline fill saves.
+inline int heads_per_cta(int B, int H, int items_per_batch, const char* env_name = "KD_HEADS_PER_CTA", int per_sm = 6,
                          int g_max = 8) {
   static int sm_count = 0;
   if (sm_count == 0) {

@@ -709,7 +709,7 @@ static int launch_fwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
   FwdArgs a;
   a.B = p.B; a.H = p.H; a.T = p.T; a.NT = L.NT; a.NP = L.NP; a.Tpad = L.NT * KD_TILE;
   a.scale_log2 = p.sm_scale * 1.4426950408889634f;
-  a.G = heads_per_cta(p.B, p.H, L.NP, "KD_HEADS_PER_CTA", 2, 4);
+  a.G = heads_per_cta(p.B, p.H, L.NP, "KD_HEADS_PER_CTA", 3, 4);
   a.desc = pv.desc; a.fwd_cnt = pv.fwd_cnt; a.fwd_list = pv.fwd_list; a.status = pv.status;
   a.order = pv.order; a.trace = trace_buffer(); a.tilebits = pv.tilebits;
   a.o = p.o.ptr; a.o_sb = p.o.stride_b; a.o_sh = p.o.stride_h; a.o_st = p.o.stride_t;
