@@ -52,10 +52,10 @@ CONFIGS = {
 }
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch and per batch row of config 2,
-# from the ncu capture summarised in profiles/attention_kernels_config2_batch4.md (batch 4: 101.3,
-# 139.8 and 158.3 MB); traffic grows in proportion to the number of (batch, head) pairs.
-NCU_TRAFFIC_PER_BATCH_ROW = {"attn_fwd_kernel": 101.3e6 / 4, "attn_bwd_dq_kernel": 139.8e6 / 4,
-                             "attn_bwd_dkdv_kernel": 158.3e6 / 4}
+# from the ncu capture summarised in profiles/attention_kernels_config2_batch4.md (batch 4: 99.7,
+# 136.2 and 159.3 MB); traffic grows in proportion to the number of (batch, head) pairs.
+NCU_TRAFFIC_PER_BATCH_ROW = {"attn_fwd_kernel": 99.7e6 / 4, "attn_bwd_dq_kernel": 136.2e6 / 4,
+                             "attn_bwd_dkdv_kernel": 159.3e6 / 4}
 
 
 def load_peaks():
