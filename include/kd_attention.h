@@ -8,8 +8,9 @@
  *
  * Conventions
  *  - Every pointer inside the parameter structs is a DEVICE pointer owned by the caller.
- *    The library allocates no device memory and keeps no state between calls other than a
- *    per-thread last-error string.
+ *    The library allocates no device memory. The state it keeps between calls is a per-thread
+ *    last-error string and, for kd_attn_bwd_static only, a fixed scratch array on every GPU
+ *    together with its cached device address.
  *  - All entry points enqueue work on the given CUDA stream and return immediately:
  *    0 = enqueued, negative = rejected on the host before any launch (see kd_last_error()).
  *  - Device-side problems (a bounded wait that ran out, an unsupported span_id value) are
@@ -105,6 +106,8 @@ typedef struct kd_attn_params {
   int32_t bwd_phases; /* kd_attn_bwd only. 0 or 3: all kernels; 1: the delta kernel and the dQ
                          kernel; 2: the dK/dV kernel alone (reads delta of an earlier pass 1).
                          Lets a caller time the two large kernels separately. */
+  int32_t heads_per_cta; /* 0: chosen by the library from the grid size. n >= 1: every CTA handles n heads
+                         one after the other (they share the plan's work list); a tuning and test knob. */
 } kd_attn_params;
 
 /* Size and layout of a plan for B sequences of T tokens. */
@@ -139,9 +142,11 @@ int kd_attn_bwd(const kd_attn_params* p, void* stream);
  * 1,048,576 rows; larger problems are rejected with KD_ERR_LIMIT. The call allocates nothing.
  *  - The first call on each device looks up the array's device address (one cudaGetSymbolAddress,
  *    with that device current); make that first call before starting any stream capture.
- *  - All calls share the one array. Nothing in it has to start at zero (the dQ kernel rewrites every
- *    row before the dK/dV kernel reads it), but two calls that overlap on the GPU -- different
- *    streams, or different host threads -- race on it. Serialise them.
+ *  - All calls share the one array. Nothing in it has to start at zero (the delta kernel rewrites
+ *    every row before the dQ and dK/dV kernels read it), but two calls that overlap on the GPU --
+ *    different streams, or different host threads -- race on it. Serialise them.
+ *  - bwd_phases must be 0 or 3: a dK/dV-only pass (2) would read whatever the previous call, perhaps
+ *    of another problem, left in the array, so it is rejected with KD_ERR_ARG.
  *  - Inputs, outputs and results are exactly those of kd_attn_bwd. */
 int kd_attn_bwd_static(const kd_attn_params* p, void* stream);
 

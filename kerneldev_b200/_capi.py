@@ -17,7 +17,7 @@ KD_TILE_EMPTY, KD_TILE_FULL, KD_TILE_PARTIAL = 0, 1, 2
 KD_STATUS_TIMEOUT = 0x10000000
 KD_STATUS_SPAN_RANGE = 0x20000000
 
-# KD_LIB_PATH selects another build of the same library (e.g. the timeline build of build.py --trace)
+# KD_LIB_PATH selects another build of the same library (the wait time-out test loads one built with a short wait limit)
 LIB_PATH = Path(os.environ.get("KD_LIB_PATH") or Path(__file__).resolve().parent / "_lib" / "libkd_attention.so")
 
 EXPORTS = (
@@ -56,7 +56,7 @@ class KdAttnParams(Structure):
         ("dtype", c_int32), ("sm_scale", c_float),
         ("q", KdTensor), ("k", KdTensor), ("v", KdTensor), ("o", KdTensor), ("d_o", KdTensor),
         ("dq", KdTensor), ("dk", KdTensor), ("dv", KdTensor),
-        ("lse", c_void_p), ("delta", c_void_p), ("plan", c_void_p), ("bwd_phases", c_int32),
+        ("lse", c_void_p), ("delta", c_void_p), ("plan", c_void_p), ("bwd_phases", c_int32), ("heads_per_cta", c_int32),
     ]
 
 

@@ -44,24 +44,28 @@ def _stale() -> bool:
     return any(d.stat().st_mtime > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False, trace: bool = False, extra_flags=(), name=None) -> Path:
+def build(force: bool = False, verbose: bool = False, extra_flags=(), name=None) -> Path:
     """Compiles every CUDA source for sm_100a and links the shared library. Returns its path.
 
-    ``trace=True`` builds the variant with in-kernel timelines (-DKD_TRACE) as
-    libkd_attention_trace.so; it is a debugging aid and is never loaded by the package itself."""
-    lib_path = LIB_DIR / "libkd_attention_trace.so" if trace else LIB_PATH
-    if name:  # experimental variant built with extra compiler flags
+    ``name`` + ``extra_flags`` build a variant of the same sources as libkd_attention_<name>.so (the
+    wait time-out test builds one with a short wait limit); the package itself loads only the
+    default library unless KD_LIB_PATH says otherwise."""
+    lib_path = LIB_PATH
+    if name:
         lib_path = LIB_DIR / f"libkd_attention_{name}.so"
-    if not trace and not name and not force and not _stale():
+        deps = [CSRC / s for s in SOURCES + HEADERS] + [INCLUDE_DIR / "kd_attention.h"]
+        if not force and lib_path.exists() and all(d.stat().st_mtime <= lib_path.stat().st_mtime for d in deps):
+            return lib_path
+    elif not force and not _stale():
         return LIB_PATH
     LIB_DIR.mkdir(exist_ok=True)
-    obj_dir = LIB_DIR / (f"obj_{name}" if name else "obj_trace" if trace else "obj")
+    obj_dir = LIB_DIR / (f"obj_{name}" if name else "obj")
     obj_dir.mkdir(exist_ok=True)
     nvcc = _nvcc()
 
     def compile_one(src: str) -> Path:
         obj = obj_dir / (src + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, *(["-DKD_TRACE"] if trace else []), *extra_flags, "-c", str(CSRC / src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, *extra_flags, "-c", str(CSRC / src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         r = subprocess.run(cmd, capture_output=True, text=True)
@@ -81,5 +85,5 @@ def build(force: bool = False, verbose: bool = False, trace: bool = False, extra
 
 
 if __name__ == "__main__":
-    p = build(force="--force" in sys.argv, verbose="-v" in sys.argv, trace="--trace" in sys.argv)
+    p = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(p)

@@ -98,80 +98,3 @@ def cocktail_scores(x_embed: torch.Tensor, tokens: torch.Tensor, special_tokens=
     rows = torch.arange(x_embed.shape[0], device=x_embed.device)
     h_context = x_embed[rows, first_mask.clamp(min=0)] * (first_mask >= 0).unsqueeze(1).to(x_embed.dtype)
     return torch.einsum("bd,bnd->bn", h_context, h_spans)
-
-
-def _bench():
-    """python -m kerneldev_b200.cocktail: forward + backward of span_means with CUDA events on batches of
-    the reference's model width (d_model 1024) and, beside it, the same computation as written in
-    model.py:276-293 (.nonzero() + a Python loop over rows and spans) on the same device."""
-    import json
-    import time
-
-    import numpy as np
-
-    dev = torch.device("cuda:0")
-    st = SPECIAL_TOKENS
-    out = []
-    for B, T, C, dtype in ((4, 1024, 1024, torch.float32), (16, 4096, 1024, torch.bfloat16)):
-        rng = np.random.default_rng(B * T)
-        x = rng.integers(6, 300, size=(B, T))
-        span_tokens = 0
-        for b in range(B):
-            t = int(rng.integers(40, 200))
-            x[b, 5] = st["[MASK]"]
-            while True:
-                ln = int(rng.integers(16, 129))
-                if t + ln + 2 >= T - 2:
-                    break
-                x[b, t] = st["[SPAN]"]; x[b, t + ln + 1] = st["[ES]"]
-                span_tokens += ln
-                t += ln + 2 + int(rng.integers(0, 40))
-        xt = torch.as_tensor(x, device=dev)
-        e = torch.randn((B, T, C), device=dev, dtype=dtype, requires_grad=True)
-
-        def ours():
-            h = span_means(e, xt)
-            h.backward(torch.ones_like(h))
-            e.grad = None
-
-        def reference_formulation():
-            span_starts = (xt == st["[SPAN]"]).nonzero()
-            span_ends = (xt == st["[ES]"]).nonzero()
-            batch_indices = span_starts[:, 0]
-            max_spans = (xt == st["[SPAN]"]).sum(dim=1).max()
-            h_spans = e.new_zeros(B, max_spans, C)
-            for i in range(B):
-                st_i = span_starts[batch_indices == i, 1]
-                ed_i = span_ends[batch_indices == i, 1]
-                for j, (s0, e0) in enumerate(zip(st_i, ed_i)):
-                    if s0 + 1 < e0:
-                        h_spans[i, j] = e[i, s0 + 1:e0].mean(dim=0)
-            h_spans.backward(torch.ones_like(h_spans))
-            e.grad = None
-
-        for _ in range(3):
-            ours()
-        torch.cuda.synchronize()
-        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(20):
-            ours()
-        b_.record()
-        torch.cuda.synchronize()
-        us = a.elapsed_time(b_) / 20 * 1e3
-        reference_formulation()
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        reference_formulation()
-        torch.cuda.synchronize()
-        us_ref = (time.perf_counter() - t0) * 1e6
-        es = e.element_size()
-        # forward reads every span token once and writes h; backward reads grad_h and writes all of grad_x
-        algo_bytes = span_tokens * C * es + B * T * C * es
-        out.append({"B": B, "T": T, "C": C, "dtype": str(dtype).split(".")[-1], "span_tokens": span_tokens,
-                    "fwd_bwd_us": round(us, 1), "GBps": round(algo_bytes / us / 1e3, 1), "reference_formulation_us": round(us_ref, 1)})
-    print(json.dumps(out))
-
-
-if __name__ == "__main__":
-    _bench()

@@ -53,29 +53,22 @@ struct BwdArgs {
   int64_t dk_sb, dk_sh, dk_st;
   void* dv;
   int64_t dv_sb, dv_sh, dv_st;
-  unsigned long long* trace;  // timeline buffer of KD_TRACE builds, else null
 };
 
 template <int HD>
 struct BwdCfg {
   static constexpr int KBLK = HD / 64;
   static constexpr int TILE_BYTES = KD_TILE * HD * 2;
-#ifndef KD_BWD_NBUF
-#define KD_BWD_NBUF 3
-#endif
-  static constexpr int NBUF = (HD == 64) ? KD_BWD_NBUF : 2;     // score / dP buffers in TMEM
+  static constexpr int NBUF = (HD == 64) ? 3 : 2;     // score / dP buffers in TMEM
   static constexpr int STAGES = NBUF;                 // ring of (tile, tile) pairs
   static constexpr int NFIX = (HD == 64) ? 2 : 1;     // buffers for the per-head resident tile pair
   static constexpr int SMEM_FIX = 0;                               // NFIX x two resident tiles
   static constexpr int SMEM_RING = SMEM_FIX + NFIX * 2 * TILE_BYTES;  // STAGES x two streamed tiles
   static constexpr int SMEM_STAGE = SMEM_RING + STAGES * 2 * TILE_BYTES;  // per-warp staging
-#ifndef KD_BWD_NSUB
-#define KD_BWD_NSUB 2
-#endif
-  static constexpr int NSUB = KD_BWD_NSUB;            // warpgroups that share a 64-column unit (1 or 2)
+  static constexpr int NSUB = 2;                      // warpgroups that share a 64-column unit
   static constexpr int CPT = 2 / NSUB;                // 32-column chunks per compute thread and unit
   static constexpr int THREADS = 128 + 256 * NSUB;    // four light warps + 2 * NSUB compute warpgroups
-  static constexpr int REGS_COMPUTE = (NSUB == 2) ? KD_REGS_COMPUTE_BWD : KD_REGS_COMPUTE;
+  static constexpr int REGS_COMPUTE = KD_REGS_COMPUTE_BWD;
   static constexpr int STAGE_WORDS = 3 * 32 * CPT;                 // per warp: 32*CPT x {lse, delta, descriptor}
   static constexpr int SMEM_ACT = SMEM_STAGE + 8 * NSUB * STAGE_WORDS * 4;  // compacted entry list
   static constexpr int SMEM_TOTAL = SMEM_ACT + 128 * 2;
@@ -158,7 +151,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   __shared__ AbortFlag abortf;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  cta_trace(a.trace, 1);
   const int h0 = blockIdx.x * a.G, b = blockIdx.y;
   const int nh = min(a.G, a.H - h0);   // this CTA handles heads h0 .. h0 + nh - 1
   const int qt = a.order[((size_t)b * 3 + 1) * a.NT + blockIdx.z];   // longest lists first
@@ -207,11 +199,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tc_fence_after_sync();
   const uint32_t tbase = tmem_base_s;
   const int na = n_act_s;
-  Tracer tr;
-  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 3 || warp == 1 || warp == 4 || warp == 4 + 4 * C::NSUB),
-          blockIdx.z * 4 + (warp == 3 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));   // issuers and one warp of each stream
-  tr.ev(1);
-  cta_trace(a.trace, 2);
 
   if (warp < 4) {
     reg_dealloc<KD_REGS_ISSUE>();
@@ -296,7 +283,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
           for (int kk = 1; kk < HD / 16; ++kk) mma_ss64<true>(dst, adesc[kk], bdesc[kk], idesc_m1);
           mma_commit(smem_u32(&bar_s_full[buf]));
-          tr.ev(15);
           if (++buf == C::NBUF) { buf = 0; ++round; }
           if (i == 1 && ++stage == C::STAGES) { stage = 0; ring_parity ^= 1; }
         }
@@ -331,7 +317,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           }
           ok = mbar_wait(smem_u32(&bar_p_full[buf]), round_parity, &abortf, a.status, W_Q_PFULL);
           if (!ok) break;
-          tr.ev(10);
           tc_fence_after_sync();
           mma_ts64_p(tAcc, aop[0], bdesc[0], idesc_m2, u > 0 ? 1u : 0u);
 #pragma unroll
@@ -339,7 +324,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           if (i == 1) mma_commit(smem_u32(&bar_ring_empty[stage]));
           tc_fence_before_sync();
           mbar_arrive(smem_u32(&bar_m2_issued[buf]));
-          tr.ev(11);
           if (++buf == C::NBUF) { buf = 0; round_parity ^= 1; }
           if (i == 1 && ++stage == C::STAGES) stage = 0;
         }
@@ -432,12 +416,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           prefetch_kd(ent_next);
         }
         const uint32_t tS = tcol + buf * 128, tP = tS + 64;
-        tr.ev(21);
         ok = mbar_wait(sfull0 + buf * 8, rnd & 1u, &abortf, a.status, W_Q_SFULL);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
-        tr.ev(22);
 
 #pragma unroll
         for (int cc = 0; cc < CPT; ++cc) {
@@ -466,11 +448,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           // dS of the chunk as 16-bit A operand over the start of the scores it was made from (this thread's own row)
           tmem_st16(tS + cc * 32, pk);
         }
-        tr.ev(24);
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(pfull0 + buf * 8);
-        tr.ev(25);
         buf += 2;
         if (buf >= C::NBUF) { buf -= C::NBUF; ++rnd; }
       }
@@ -512,11 +492,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   }
 
-  tr.ev(31);
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tbase, 512);
-  cta_trace(a.trace, 3);
 }
 
 // =========================================================================================
@@ -543,7 +521,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   __shared__ AbortFlag abortf;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  cta_trace(a.trace, 1);
   const int h0 = blockIdx.x * a.G, b = blockIdx.y;
   const int nh = min(a.G, a.H - h0);   // this CTA handles heads h0 .. h0 + nh - 1
   const int kt = a.order[((size_t)b * 3 + 2) * a.NT + blockIdx.z];   // longest lists first
@@ -581,11 +558,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   tc_fence_after_sync();
   const uint32_t tbase = tmem_base_s;
   const uint16_t* list = sList;
-  Tracer tr;
-  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 3 || warp == 1 || warp == 4 || warp == 4 + 4 * C::NSUB),
-          blockIdx.z * 4 + (warp == 3 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));   // issuers and one warp of each stream
-  tr.ev(1);
-  cta_trace(a.trace, 2);
 
   if (warp < 4) {
     reg_dealloc<KD_REGS_ISSUE>();
@@ -615,7 +587,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           const int qt = list[e] & 0xFF;
           ok = mbar_wait(smem_u32(&bar_ring_empty[s]), ph ^ 1, &abortf, a.status, W_K_RINGEMPTY);
           if (!ok) break;
-          tr.ev(40);
           mbar_arrive_expect_tx(smem_u32(&bar_ring_full[s]), 2 * C::TILE_BYTES);
           const uint32_t dst = sRing + s * 2 * C::TILE_BYTES;
           for (int kb = 0; kb < C::KBLK; ++kb) {
@@ -671,7 +642,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
           for (int kk = 1; kk < HD / 16; ++kk) mma_ss64<true>(dst, adesc[kk], bdesc[kk], idesc_m1);
           mma_commit(smem_u32(&bar_s_full[buf]));
-          tr.ev(15);
           if (++buf == C::NBUF) { buf = 0; ++round; }
           if (i == 1 && ++stage == C::STAGES) { stage = 0; ring_parity ^= 1; }
         }
@@ -709,7 +679,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           }
           ok = mbar_wait(smem_u32(&bar_p_full[buf]), round_parity, &abortf, a.status, W_K_PFULL);
           if (!ok) break;
-          tr.ev(10);
           tc_fence_after_sync();
           // dV += P^T_u dO_u   (P^T_u on top of S^T_u)
           mma_ts64_p(tDV, aop[0], bdo[0], idesc_m2, u > 0 ? 1u : 0u);
@@ -722,7 +691,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           if (i == 1) mma_commit(smem_u32(&bar_ring_empty[stage]));
           tc_fence_before_sync();
           mbar_arrive(smem_u32(&bar_m2_issued[buf]));
-          tr.ev(11);
           if (++buf == C::NBUF) { buf = 0; round_parity ^= 1; }
           if (i == 1 && ++stage == C::STAGES) stage = 0;
         }
@@ -796,7 +764,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       for (int e = 0; e < n; ++e) {
         const uint32_t ent = ent_next;
         const uint32_t cls = ent >> 8;
-        tr.ev(20);
         __syncwarp();
 #pragma unroll
         for (int cc = 0; cc < CPT; ++cc) {
@@ -805,7 +772,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           st_buf[2 * QW + cc * 32 + lane] = pre_desc[cc];
         }
         __syncwarp();
-        tr.ev(41);
         uint32_t mk[CPT];   // visibility of this key for the chunks' queries
 #pragma unroll
         for (int cc = 0; cc < CPT; ++cc) mk[cc] = 0xFFFFFFFFu;
@@ -825,7 +791,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             }
           }
         }
-        tr.ev(42);
         // the next entry: of this head or, at the end of the list, the first one again for the next head
         if (e + 1 < n) {
           ent_next = list[e + 1];
@@ -835,12 +800,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           prefetch(ent_next, h + 1);
         }
         const uint32_t tS = tcol + buf * 128, tP = tS + 64;
-        tr.ev(21);
         ok = mbar_wait(sfull0 + buf * 8, rnd & 1u, &abortf, a.status, W_K_SFULL);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
-        tr.ev(22);
 
 #pragma unroll
         for (int cc = 0; cc < CPT; ++cc) {
@@ -888,11 +851,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           tmem_st16(tS + cc * 32, pk_p);    // P^T of the chunk over the start of the scores it was made from
           tmem_st16(tP + cc * 32, pk_ds);   // dS^T of the chunk over the start of its dP^T
         }
-        tr.ev(24);
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(pfull0 + buf * 8);
-        tr.ev(25);
         buf += 2;
         if (buf >= C::NBUF) { buf -= C::NBUF; ++rnd; }
       }
@@ -904,7 +865,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
       }
-      tr.ev(30);
       tc_fence_after_sync();
       constexpr int EC = HD / (2 * C::NSUB);
       constexpr int ECH = EC < 32 ? EC : 32;   // columns per TMEM load
@@ -943,11 +903,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
   }
 
-  tr.ev(31);
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tbase, 512);
-  cta_trace(a.trace, 3);
 }
 
 template <int HD, bool kBf16>
@@ -963,7 +921,7 @@ static int launch_bwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
   a.B = p.B; a.H = p.H; a.T = p.T; a.NT = L.NT; a.NP = L.NP; a.Tpad = L.NT * KD_TILE;
   a.scale_log2 = p.sm_scale * 1.4426950408889634f;
   a.sm_scale = p.sm_scale;
-  a.G = heads_per_cta(p.B, p.H, L.NT, "KD_HEADS_PER_CTA_BWD");
+  a.G = heads_per_cta(p.B, p.H, L.NT, p.heads_per_cta);
   a.desc = pv.desc; a.fwd_cnt = pv.fwd_cnt; a.fwd_list = pv.fwd_list;
   a.bwd_cnt = pv.bwd_cnt; a.bwd_list = pv.bwd_list; a.status = pv.status; a.order = pv.order; a.tilebits = pv.tilebits;
   a.o = p.o.ptr; a.o_sb = p.o.stride_b; a.o_sh = p.o.stride_h; a.o_st = p.o.stride_t;
@@ -972,7 +930,7 @@ static int launch_bwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
   a.dq = p.dq.ptr; a.dq_sb = p.dq.stride_b; a.dq_sh = p.dq.stride_h; a.dq_st = p.dq.stride_t;
   a.dk = p.dk.ptr; a.dk_sb = p.dk.stride_b; a.dk_sh = p.dk.stride_h; a.dk_st = p.dk.stride_t;
   a.dv = p.dv.ptr; a.dv_sb = p.dv.stride_b; a.dv_sh = p.dv.stride_h; a.dv_st = p.dv.stride_t;
-  a.trace = trace_buffer();
+ 
   auto kq = attn_bwd_dq_kernel<HD, kBf16>;
   auto kk = attn_bwd_dkdv_kernel<HD, kBf16>;
   cudaError_t e = cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_ALLOC);

@@ -2,8 +2,6 @@
 // descriptors (so the single MMA-issuing thread spends two integer adds per MMA, not a 64-bit
 // descriptor build), work-list staging, 16-bit row stores.
 #pragma once
-#include <stdlib.h>
-
 #include "common.cuh"
 #include "mask_rule.cuh"
 #include "sm100_prims.cuh"
@@ -137,8 +135,8 @@ __device__ __forceinline__ void store_row16(uint16_t* dst, const uint32_t (&r)[1
 // best over batches 4-16 of config 2 and configs 1 and 3: backward 6 per SM, up to 8 heads; forward (a
 // CTA already holds two query tiles) 3 per SM, up to 4. Fewer CTAs than that lose more to imbalance
 // between sequences of different section lengths than the shared pipeline fill saves.
-inline int heads_per_cta(int B, int H, int items_per_batch, const char* env_name = "KD_HEADS_PER_CTA", int per_sm = 6,
-                         int g_max = 8) {
+inline int heads_per_cta(int B, int H, int items_per_batch, int forced, int per_sm = 6, int g_max = 8) {
+  if (forced >= 1) return forced < H ? forced : H;
   static int sm_count = 0;
   if (sm_count == 0) {
     int dev = 0;
@@ -150,10 +148,6 @@ inline int heads_per_cta(int B, int H, int items_per_batch, const char* env_name
   if (g < 1) g = 1;
   if (g > g_max) g = g_max;
   if (g > H) g = H;
-  if (const char* env = getenv(env_name)) {   // tuning aid
-    const int v = atoi(env);
-    if (v >= 1 && v <= H) g = v;
-  }
   return static_cast<int>(g);
 }
 

@@ -36,7 +36,6 @@ struct FwdArgs {
   const int32_t* fwd_cnt;
   const uint16_t* fwd_list;
   const uint8_t* order;   // [B][3][NT]; row 0 = pairs sorted by decreasing list length
-  unsigned long long* trace;
   uint32_t* status;
   void* o;
   int64_t o_sb, o_sh, o_st;
@@ -59,16 +58,11 @@ struct FwdCfg {
   static constexpr int SMEM_UNITS = SMEM_LIST + 128 * 2;           // unit list (<= 256 units)
   static constexpr int SMEM_CMD = SMEM_UNITS + 256 * 2;            // 256 x {S command, P V command} (uint4 each)
   static constexpr int SMEM_WCMD = SMEM_CMD + 256 * 2 * 16;        // 2 x 256 softmax commands (u32 each)
-  static constexpr int SMEM_XCHG = SMEM_WCMD + 2 * 256 * 4;        // row maxima / row sums exchanged between the warpgroups of a tile
-  static constexpr int SMEM_TOTAL = SMEM_XCHG + 2 * 2 * 2 * KD_TILE * 4;   // [tile][slot][half][row]
+  static constexpr int SMEM_TOTAL = SMEM_WCMD + 2 * 256 * 4;
   static constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;   // slack for 1024-byte alignment
-#ifndef KD_FWD_NSUB
-#define KD_FWD_NSUB 1
-#endif
-  static constexpr int NSUB = KD_FWD_NSUB;               // softmax warpgroups per query tile (1 or 2)
-  static constexpr int CW = KD_TILE / NSUB;              // score columns per softmax thread
-  static constexpr int THREADS = 128 + 256 * NSUB;
-  static constexpr int REGS_COMPUTE = (NSUB == 2) ? KD_REGS_COMPUTE_BWD : KD_REGS_COMPUTE;
+  static constexpr int CW = KD_TILE;                     // score columns per softmax thread: a whole row
+  static constexpr int THREADS = 384;                    // four light warps + one softmax warpgroup per query tile
+  static constexpr int REGS_COMPUTE = KD_REGS_COMPUTE;
   // TMEM columns: NBUF score buffers of 128, then O0 and O1 (HD each)
   static constexpr uint32_t TM_O0 = NBUF * 128, TM_O1 = NBUF * 128 + HD;
   static_assert(TM_O1 + HD <= 512, "TMEM budget");
@@ -90,7 +84,7 @@ __device__ __forceinline__ int wcmd_buf(uint32_t c) { return (c >> 10) & 3; }
 // wait-site codes reported in the status word
 enum : uint32_t {
   W_F_QFULL = 0x101, W_F_KEMPTY = 0x102, W_F_VEMPTY = 0x103, W_F_KFULL = 0x104, W_F_VFULL = 0x105,
-  W_F_PFULL = 0x106, W_F_SFULL = 0x107, W_F_PVDONE = 0x108, W_F_PVISSUED = 0x109, W_F_QEMPTY = 0x10A, W_F_OFREE = 0x10B, W_F_XCHG = 0x10C,
+  W_F_PFULL = 0x106, W_F_SFULL = 0x107, W_F_PVDONE = 0x108, W_F_PVISSUED = 0x109, W_F_QEMPTY = 0x10A, W_F_OFREE = 0x10B,
 };
 
 template <int HD, bool kBf16>
@@ -111,7 +105,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   __shared__ __align__(8) uint64_t bar_q_full[C::NQ], bar_q_empty[C::NQ], bar_k_full[C::KST], bar_k_empty[C::KST],
       bar_v_full[C::VST], bar_v_empty[C::VST], bar_s_full[2 * C::NBUF], bar_p_full[C::NBUF], bar_pv_issued[C::NBUF],
-      bar_pv_done[2], bar_o_free[2], bar_xchg[2];
+      bar_pv_done[2], bar_o_free[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int n_units_s, n_own_s[2];
   __shared__ AbortFlag abortf;
@@ -143,15 +137,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // phase of the barriers it waits on, which is what makes a parity wait sound
       mbar_init(smem_u32(&bar_s_full[2 * s]), 1);
       mbar_init(smem_u32(&bar_s_full[2 * s + 1]), 1);
-      mbar_init(smem_u32(&bar_p_full[s]), 128 * C::NSUB);
+      mbar_init(smem_u32(&bar_p_full[s]), 128);
       mbar_init(smem_u32(&bar_pv_issued[s]), 1);
     }
     mbar_init(smem_u32(&bar_pv_done[0]), 1);
     mbar_init(smem_u32(&bar_pv_done[1]), 1);
-    mbar_init(smem_u32(&bar_xchg[0]), 256);   // both warpgroups of a tile have published their half-row value
-    mbar_init(smem_u32(&bar_xchg[1]), 256);
-    mbar_init(smem_u32(&bar_o_free[0]), 128 * C::NSUB);
-    mbar_init(smem_u32(&bar_o_free[1]), 128 * C::NSUB);
+    mbar_init(smem_u32(&bar_o_free[0]), 128);
+    mbar_init(smem_u32(&bar_o_free[1]), 128);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -244,11 +236,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_after_sync();
   const uint32_t tbase = tmem_base_s;
   const int U = n_units_s;
-  Tracer tr;
-  tr.init(a.trace, blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 3 || warp == 1 || warp == 4 || warp == 4 + 4 * C::NSUB),
-          blockIdx.z * 4 + (warp == 3 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : 3));
-  tr.ev(1);
-  tr.acc_init();
 
   if (warp < 4) {
     reg_dealloc<KD_REGS_ISSUE>();
@@ -323,7 +310,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         ok = mbar_wait(smem_u32(&bar_q_full[qb]), (hh / C::NQ) & 1, &abortf, a.status, W_F_QFULL);
         const uint32_t q_off = qb * (2 * C::TILE_BYTES >> 4);
         for (int u = 0; u < U && ok; ++u) {
-          tr.tb();
           const uint4 c = sCmd[2 * u];
           // operands of the unit, formed ahead of the waits
           const uint32_t d = tbase + buf * 128;
@@ -339,12 +325,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             ok = mbar_wait(smem_u32(&bar_pv_issued[buf]), (round - 1) & 1, &abortf, a.status, W_F_PVISSUED);
             if (!ok) break;
           }
-          tr.te(1);
           if (c.z & CMD_WAIT) {
             ok = mbar_wait(smem_u32(&bar_k_full[kstage]), kparity, &abortf, a.status, W_F_KFULL);
             if (!ok) break;
           }
-          tr.te(2);
           tc_fence_after_sync();
           mma_ss64<false>(d, qdesc[0], kdesc[0], idesc_s);
 #pragma unroll
@@ -354,8 +338,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             mma_commit(smem_u32(&bar_k_empty[kstage]));
             if (++kstage == C::KST) { kstage = 0; kparity ^= 1; }
           }
-          tr.ev(15);
-          tr.te(3);
           if (++buf == C::NBUF) {
             buf = 0;
             ++round;
@@ -372,7 +354,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       uint32_t round_parity = 0, vparity = 0;
       for (int hh = 0; hh < nh && ok; ++hh) {
         for (int u = 0; u < U && ok; ++u) {
-          tr.tb();
           const uint4 c = sCmd[2 * u + 1];
           // operands of the unit, formed ahead of the waits
           const uint32_t vlo = c.y + vstage * (C::TILE_BYTES >> 4);
@@ -382,13 +363,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
           for (int kk = 0; kk < KD_TILE / 16; ++kk) {
             vdesc[kk] = desc64(vlo + koff_mnmajor(kk), hi);
-            // P of 16 keys = 8 packed columns; each softmax warpgroup writes its keys at the start of its own score columns
-            pop[kk] = aP + ((C::NSUB == 2) ? (kk >> 2) * 64 + (kk & 3) * 8 : kk * 8);
+            pop[kk] = aP + kk * 8;   // P of 16 keys = 8 packed columns at the start of the score buffer
           }
           ok = mbar_wait(smem_u32(&bar_p_full[buf]), round_parity, &abortf, a.status, W_F_PFULL);
           if (!ok) break;
-          tr.te(1);
-          tr.ev(10);
           if (c.z & CMD_WAIT) {
             ok = mbar_wait(smem_u32(&bar_v_full[vstage]), vparity, &abortf, a.status, W_F_VFULL);
             if (!ok) break;
@@ -401,7 +379,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             ok = mbar_wait(smem_u32(&bar_o_free[i]), (hh - 1) & 1, &abortf, a.status, W_F_OFREE);
             if (!ok) break;
           }
-          tr.te(2);
           tc_fence_after_sync();
           const uint32_t dO = tbase + C::TM_O0 + i * HD;
           mma_ts64_p(dO, pop[0], vdesc[0], idesc_o, acc0);
@@ -415,8 +392,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           // hand the buffer back to the S issuer, ordered after the MMAs above
           tc_fence_before_sync();
           mbar_arrive(smem_u32(&bar_pv_issued[buf]));
-          tr.ev(11);
-          tr.te(3);
           if (++buf == C::NBUF) {
             buf = 0;
             round_parity ^= 1;
@@ -427,22 +402,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   } else {
     reg_alloc<C::REGS_COMPUTE>();
     // ------------------------------ softmax warpgroups ------------------------------
-    // NSUB warpgroups share a query tile; each thread owns one row and CW of its 128 score columns.
-    // With two warpgroups per tile the row maximum (per unit) and the row sum (per head) are
-    // exchanged through shared memory and a named barrier of the two warpgroups.
-    constexpr int NS = C::NSUB, CW = C::CW, NW = CW / 32;
-    const int g = (warp - 4) >> 2;        // warpgroup
-    const int i = g / NS;                 // query tile of the pair
-    const int sub = g % NS;               // which CW columns of a unit
+    // One warpgroup per query tile; each thread owns one row of 128 scores.
+    constexpr int CW = C::CW, NW = CW / 32;
+    const int i = (warp - 4) >> 2;        // warpgroup = query tile of the pair
     const int wq = warp & 3;              // TMEM lane quadrant of this warp
     const int row = wq * 32 + lane;       // row inside the tile
     const int qtile = 2 * pair + i;
     const int qi = qtile * KD_TILE + row;  // token index of this thread's query
     const bool tile_valid = qtile < a.NT;
     uint32_t* kd_buf = sKdesc + (size_t)(warp - 4) * CW;   // this warp's copy of its keys' descriptors
-    float* xchg = reinterpret_cast<float*>(smem + C::SMEM_XCHG) + i * (2 * 2 * KD_TILE);   // [slot][half][row]
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
-    const uint32_t tO = tbase + lane_base + (i == 0 ? C::TM_O0 : C::TM_O1) + sub * (HD / NS);   // this thread's share of O
+    const uint32_t tO = tbase + lane_base + (i == 0 ? C::TM_O0 : C::TM_O1);   // this thread's row of O
     const float c = a.scale_log2;
 
     const uint32_t qd = tile_valid ? a.desc[(size_t)b * a.Tpad + qi] : 0u;
@@ -458,8 +428,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     for (int w = 0; w < NW; ++w) { kd_pre[w] = 0u; tb_pre[0][w] = 0u; tb_pre[1][w] = 0u; tb_pre[2][w] = 0u; }
     auto prefetch_kd = [&](uint32_t cmd) {
       if (wcmd_class(cmd) == KD_TILE_PARTIAL) {
-        const uint32_t* src = a.desc + (size_t)b * a.Tpad + (size_t)wcmd_kt(cmd) * KD_TILE + sub * CW;
-        const uint32_t* tbp = a.tilebits + ((size_t)b * a.NT + wcmd_kt(cmd)) * 32 + sub * NW;
+        const uint32_t* src = a.desc + (size_t)b * a.Tpad + (size_t)wcmd_kt(cmd) * KD_TILE;
+        const uint32_t* tbp = a.tilebits + ((size_t)b * a.NT + wcmd_kt(cmd)) * 32;
 #pragma unroll
         for (int w = 0; w < NW; ++w) {
           kd_pre[w] = src[w * 32 + lane];
@@ -475,10 +445,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     int buf_off = 0;            // (units of the heads done so far) mod NBUF: rotation of the buffers
     uint32_t sfull_par = 0;     // bit j: parity of the next phase of this tile's score barrier on buffer j
     int pv_seen = 0;            // P V products of this query tile issued so far (phases of bar_pv_done[i])
-    uint32_t xcnt = 0;          // exchanges so far: phase of bar_xchg[i] and slot (two slots, so that a fast warpgroup
-                                // cannot overwrite a value its partner has not read yet)
 
-    tr.tb();
     for (int hh = 0; hh < nh && ok; ++hh) {
     const int h = h0 + hh;
     float m = -INFINITY, l = 0.f;
@@ -489,8 +456,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int kt = wcmd_kt(cmd);
       int buf = wcmd_buf(cmd) + buf_off;
       if (buf >= C::NBUF) buf -= C::NBUF;
-      const uint32_t tS = tbase + lane_base + buf * 128 + sub * CW;
-      tr.ev(20);
+      const uint32_t tS = tbase + lane_base + buf * 128;
       uint32_t tb[3][NW];
       if (cls == KD_TILE_PARTIAL) {
         __syncwarp();
@@ -505,15 +471,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         cmd_next = wcmd[k + 1 < n_own ? k + 1 : 0];
         prefetch_kd(cmd_next);
       }
-      tr.ev(21);
-      tr.te(7);
       ok = mbar_wait(smem_u32(&bar_s_full[2 * buf + i]), (sfull_par >> buf) & 1u, &abortf, a.status, W_F_SFULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       sfull_par ^= 1u << buf;
       tc_fence_after_sync();
-      tr.ev(22);
-      tr.te(1);
 
       float sc[CW];
 #pragma unroll
@@ -524,15 +486,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int j = 0; j < 32; ++j) sc[cb * 32 + j] = __uint_as_float(r[j]);
       }
       tmem_wait_ld();
-      tr.ev(23);
-      tr.te(2);
       if (cls == KD_TILE_PARTIAL) {
         // The row's visibility mask comes from the tile's class masks with a few word-wide
         // operations; only the "same span" term needs the individual key descriptors.
-        const int j0 = kt * KD_TILE + sub * CW;
+        const int j0 = kt * KD_TILE;
         uint32_t mk[NW];
         query_row_mask<NW>(qd, qi, j0, tb[0], tb[1], tb[2], mk);
-        tr.ev(26);
         uint32_t any_ins = 0u;
 #pragma unroll
         for (int w = 0; w < NW; ++w) any_ins |= tb[2][w];
@@ -545,13 +504,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                           (span_match_key(key, k4.z) << ((j + 2) & 31)) | (span_match_key(key, k4.w) << ((j + 3) & 31));
           }
         }
-        tr.ev(27);
 #pragma unroll
         for (int j = 0; j < CW; ++j)
           if ((mk[j >> 5] & (1u << (j & 31))) == 0u) sc[j] = -INFINITY;
-        tr.ev(28);
       }
-      tr.te(3);
       // four independent chains for the row maximum and for the row sum: a single chain of
       // dependent operations would be latency-bound
       float mx4[4] = {sc[0], sc[1], sc[2], sc[3]};
@@ -563,17 +519,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mx4[3] = fmaxf(mx4[3], sc[j + 3]);
       }
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      if constexpr (NS == 2) {
-        // the other warpgroup of this tile holds the other half of the row
-        float* slot = xchg + (xcnt & 1u) * (2 * KD_TILE);
-        slot[sub * KD_TILE + row] = mx;
-        mbar_arrive(smem_u32(&bar_xchg[i]));
-        ok = mbar_wait(smem_u32(&bar_xchg[i]), xcnt & 1u, &abortf, a.status, W_F_XCHG);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        mx = fmaxf(mx, slot[(sub ^ 1) * KD_TILE + row]);
-        ++xcnt;
-      }
       // The running maximum is refreshed only when it would grow by more than 2^8 in the
       // exponent; until then the stale value is used consistently for P, l and O, which leaves
       // the normalised result unchanged and skips most O rescales.
@@ -599,9 +544,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         pk[j / 2 + 1] = pack2<kBf16>(p2, p3);
       }
       const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      tr.ev(32);
-      tr.te(4);
-      l = l * alpha + sum;   // with two warpgroups per tile: the sum over this thread's columns only
+      l = l * alpha + sum;
       m = m_new;
 #pragma unroll
       for (int cb = 0; cb < CW / 64; ++cb) {
@@ -617,13 +560,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
       }
-      tr.ev(33);
-      tr.te(5);
       if (__any_sync(0xffffffffu, need_rescale)) {
         tc_fence_after_sync();
         const float f = need_rescale ? alpha : 1.f;
 #pragma unroll
-        for (int cb = 0; cb < HD / NS / 32; ++cb) {
+        for (int cb = 0; cb < HD / 32; ++cb) {
           uint32_t r[32];
           tmem_ld32(tO + cb * 32, r);
           tmem_wait_ld();
@@ -632,12 +573,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tmem_st32(tO + cb * 32, r);
         }
       }
-      tr.ev(24);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&bar_p_full[buf]));
-      tr.ev(25);
-      tr.te(6);
       ++nact;
       ++pv_seen;
     }
@@ -650,28 +588,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       ok = mbar_wait(smem_u32(&bar_pv_done[i]), (pv_seen - 1) & 1, &abortf, a.status, W_F_PVDONE);
       ok = __all_sync(0xffffffffu, ok);
     }
-    tr.ev(30);
-    if constexpr (NS == 2) {
-      // total row sum = the two halves' sums (both carry the same running maximum)
-      if (ok) {
-        float* slot = xchg + (xcnt & 1u) * (2 * KD_TILE);
-        slot[sub * KD_TILE + row] = l;
-        mbar_arrive(smem_u32(&bar_xchg[i]));
-        ok = mbar_wait(smem_u32(&bar_xchg[i]), xcnt & 1u, &abortf, a.status, W_F_XCHG);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) l += slot[(sub ^ 1) * KD_TILE + row];
-        ++xcnt;
-      }
-    }
-    if (ok && tile_valid && qi < a.T && sub == 0) {
+    if (ok && tile_valid && qi < a.T) {
       a.lse[((size_t)b * a.H + h) * a.T + qi] = (l > 0.f) ? (m * c + log2f(l)) : -INFINITY;
     }
     if (ok) {
       tc_fence_after_sync();
       const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
-      uint16_t* orow = reinterpret_cast<uint16_t*>(a.o) + (size_t)b * a.o_sb + (size_t)h * a.o_sh + (size_t)qi * a.o_st + sub * (HD / NS);
+      uint16_t* orow = reinterpret_cast<uint16_t*>(a.o) + (size_t)b * a.o_sb + (size_t)h * a.o_sh + (size_t)qi * a.o_st;
 #pragma unroll
-      for (int cb = 0; cb < HD / NS / 32; ++cb) {
+      for (int cb = 0; cb < HD / 32; ++cb) {
         uint32_t r[32];
         if (nact > 0) {
           tmem_ld32(tO + cb * 32, r);
@@ -680,7 +605,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
-        if (cb == HD / NS / 32 - 1 && nact > 0) {
+        if (cb == HD / 32 - 1 && nact > 0) {
           // this thread's share of O_i has been read out: the next head's first product may overwrite it
           tc_fence_before_sync();
           mbar_arrive(smem_u32(&bar_o_free[i]));
@@ -691,8 +616,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }  // heads
   }
 
-  tr.ev(31);
-  tr.flush();
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tbase, 512);
@@ -709,9 +632,9 @@ static int launch_fwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
   FwdArgs a;
   a.B = p.B; a.H = p.H; a.T = p.T; a.NT = L.NT; a.NP = L.NP; a.Tpad = L.NT * KD_TILE;
   a.scale_log2 = p.sm_scale * 1.4426950408889634f;
-  a.G = heads_per_cta(p.B, p.H, L.NP, "KD_HEADS_PER_CTA", 3, 4);
+  a.G = heads_per_cta(p.B, p.H, L.NP, p.heads_per_cta, 3, 4);
   a.desc = pv.desc; a.fwd_cnt = pv.fwd_cnt; a.fwd_list = pv.fwd_list; a.status = pv.status;
-  a.order = pv.order; a.trace = trace_buffer(); a.tilebits = pv.tilebits;
+  a.order = pv.order; a.tilebits = pv.tilebits;
   a.o = p.o.ptr; a.o_sb = p.o.stride_b; a.o_sh = p.o.stride_h; a.o_st = p.o.stride_t;
   a.lse = p.lse;
   auto kern = attn_fwd_kernel<HD, kBf16>;

@@ -18,13 +18,6 @@ int set_error(int code, const char* fmt, ...) {
   return code;
 }
 
-#ifdef KD_TRACE
-static unsigned long long* g_trace = nullptr;
-unsigned long long* trace_buffer() { return g_trace; }
-#else
-unsigned long long* trace_buffer() { return nullptr; }
-#endif
-
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -90,6 +83,7 @@ static int check_attn(const kd_attn_params* p, bool backward) {
   if (p->T > 128 * KD_TILE) return set_error(KD_ERR_LIMIT, "T=%d exceeds the maximum of %d tokens", p->T, 128 * KD_TILE);
   if (p->H > 65535 || p->B > 65535) return set_error(KD_ERR_LIMIT, "B and H must not exceed 65535");
   if (!(p->sm_scale > 0.f) || !(p->sm_scale < 1e30f)) return set_error(KD_ERR_ARG, "sm_scale must be positive and finite");
+  if (p->heads_per_cta < 0) return set_error(KD_ERR_ARG, "heads_per_cta must be 0 (automatic) or positive");
   if (!p->plan) return set_error(KD_ERR_ARG, "plan is null (call kd_classify first)");
   if (!p->lse) return set_error(KD_ERR_ARG, "lse is null");
   if (!p->o.ptr) return set_error(KD_ERR_ARG, "o is null");
@@ -112,15 +106,6 @@ static int check_attn(const kd_attn_params* p, bool backward) {
 using namespace kd;
 
 extern "C" {
-
-#ifdef KD_TRACE
-// debug builds only: device buffer of 256 x uint64 per (traced CTA, role) that kernels fill with
-// (event id << 48 | clock64) records
-int kd_debug_set_trace(void* buf) {
-  kd::g_trace = static_cast<unsigned long long*>(buf);
-  return 0;
-}
-#endif
 
 int kd_version(void) { return 1; }
 
@@ -186,6 +171,8 @@ int kd_attn_bwd_static(const kd_attn_params* p, void* stream) {
   if (p->B < 1 || p->H < 1 || p->T < 1) return set_error(KD_ERR_ARG, "bad shape B=%d H=%d T=%d", p->B, p->H, p->T);
   int rc = check_device();
   if (rc) return rc;
+  if ((p->bwd_phases & 3) != 0 && (p->bwd_phases & 3) != 3)
+    return set_error(KD_ERR_ARG, "kd_attn_bwd_static runs all backward kernels in one call: bwd_phases must be 0 or 3");
   kd_attn_params q = *p;   // same call as kd_attn_bwd, with the scratch pointed at the library's own array
   float* scratch = nullptr;
   if ((rc = static_delta_address((size_t)p->B * p->H * p->T, &scratch)) != 0) return rc;

@@ -55,9 +55,6 @@ int set_error(int code, const char* fmt, ...);
 int encode_tensor_map(CUtensorMap* out, const kd_tensor& t, int B, int H, int T, int D, int dtype,
                       int box_rows, const char* name);
 
-// timeline buffer of KD_TRACE builds (null otherwise)
-unsigned long long* trace_buffer();
-
 int launch_classify(const kd_meta& m, void* plan, cudaStream_t stream);
 int launch_mask_dense(const void* plan, int B, int T, uint8_t* out, cudaStream_t stream);
 int launch_attn_fwd(const kd_attn_params& p, cudaStream_t stream);

@@ -350,78 +350,6 @@ __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
-// ---------------------------------------------------------------------------------------
-// optional in-kernel timeline (compiled in only with -DKD_TRACE; used to find the critical path)
-// ---------------------------------------------------------------------------------------
-#ifdef KD_TRACE
-#ifndef KD_TRACE_SLOTS
-#define KD_TRACE_SLOTS 256
-#endif
-#ifndef KD_TRACE_MASK
-#define KD_TRACE_MASK 0xFFFFFFFFFFFFFFFFull   // bit id: record event id (ids below 64)
-#endif
-struct Tracer {
-  unsigned long long* p;
-  int n;
-  __device__ __forceinline__ void init(unsigned long long* base, bool on, int slot) {
-    p = (on && base) ? base + (size_t)slot * KD_TRACE_SLOTS : nullptr;
-    n = 0;
-  }
-  // time accumulators (KD_TRACE_ACC builds): tb() starts a section, te(k) adds its length to
-  // counter k, flush() stores the counters as the role's record
-  long long t_, acc_[8];
-  __device__ __forceinline__ void acc_init() {
-#ifdef KD_TRACE_ACC
-    for (int k = 0; k < 8; ++k) acc_[k] = 0;
-#endif
-  }
-  __device__ __forceinline__ void tb() {
-#ifdef KD_TRACE_ACC
-    if (p) t_ = clock64();
-#endif
-  }
-  __device__ __forceinline__ void te(int k) {
-#ifdef KD_TRACE_ACC
-    if (p) { const long long now = clock64(); acc_[k] += now - t_; t_ = now; }
-#endif
-  }
-  __device__ __forceinline__ void flush() {
-#ifdef KD_TRACE_ACC
-    if (p) { for (int k = 0; k < 8; ++k) p[1 + k] = static_cast<unsigned long long>(acc_[k]); p[0] = 8; }
-#endif
-  }
-  __device__ __forceinline__ void ev(uint32_t id) {
-    if (((KD_TRACE_MASK >> (id & 63u)) & 1ull) && p && n < KD_TRACE_SLOTS - 1) {
-      p[1 + n] = (static_cast<unsigned long long>(id) << 48) | (static_cast<unsigned long long>(clock64()) & 0xFFFFFFFFFFFFull);
-      ++n;
-      p[0] = n;
-    }
-  }
-};
-// per-CTA record behind the per-role timelines: {SM id, globaltimer at three points of the kernel}
-#ifndef KD_TRACE_CTA_BASE
-#define KD_TRACE_CTA_BASE (256 * KD_TRACE_SLOTS)
-#endif
-__device__ __forceinline__ void cta_trace(unsigned long long* base, int slot) {
-  if (base && threadIdx.x == 0) {
-    const size_t cta = blockIdx.x + (size_t)gridDim.x * (blockIdx.y + (size_t)gridDim.y * blockIdx.z);
-    unsigned long long* p = base + KD_TRACE_CTA_BASE + cta * 4;
-    if (slot == 1) { uint32_t sm; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm)); p[0] = sm; }
-    p[slot] = globaltimer_ns();
-  }
-}
-#else
-struct Tracer {
-  __device__ __forceinline__ void init(unsigned long long*, bool, int) {}
-  __device__ __forceinline__ void ev(uint32_t) {}
-  __device__ __forceinline__ void acc_init() {}
-  __device__ __forceinline__ void tb() {}
-  __device__ __forceinline__ void te(int) {}
-  __device__ __forceinline__ void flush() {}
-};
-__device__ __forceinline__ void cta_trace(unsigned long long*, int) {}
-#endif
-
 template <uint32_t kRegs>
 __device__ __forceinline__ void reg_dealloc() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));

@@ -34,6 +34,10 @@ __all__ = ["flash_attention", "generate_hadamard_signs", "hadamard_transform"]
 
 _DTYPES = {torch.float16: _capi.KD_F16, torch.bfloat16: _capi.KD_BF16}
 
+# Heads a CTA handles one after the other (kd_attn_params.heads_per_cta): 0 lets the library choose from
+# the grid size. Small problems get 1 by themselves, so the tests of the multi-head path set this.
+HEADS_PER_CTA = 0
+
 
 def _kd_tensor(t: torch.Tensor) -> _capi.KdTensor:
     return _capi.KdTensor(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
@@ -72,7 +76,17 @@ def _params(q, k, v, o, lse, plan, sm_scale):
     p.q, p.k, p.v, p.o = _kd_tensor(q), _kd_tensor(k), _kd_tensor(v), _kd_tensor(o)
     p.lse = lse.data_ptr()
     p.plan = plan.ptr
+    p.heads_per_cta = HEADS_PER_CTA
     return p
+
+
+def _after_launch(plan: AttentionPlan) -> None:
+    """Device-side failures (a bounded wait that gave up) are written to the plan's status word. The word
+    follows every launch to a pinned host mirror; ``plan.poll()`` at the next call raises from it without
+    a synchronisation. KD_CHECK_STATUS=1 synchronises and checks after every launch instead."""
+    plan.mirror_status()
+    if os.environ.get("KD_CHECK_STATUS") == "1":
+        plan.check_status()
 
 
 def _forward(q, k, v, plan: AttentionPlan, sm_scale: float, like_input: bool = False):
@@ -85,15 +99,15 @@ def _forward(q, k, v, plan: AttentionPlan, sm_scale: float, like_input: bool = F
     lse = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
     p = _params(q, k, v, o, lse, plan, sm_scale)
     stream = torch.cuda.current_stream(q.device).cuda_stream
+    plan.poll()
     with torch.cuda.device(q.device):
         _capi.check(_capi.load().kd_attn_fwd(ctypes.byref(p), stream))
-    if os.environ.get("KD_CHECK_STATUS") == "1":
-        plan.check_status()
+    _after_launch(plan)
     return o, lse
 
 
 def _backward(q, k, v, o, lse, d_o, plan: AttentionPlan, sm_scale: float, phases: int = 0, bufs=None,
-              like_input: bool = False):
+              like_input: bool = False, deterministic: bool = True):
     """One kd_attn_bwd call: returns (dQ, dK, dV). ``phases`` selects one of the two backward
     kernels (see kd_attn_params.bwd_phases); ``bufs`` = (dq, dk, dv, delta) reuses buffers."""
     q, k, v, d_o = _usable(q), _usable(k), _usable(v), _usable(d_o)
@@ -114,29 +128,31 @@ def _backward(q, k, v, o, lse, d_o, plan: AttentionPlan, sm_scale: float, phases
     p.delta = delta.data_ptr()
     p.bwd_phases = phases
     stream = torch.cuda.current_stream(q.device).cuda_stream
+    plan.poll()
     with torch.cuda.device(q.device):
         _capi.check(_capi.load().kd_attn_bwd(ctypes.byref(p), stream))
-    if os.environ.get("KD_CHECK_STATUS") == "1":
-        plan.check_status()
+    _after_launch(plan)
     return dq, dk, dv
 
 
 class _FlashAttentionFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, plan, sm_scale, like_input=False):
+    def forward(ctx, q, k, v, plan, sm_scale, like_input=False, deterministic=False):
         o, lse = _forward(q, k, v, plan, sm_scale, like_input)
         ctx.save_for_backward(q, k, v, o, lse)
         ctx.plan = plan
         ctx.sm_scale = sm_scale
         ctx.like_input = like_input
+        ctx.deterministic = deterministic
         ctx.mark_non_differentiable(lse)
         return o, lse
 
     @staticmethod
     def backward(ctx, d_o, _d_lse):
         q, k, v, o, lse = ctx.saved_tensors
-        dq, dk, dv = _backward(q, k, v, o, lse, d_o, ctx.plan, ctx.sm_scale, like_input=ctx.like_input)
-        return dq, dk, dv, None, None, None
+        dq, dk, dv = _backward(q, k, v, o, lse, d_o, ctx.plan, ctx.sm_scale, like_input=ctx.like_input,
+                               deterministic=ctx.deterministic)
+        return dq, dk, dv, None, None, None, None
 
 
 def _hadamard_call(x: torch.Tensor, signs, inverse: bool) -> torch.Tensor:
@@ -205,6 +221,7 @@ def flash_attention(
     return_attention_mask: bool = False,
     hadamard_signs: torch.Tensor | None = None,
     out_layout: str = "contiguous",
+    deterministic: bool = False,
 ):
     """Self-attention with the 4-section hierarchical mask; arguments and return value as the
     reference's ``flash_attention`` (original_kernel.py:2096-2168).
@@ -241,7 +258,7 @@ def flash_attention(
 
     if out_layout not in ("contiguous", "input"):
         raise ValueError("out_layout must be 'contiguous' or 'input'")
-    o, lse = _FlashAttentionFn.apply(q, k, v, plan, sm_scale, out_layout == "input")
+    o, lse = _FlashAttentionFn.apply(q, k, v, plan, sm_scale, out_layout == "input", bool(deterministic))
 
     if return_attention_mask:
         mask = plan.dense_mask().unsqueeze(1).expand(B, H, T, T)

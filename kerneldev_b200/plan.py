@@ -5,7 +5,17 @@ A plan holds the packed token descriptors, the class (EMPTY / FULL / PARTIAL) of
 metadata (``in_span``, ``span_id``, ``is_prefix``, ``lens``, ``causal``), not on the head, so one
 plan serves all heads and -- because ``model.GPTModel`` passes the same three metadata tensors
 to every layer (model.py:243-244) -- all layers of a step. Plans are cached on the identity and
-version of the metadata tensors.
+version of the metadata tensors (the cache keeps those tensors alive, so an address cannot be
+reused while its plan is cached). Metadata rewritten in place through raw pointers -- by
+kd_metadata_from_tokens into preallocated buffers, or through ``.data`` -- does not change a tensor's
+version: call ``clear_plan_cache()`` after such a write.
+
+Device status. Kernels report problems (a bounded wait that ran out, a span id out of range) in the
+plan's status word. After every launch the word is copied to a pinned host mirror with an
+asynchronous copy on the launching stream; the next call that uses the plan (or ``poll()``) looks at
+the mirror without synchronising and raises, so a failed launch surfaces one call later at the
+latest -- normally at the backward of the same step. ``KD_CHECK_STATUS=1`` makes every call
+synchronise and check at once.
 """
 from __future__ import annotations
 
@@ -69,11 +79,21 @@ class AttentionPlan:
             meta.lens = lens.data_ptr()
         meta.causal = 1 if causal else 0
         meta.rules = 1 if rules else 0
-        self._keep = keep  # metadata stays alive (and its addresses unique) while the plan is cached
-        stream = torch.cuda.current_stream(device).cuda_stream
+        # the caller's tensors and their converted copies stay alive while the plan is cached, so none of
+        # the addresses in the cache key can be handed to another tensor
+        self._keep = keep + [x for x in (in_span, span_id, is_prefix, lens) if x is not None]
+        off = self.layout.off_status
+        self._status_dev = self.buf[off:off + 4].view(torch.int32)
+        self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        cur = torch.cuda.current_stream(device)
         with torch.cuda.device(device):
-            _capi.check(_capi.load().kd_classify(ctypes.byref(meta), self.buf.data_ptr(), stream))
-        if os.environ.get("KD_PLAN_CHECK", "1") != "0":
+            _capi.check(_capi.load().kd_classify(ctypes.byref(meta), self.buf.data_ptr(), cur.cuda_stream))
+        # a plan used later from another stream must wait for the classifier
+        self._built_on = cur
+        self._built = torch.cuda.Event()
+        self._built.record(cur)
+        self.mirror_status()
+        if os.environ.get("KD_CHECK_STATUS") == "1":
             self.check_status()
 
     # ---- views into the plan buffer -------------------------------------------------------------
@@ -108,19 +128,42 @@ class AttentionPlan:
     def bwd_counts(self) -> torch.Tensor:
         return self._view(self.layout.off_bwd_cnt, self.B * self.NT * 4, torch.int32, (self.B, self.NT))
 
+    def use_on_current_stream(self) -> None:
+        """Orders the current stream after the classifier when the plan was built on another one."""
+        cur = torch.cuda.current_stream(self.device)
+        if cur != self._built_on:
+            cur.wait_event(self._built)
+
     def status(self) -> int:
         """Reads the device status word (synchronises the current stream)."""
-        off = self.layout.off_status
-        return int(self.buf[off:off + 4].view(torch.int32).item()) & 0xFFFFFFFF
+        return int(self._status_dev.item()) & 0xFFFFFFFF
+
+    def mirror_status(self) -> None:
+        """Enqueues a copy of the status word to the pinned host mirror behind the work just launched."""
+        self._status_host.copy_(self._status_dev, non_blocking=True)
+
+    def poll(self) -> None:
+        """Raises if the host mirror holds a status a finished launch reported. Never synchronises."""
+        s = int(self._status_host[0]) & 0xFFFFFFFF
+        if s:
+            self._report(s)
 
     def check_status(self) -> None:
+        """Synchronises the current stream, reads the device status word and raises if it is set."""
         s = self.status()
+        if s:
+            self._report(s)
+
+    def _report(self, s: int) -> None:
+        # the word is cleared so that one event is reported once and later launches start clean
+        self._status_dev.zero_()
+        self._status_host.zero_()
         if s & _capi.KD_STATUS_SPAN_RANGE:
             raise ValueError("span_id values must fit in 24 signed bits (|span_id| < 2**23)")
         if s & _capi.KD_STATUS_TIMEOUT:
-            raise RuntimeError(f"a device-side wait timed out (status 0x{s:08x}); results are invalid")
-        if s:
-            raise RuntimeError(f"device status 0x{s:08x}")
+            raise RuntimeError(f"a device-side wait timed out (status 0x{s:08x}, wait site 0x{s & 0xFFFF:x}); "
+                               "the results of that launch are invalid")
+        raise RuntimeError(f"device status 0x{s:08x}")
 
     def dense_mask(self) -> torch.Tensor:
         """bool (B, T, T) mask materialised on the device from the descriptors."""
@@ -143,6 +186,8 @@ def get_plan(B, T, device, in_span=None, span_id=None, is_prefix=None, lens=None
     plan = _CACHE.get(key)
     if plan is not None:
         _CACHE.move_to_end(key)
+        plan.use_on_current_stream()
+        plan.poll()
         return plan
     plan = AttentionPlan(B, T, device, in_span, span_id, is_prefix, lens, causal, rules)
     _CACHE[key] = plan

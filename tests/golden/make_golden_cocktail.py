@@ -14,7 +14,7 @@ import textwrap
 import numpy as np
 import torch
 
-REF = os.environ.get("REFERENCE_DIR", "/root/reference")
+REF = os.environ["REFERENCE_DIR"]   # path of a checkout of the reference project
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REF)
 sys.path.insert(0, HERE)

@@ -13,7 +13,7 @@ import textwrap
 import numpy as np
 import torch
 
-REF = os.environ.get("REFERENCE_DIR", "/root/reference")
+REF = os.environ["REFERENCE_DIR"]   # path of a checkout of the reference project
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REF)
 from data_builder import SPECIAL_TOKENS  # noqa: E402  (the reference's table)

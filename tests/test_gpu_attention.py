@@ -208,21 +208,154 @@ def test_unsupported_inputs_raise():
         flash_attention(q, q, q, lens=torch.tensor([128], device=DEV))  # int64 lens
 
 
-def test_hadamard_kernel_and_fused_use():
-    from kerneldev_b200 import flash_attention, generate_hadamard_signs, hadamard_transform
+def test_hadamard_kernel():
+    from kerneldev_b200 import generate_hadamard_signs, hadamard_transform
     B, H, T, D = 2, 4, 384, 128
     signs = generate_hadamard_signs(H, D, seed=3, device=DEV)
     assert torch.equal(signs.cpu(), ao.generate_hadamard_signs(H, D, seed=3))
-    q, k, v, do = rand_inputs(B, H, T, D, torch.float16, seed=8, outlier_frac=1e-3)
+    q, k, _, _ = rand_inputs(B, H, T, D, torch.float16, seed=8, outlier_frac=1e-3)
     for x in (q, k):
         y = hadamard_transform(x.to(DEV), signs)
         assert_close("hadamard", y, ao.hadamard_transform(x, signs.cpu()), atol=2e-2, rtol=2e-3)
     y64 = hadamard_transform(q[..., :64].contiguous().to(DEV).to(torch.bfloat16), None)
     assert_close("hadamard64", y64, ao.hadamard_transform(q[..., :64].to(torch.bfloat16)), atol=3e-2, rtol=1e-2)
-    ins, sid, pre, lens = ao.batch_metadata(5, B, T, prefix=(8, 32), context=(64, 128), n_spans=(2, 6), span_len=(8, 32))
+
+
+def _inverse_hadamard(x, signs):
+    """Transpose of ao.hadamard_transform: WHT(x) / sqrt(D) * signs[h] (maps gradients of the transformed
+    Q, K back to the inputs)."""
+    D = x.shape[-1]
+    return (x.float() @ ao.hadamard_matrix(D)) / (D ** 0.5) * signs[None, :, None, :]
+
+
+def hadamard_oracles(q, k, v, do, mask, signs, dtype):
+    """The two references for the Hadamard path (inputs on CPU, signs (H, D)):
+      (i)  fp32 attention on the UNTRANSFORMED inputs -- the transform is orthogonal, so this is the truth;
+      (ii) rounding-faithful: transform in fp32, round to `dtype` as the operator stores the transformed
+           Q and K, fp32 attention on those, gradients of the transformed tensors rounded to `dtype` and
+           mapped back in fp32. (ii) - (i) is the cost of storing the transformed tensors in 16 bits;
+           operator - (ii) is the error of the attention kernels themselves."""
+    r1 = ao.attention_fwd_bwd(q, k, v, do, mask)
+    qt = ao.hadamard_transform(q, signs).to(dtype).float()
+    kt = ao.hadamard_transform(k, signs).to(dtype).float()
+    o, lse, dqt, dkt, dv = ao.attention_fwd_bwd(qt, kt, v, do, mask)
+    r2 = (o, lse, _inverse_hadamard(dqt.to(dtype), signs), _inverse_hadamard(dkt.to(dtype), signs), dv)
+    return r1, r2, (qt, kt)
+
+
+@pytest.mark.parametrize("D,dtype", [(128, torch.float16), (64, torch.bfloat16), (64, torch.float16)])
+def test_hadamard_path_against_both_oracles(D, dtype):
+    """N(0,1) inputs: the Hadamard path holds the stated tolerance (atol 2e-2 / rtol 1e-2, LSE 1e-3) against
+    the untransformed fp32 oracle AND against the rounding-faithful one."""
+    from kerneldev_b200 import generate_hadamard_signs
+    B, H, T = 2, 4, 1024
+    signs = generate_hadamard_signs(H, D, seed=3, device=DEV)
+    q, k, v, do = rand_inputs(B, H, T, D, dtype, seed=8)
+    ins, sid, pre, lens = ao.batch_metadata(5, B, T, prefix=(8, 64), context=(256, 512), n_spans=(4, 12), span_len=(8, 48))
     got = run_op(q, k, v, do, ins, sid, pre, lens, hadamard_signs=signs)
-    # mathematical truth: attention on the untransformed inputs (the transform is orthogonal)
-    compare(q, k, v, do, ao.dense_mask(T, ins, sid, pre, lens), got, atol=6e-2, rtol=3e-2)
+    mask = ao.dense_mask(T, ins, sid, pre, lens)
+    r1, r2, _ = hadamard_oracles(q, k, v, do, mask, signs.cpu(), dtype)
+    for tag, ref in (("untransformed", r1), ("rounding-faithful", r2)):
+        assert_lse_close(got[1], ref[1])
+        for nm, g, r in zip(("O", "dQ", "dK", "dV"), (got[0], got[2], got[3], got[4]), (ref[0], ref[2], ref[3], ref[4])):
+            assert_close(f"{nm} vs {tag} oracle", g, r)
+
+
+def _outlier_inputs(B, H, T, D, dtype, seed):
+    """BASELINE config 3's distribution: N(0,1) with 0.1 % of the entries of Q, K, V replaced by N(0,20)."""
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    xs = []
+    for i in range(4):
+        x = torch.randn((B, H, T, D), generator=g, device=DEV)
+        if i < 3:
+            sel = torch.rand((B, H, T, D), generator=g, device=DEV) < 1e-3
+            x = torch.where(sel, torch.randn((B, H, T, D), generator=g, device=DEV) * 20.0, x)
+        xs.append(x.to(dtype))
+    return xs
+
+
+def _check_with_operand_bound(tag, got, ref, bounds, max_outside):
+    """Every element within atol 2e-2 + rtol 1e-2 |ref| + 2 x the first-order bound of rounding the 16-bit
+    MMA operands (oracle.operand_rounding_bounds); the share of elements outside the PLAIN tolerance is
+    reported and must stay below `max_outside`."""
+    shares = {}
+    for nm, g, r, bnd in zip(("O", "dQ", "dK", "dV"), (got[0], got[2], got[3], got[4]), (ref[0], ref[2], ref[3], ref[4]), bounds):
+        g = g.float().cpu()
+        err = (g - r).abs()
+        plain = 2e-2 + 1e-2 * r.abs()
+        assert torch.isfinite(g).all(), f"{nm}: non-finite"
+        worst = float((err / (plain + 2.0 * bnd)).max())
+        assert worst <= 1.0, f"{nm} vs {tag}: {worst:.2f} x (tolerance + operand-rounding bound), max err {float(err.max()):.4g}"
+        shares[nm] = float((err > plain).float().mean())
+        assert shares[nm] <= max_outside, f"{nm} vs {tag}: share {shares[nm]:.2e} of the elements outside atol 2e-2 / rtol 1e-2"
+    return shares
+
+
+def test_full_size_config3_hadamard_sampled_heads():
+    """BASELINE config 3 at full size: fp16, B=4, H=32, L=8192, D=128, 0.1 % N(0,20) outliers in Q, K, V,
+    seeded +-1 signs per head, config-3 section ranges; sampled (batch, head) pairs against both oracles.
+
+    With the outliers single products |dS_ij K_jd| reach the hundreds, so the rounding of ONE 16-bit dS (or
+    P) operand moves an output by more than an absolute 2e-2 whatever the kernel does: measured on a B200,
+    about 2e-5 of the dQ elements (and 3e-6 of dK) lie outside the plain tolerance, with AND without the
+    Hadamard step, and O and dV never do. The check therefore adds the first-order operand-rounding bound
+    to the tolerance and limits the share of elements outside the plain one to 1e-4."""
+    from kerneldev_b200 import generate_hadamard_signs, synthetic
+    B, H, T, D, dtype = 4, 32, 8192, 128, torch.float16
+    ins, sid, pre, lens = synthetic.batch_metadata(3, B, T, **synthetic.CONFIG_RANGES[3])
+    q, k, v, do = _outlier_inputs(B, H, T, D, dtype, seed=3)
+    signs = generate_hadamard_signs(H, D, seed=3, device=DEV)
+    got = run_op(q, k, v, do, ins, sid, pre, lens, hadamard_signs=signs)
+    for (b, h) in [(0, 0), (3, 31)]:
+        mask = ao.dense_mask(T, ins[b:b + 1], sid[b:b + 1], pre[b:b + 1], lens[b:b + 1])
+        sl = lambda x: x[b:b + 1, h:h + 1].detach().cpu()
+        q1, k1, v1, do1 = sl(q), sl(k), sl(v), sl(do)
+        s1 = signs[h:h + 1].cpu()
+        r1, r2, (qt, kt) = hadamard_oracles(q1, k1, v1, do1, mask, s1, dtype)
+        mine = tuple(sl(x) for x in got)
+        assert_lse_close(mine[1], r2[1])               # kernel error alone: 1e-3
+        assert_lse_close(mine[1], r1[1], tol=2e-3)     # plus the 16-bit storage of the transformed Q, K
+        _check_with_operand_bound("rounding-faithful oracle", mine, r2, ao.operand_rounding_bounds(qt, kt, v1, do1, mask, dtype), 1e-4)
+        _check_with_operand_bound("untransformed oracle", mine, r1, ao.operand_rounding_bounds(q1, k1, v1, do1, mask, dtype), 1e-4)
+
+
+def test_outlier_inputs_without_hadamard_config3_distribution():
+    """The same distribution without the transform (fp16, D=128, T=2048): what the operand-rounding term of the
+    check above is needed for is a property of 16-bit MMA operands, not of the Hadamard step."""
+    from kerneldev_b200 import synthetic
+    B, H, T, D, dtype = 2, 4, 2048, 128, torch.float16
+    ins, sid, pre, lens = synthetic.batch_metadata(4, B, T, **synthetic.CONFIG_RANGES[4])
+    q, k, v, do = _outlier_inputs(B, H, T, D, dtype, seed=5)
+    got = run_op(q, k, v, do, ins, sid, pre, lens)
+    mask = ao.dense_mask(T, ins, sid, pre, lens)
+    qc, kc, vc, doc = (x.cpu() for x in (q, k, v, do))
+    ref = ao.attention_fwd_bwd(qc, kc, vc, doc, mask)
+    assert_lse_close(got[1], ref[1])
+    _check_with_operand_bound("fp32 oracle", got, ref, ao.operand_rounding_bounds(qc, kc, vc, doc, mask, dtype), 1e-4)
+
+
+def test_repeat_runs_are_bit_identical_config2():
+    """BASELINE config 2 at full size, 12 forward + backward passes on the same inputs: O, LSE, dK, dV (and dQ
+    of the two-kernel backward) must be bit-identical every time. The kernels hand TMEM buffers between
+    MMA-issuing threads and rely on the tensor pipe executing in issue order; a race there would show up as
+    run-to-run differences long before it breaks a tolerance."""
+    from kerneldev_b200 import flash_attention, synthetic
+    B, H, T, D = 16, 16, 4096, 64
+    ins, sid, pre, lens = synthetic.batch_metadata(2, B, T, **synthetic.CONFIG_RANGES[2])
+    meta = dict(in_span=_t(ins, torch.bool), span_id=_t(sid, torch.int64), is_prefix=_t(pre, torch.bool), lens=_t(lens, torch.int32))
+    g = torch.Generator(device=DEV).manual_seed(2)
+    q, k, v, do = (torch.randn((B, H, T, D), generator=g, device=DEV, dtype=torch.bfloat16) for _ in range(4))
+    ref = None
+    for it in range(12):
+        qg, kg, vg = (x.clone().requires_grad_() for x in (q, k, v))
+        o, lse = flash_attention(qg, kg, vg, return_lse=True, deterministic=True, **meta)
+        o.backward(do)
+        cur = [o.detach(), lse, qg.grad, kg.grad, vg.grad]
+        if ref is None:
+            ref = [x.clone() for x in cur]
+        else:
+            for nm, a, b in zip(("O", "LSE", "dQ", "dK", "dV"), cur, ref):
+                assert torch.equal(a, b), f"{nm} differs in repeat {it}"
 
 
 def test_full_size_config2_sampled_heads():
@@ -304,8 +437,8 @@ def test_head_groups_per_cta(monkeypatch, D, dtype, G):
     """A CTA handles G heads one after the other (the work list is shared, the pipeline runs on across
     heads). Small problems get G = 1 by themselves, so the group size is forced here: H = 5 is not a
     multiple of 2 or 3, a sequence is empty and one ends inside a tile."""
-    monkeypatch.setenv("KD_HEADS_PER_CTA", str(G))
-    monkeypatch.setenv("KD_HEADS_PER_CTA_BWD", str(G))
+    from kerneldev_b200 import original_kernel
+    monkeypatch.setattr(original_kernel, "HEADS_PER_CTA", G)
     B, H, T = 3, 5, 520
     ins, sid, pre = random_meta(17 + G, B, T)
     lens = np.array([T, 0, T - 77], np.int32)

@@ -120,3 +120,49 @@ def test_pair_sharding_covers_every_pair_once_world2():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert cover == [1] * 30 and sum(counts) == 30 and max(counts) - min(counts) <= 1
+
+
+def test_status_word_reporting_and_clearing_on_the_host():
+    """Host half of the device status protocol: poll() reads the pinned mirror without touching the device
+    tensor's stream, raises the right exception for each status bit and clears both copies, so that one
+    event is reported once and a later launch on the same plan starts clean."""
+    from kerneldev_b200 import _capi
+    from kerneldev_b200.plan import AttentionPlan
+    plan = object.__new__(AttentionPlan)          # no device: CPU tensors stand in for the two copies
+    plan._status_dev = torch.zeros(1, dtype=torch.int32)
+    plan._status_host = torch.zeros(1, dtype=torch.int32)
+    plan.poll()                                    # clean: nothing happens
+    plan._status_dev[0] = _capi.KD_STATUS_TIMEOUT | 0x104
+    plan.poll()                                    # not mirrored yet: still silent
+    plan.mirror_status()
+    with pytest.raises(RuntimeError, match="wait site 0x104"):
+        plan.poll()
+    assert int(plan._status_dev[0]) == 0 and int(plan._status_host[0]) == 0
+    plan.poll()
+    plan._status_dev[0] = _capi.KD_STATUS_SPAN_RANGE
+    with pytest.raises(ValueError, match="24 signed bits"):
+        plan.check_status()
+    assert int(plan._status_dev[0]) == 0
+    plan._status_dev[0] = 5
+    with pytest.raises(RuntimeError, match="0x00000005"):
+        plan.check_status()
+
+
+@pytest.mark.skipif(not os.environ.get("REFERENCE_DIR"), reason="needs a checkout of the reference project (REFERENCE_DIR)")
+def test_reference_model_binds_the_dropin_operator():
+    """With kerneldev_b200/dropin ahead of the reference checkout on sys.path, the reference's own model.py
+    (`from original_kernel import flash_attention`, model.py:24) binds this package's operator."""
+    code = (
+        "import sys, functools\n"
+        f"sys.path.insert(0, {os.environ['REFERENCE_DIR']!r})\n"
+        f"sys.path.insert(0, {os.path.join(ROOT, 'kerneldev_b200', 'dropin')!r})\n"
+        f"sys.path.insert(0, {ROOT!r})\n"
+        "import model\n"
+        "from kerneldev_b200.original_kernel import flash_attention as ours\n"
+        "fa = model.flash_attention\n"
+        "assert isinstance(fa, functools.partial) and fa.func is ours and fa.keywords == {'out_layout': 'input'}, fa\n"
+        "import original_kernel\n"
+        "assert original_kernel.__file__.startswith(" + repr(os.path.join(ROOT, 'kerneldev_b200', 'dropin')) + ")\n"
+        "print('bound')\n")
+    r = subprocess.run([os.sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "bound" in r.stdout, r.stdout + r.stderr
