@@ -40,6 +40,10 @@ extern "C" {
 #define KD_TILE_FULL 1    /* every pair allowed: no per-element rule */
 #define KD_TILE_PARTIAL 2 /* mixed: 4-section rule evaluated per element */
 
+/* kd_attn_params.bwd_mode */
+#define KD_BWD_SPLIT 0
+#define KD_BWD_FUSED 1
+
 /* error codes (negative return values) */
 #define KD_ERR_ARG (-1)     /* bad shape / dtype / null pointer */
 #define KD_ERR_ALIGN (-2)   /* pointer or stride not 16-byte aligned */
@@ -106,6 +110,13 @@ typedef struct kd_attn_params {
   int32_t bwd_phases; /* kd_attn_bwd only. 0 or 3: all kernels; 1: the delta kernel and the dQ
                          kernel; 2: the dK/dV kernel alone (reads delta of an earlier pass 1).
                          Lets a caller time the two large kernels separately. */
+  int32_t bwd_mode;   /* kd_attn_bwd only. KD_BWD_SPLIT (0): a dQ kernel and a dK/dV kernel as in the reference
+                         (original_kernel.py:1173-1336, :1339-1525), results bit-reproducible. KD_BWD_FUSED (1),
+                         D = 64 only: one kernel forms S and dP once per tile and adds its dQ partials to dq_acc
+                         with fp32 atomics (dQ then differs in the last bits from run to run). With
+                         KD_BWD_FUSED, bwd_phases 1 runs the delta kernel alone and 2 the fused kernel. */
+  float* dq_acc;      /* KD_BWD_FUSED: (B,H,T,D) contiguous fp32 scratch (kd_workspace_bytes_fused gives its
+                         size); the library zeroes it itself. Ignored otherwise. */
   int32_t heads_per_cta; /* 0: chosen by the library from the grid size. n >= 1: every CTA handles n heads
                          one after the other (they share the plan's work list); a tuning and test knob. */
 } kd_attn_params;
@@ -152,6 +163,10 @@ int kd_attn_bwd_static(const kd_attn_params* p, void* stream);
 
 /* Bytes of the scratch buffer `delta` that kd_attn_bwd needs. */
 int kd_workspace_bytes(int32_t B, int32_t H, int32_t T, int32_t D, size_t* bytes);
+
+/* Bytes of the scratch buffer `dq_acc` that kd_attn_bwd needs with bwd_mode KD_BWD_FUSED (no counterpart in
+ * the reference, which accumulates dQ in registers of its query-tile-major worker). */
+int kd_workspace_bytes_fused(int32_t B, int32_t H, int32_t T, int32_t D, size_t* bytes);
 
 /* Incoherent-processing transform over the last dimension, the "hadamard_transform" /
  * "generate_hadamard_signs" utilities the reference names in README.md:68-77 without shipping

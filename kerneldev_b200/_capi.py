@@ -16,13 +16,14 @@ KD_TILE = 128
 KD_TILE_EMPTY, KD_TILE_FULL, KD_TILE_PARTIAL = 0, 1, 2
 KD_STATUS_TIMEOUT = 0x10000000
 KD_STATUS_SPAN_RANGE = 0x20000000
+KD_BWD_SPLIT, KD_BWD_FUSED = 0, 1
 
 # KD_LIB_PATH selects another build of the same library (the wait time-out test loads one built with a short wait limit)
 LIB_PATH = Path(os.environ.get("KD_LIB_PATH") or Path(__file__).resolve().parent / "_lib" / "libkd_attention.so")
 
 EXPORTS = (
     "kd_version", "kd_last_error", "kd_plan_layout_get", "kd_classify", "kd_mask_dense",
-    "kd_attn_fwd", "kd_attn_bwd", "kd_attn_bwd_static", "kd_workspace_bytes", "kd_hadamard",
+    "kd_attn_fwd", "kd_attn_bwd", "kd_attn_bwd_static", "kd_workspace_bytes", "kd_workspace_bytes_fused", "kd_hadamard",
     "kd_metadata_from_tokens", "kd_span_index", "kd_span_mean",
 )
 
@@ -56,7 +57,8 @@ class KdAttnParams(Structure):
         ("dtype", c_int32), ("sm_scale", c_float),
         ("q", KdTensor), ("k", KdTensor), ("v", KdTensor), ("o", KdTensor), ("d_o", KdTensor),
         ("dq", KdTensor), ("dk", KdTensor), ("dv", KdTensor),
-        ("lse", c_void_p), ("delta", c_void_p), ("plan", c_void_p), ("bwd_phases", c_int32), ("heads_per_cta", c_int32),
+        ("lse", c_void_p), ("delta", c_void_p), ("plan", c_void_p), ("bwd_phases", c_int32), ("bwd_mode", c_int32),
+        ("dq_acc", c_void_p), ("heads_per_cta", c_int32),
     ]
 
 
@@ -86,6 +88,7 @@ def load() -> ctypes.CDLL:
     lib.kd_attn_bwd.argtypes = [POINTER(KdAttnParams), c_void_p]
     lib.kd_attn_bwd_static.argtypes = [POINTER(KdAttnParams), c_void_p]
     lib.kd_workspace_bytes.argtypes = [c_int32, c_int32, c_int32, c_int32, POINTER(c_size_t)]
+    lib.kd_workspace_bytes_fused.argtypes = [c_int32, c_int32, c_int32, c_int32, POINTER(c_size_t)]
     lib.kd_hadamard.argtypes = [POINTER(KdTensor), POINTER(KdTensor), c_int32, c_int32, c_int32, c_int32,
                                 c_int32, c_void_p, c_int32, c_void_p]
     lib.kd_span_index.argtypes = [c_void_p, c_int64, c_int32, c_int32, c_int64, c_int64, c_int64, c_void_p, c_void_p,
@@ -95,7 +98,7 @@ def load() -> ctypes.CDLL:
     lib.kd_metadata_from_tokens.argtypes = [c_void_p, c_int64, c_int32, c_int32, c_int64, c_int64, c_int64, c_int64,
                                             c_void_p, c_void_p, c_void_p, c_void_p]
     for name in ("kd_plan_layout_get", "kd_classify", "kd_mask_dense", "kd_attn_fwd", "kd_attn_bwd", "kd_attn_bwd_static",
-                 "kd_workspace_bytes", "kd_hadamard", "kd_metadata_from_tokens", "kd_span_index", "kd_span_mean"):
+                 "kd_workspace_bytes", "kd_workspace_bytes_fused", "kd_hadamard", "kd_metadata_from_tokens", "kd_span_index", "kd_span_mean"):
         getattr(lib, name).restype = c_int32
     _lib = lib
     return lib

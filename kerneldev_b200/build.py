@@ -18,7 +18,7 @@ LIB_DIR = PKG_DIR / "_lib"
 LIB_PATH = LIB_DIR / "libkd_attention.so"
 INCLUDE_DIR = PKG_DIR.parent / "include"
 
-SOURCES = ["capi.cu", "plan.cu", "attn_fwd.cu", "attn_bwd.cu", "hadamard.cu", "metadata.cu", "cocktail.cu"]
+SOURCES = ["capi.cu", "plan.cu", "attn_fwd.cu", "attn_bwd.cu", "attn_bwd_fused.cu", "hadamard.cu", "metadata.cu", "cocktail.cu"]
 HEADERS = sorted(p.name for p in (Path(__file__).resolve().parent / "csrc").glob("*.cuh"))
 
 NVCC_FLAGS = [

@@ -24,36 +24,10 @@
 #include <algorithm>
 #include <mutex>
 
-#include "attn_common.cuh"
+#include "attn_bwd.cuh"
 
 namespace kd {
 
-struct BwdArgs {
-  int B, H, T, NT, NP, Tpad;
-  int G;             // heads per CTA
-  float scale_log2;  // sm_scale * log2(e)
-  float sm_scale;
-  const uint32_t* desc;
-  const uint32_t* tilebits;   // [B][NT][8][4] class masks of every 128-token tile
-  const int32_t* fwd_cnt;
-  const uint16_t* fwd_list;
-  const int32_t* bwd_cnt;
-  const uint16_t* bwd_list;
-  const uint8_t* order;   // [B][3][NT]; row 1 = q tiles, row 2 = k tiles, by decreasing list length
-  uint32_t* status;
-  const void* o;
-  int64_t o_sb, o_sh, o_st;
-  const void* d_o;
-  int64_t do_sb, do_sh, do_st;
-  const float* lse;
-  float* delta;
-  void* dq;
-  int64_t dq_sb, dq_sh, dq_st;
-  void* dk;
-  int64_t dk_sb, dk_sh, dk_st;
-  void* dv;
-  int64_t dv_sb, dv_sh, dv_st;
-};
 
 template <int HD>
 struct BwdCfg {
@@ -91,7 +65,8 @@ enum : uint32_t {
 // =========================================================================================
 // delta kernel: delta[b, h, t] = sum_d O[b, h, t, d] * dO[b, h, t, d] in fp32 (the reference's
 // _flash_attn_bwd_precompute, original_kernel.py:629-710). HD/8 threads share a row, 16 bytes of
-// each tensor per thread, so a warp reads whole 128-byte lines; bound by HBM bandwidth.
+// each tensor per thread, so a warp reads whole 128-byte lines; bound by HBM bandwidth. For the fused
+// backward it also zeroes the row of the fp32 dQ accumulation scratch (8 floats per thread).
 // =========================================================================================
 template <int HD, bool kBf16>
 __global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const BwdArgs a) {
@@ -121,6 +96,11 @@ __global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const BwdArgs a) {
 #pragma unroll
     for (int d = TPR / 2; d >= 1; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
     if (live && sub == 0) a.delta[r] = acc;
+    if (live && a.dq_acc != nullptr) {
+      float4* z = reinterpret_cast<float4*>(a.dq_acc + r * HD + sub * 8);
+      z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+      z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
   }
 }
 
@@ -927,6 +907,8 @@ static int launch_bwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
   a.o = p.o.ptr; a.o_sb = p.o.stride_b; a.o_sh = p.o.stride_h; a.o_st = p.o.stride_t;
   a.d_o = p.d_o.ptr; a.do_sb = p.d_o.stride_b; a.do_sh = p.d_o.stride_h; a.do_st = p.d_o.stride_t;
   a.lse = p.lse; a.delta = p.delta;
+  const bool fused = (p.bwd_mode == KD_BWD_FUSED);
+  a.dq_acc = fused ? p.dq_acc : nullptr;
   a.dq = p.dq.ptr; a.dq_sb = p.dq.stride_b; a.dq_sh = p.dq.stride_h; a.dq_st = p.dq.stride_t;
   a.dk = p.dk.ptr; a.dk_sb = p.dk.stride_b; a.dk_sh = p.dk.stride_h; a.dk_st = p.dk.stride_t;
   a.dv = p.dv.ptr; a.dv_sb = p.dv.stride_b; a.dv_sh = p.dv.stride_h; a.dv_st = p.dv.stride_t;
@@ -943,9 +925,16 @@ static int launch_bwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
     const int rows_per_block = 256 / (HD / 8);
     const int blocks = static_cast<int>(std::min<size_t>((rows + rows_per_block - 1) / rows_per_block, size_t(148) * 32));
     attn_bwd_delta_kernel<HD, kBf16><<<blocks, 256, 0, stream>>>(a);
-    kq<<<grid, C::THREADS, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
+    if (!fused) kq<<<grid, C::THREADS, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
   }
-  if (phases & 2) kk<<<grid, C::THREADS, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
+  if (fused) {
+    // bwd_phases 1: the delta kernel alone (it also zeroes dq_acc); 2: the fused kernel and the conversion
+    if constexpr (HD == 64) {
+      if (phases & 2) return launch_bwd_fused(tmQ, tmK, tmV, tmDO, a, p.dtype, grid, stream);
+    }
+  } else if (phases & 2) {
+    kk<<<grid, C::THREADS, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
+  }
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "attn_bwd kernels launch: %s", cudaGetErrorString(e));
   return 0;

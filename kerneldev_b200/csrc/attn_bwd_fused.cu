@@ -1,0 +1,539 @@
+// Fused backward for head dim 64 on sm_100a: dK, dV and dQ from ONE pass over the non-empty tiles.
+//
+// The two-kernel backward (attn_bwd.cu) follows the reference's split into a dQ worker and a dK/dV
+// worker (original_kernel.py:1173-1336, :1339-1525) and so forms S = Q K^T, dP = dO V^T and the
+// exponentials twice per tile: 7 matrix products and two exponential passes. This kernel is key-tile
+// major like the dK/dV worker and forms them once: per (query tile, key tile)
+//     S^T = K Q^T, dP^T = V dO^T                      (smem x smem -> TMEM)
+//     P^T = exp2(S^T c - LSE), dS^T = P^T (dP^T - delta)   (compute warps; 16-bit results)
+//     dV += P^T dO, dK += dS^T Q                      (P^T, dS^T read from TMEM as the A operand)
+//     dQ_tile = dS K                                  (dS^T is also written to shared memory, which the
+//                                                      tensor core reads as an MN-major A operand)
+// 5 products and one exponential pass. dK and dV stay in TMEM for the whole key tile; the dQ partial of
+// every tile is added to an fp32 scratch (B,H,T,64) with red.global.add.v4.f32 (the additions of
+// different key tiles arrive in no fixed order, so dQ is not bit-reproducible from run to run) and a
+// bandwidth-bound kernel converts the scratch to the output dtype afterwards. The delta kernel, which
+// runs first anyway, zeroes the scratch.
+//
+// 768 threads: warp 0 TMA producer; warp 3 / warp 2 issue S^T / dP^T per 64-query unit (N = 64);
+// warp 1 issues the accumulating products and dQ; warps 4-19 are four compute warpgroups (two per unit,
+// 32 query columns each, as in the two-kernel backward); warps 20-23 move finished dQ tiles from TMEM to
+// global memory. TMEM: two unit buffers (64 columns S^T + 64 columns dP^T each), dK, dV, two dQ buffers.
+// A unit's products keep the tensor pipe busy for about as long as its arithmetic keeps the compute
+// warps, so two unit buffers are enough to overlap them.
+#include <algorithm>
+
+#include "attn_bwd.cuh"
+
+namespace kd {
+
+struct FusedCfg {
+  static constexpr int HD = 64;
+  static constexpr int TILE_BYTES = KD_TILE * HD * 2;
+  static constexpr int NBUF = 2;                     // unit buffers in TMEM
+  static constexpr int STAGES = 2;                   // ring of streamed (Q, dO) tile pairs
+  static constexpr int NFIX = 2;                     // resident (K, V) pairs: the next head's load while this head runs
+  static constexpr int SMEM_FIX = 0;
+  static constexpr int SMEM_RING = SMEM_FIX + NFIX * 2 * TILE_BYTES;
+  static constexpr int SMEM_DS = SMEM_RING + STAGES * 2 * TILE_BYTES;   // 2 x dS^T of a query tile: two [128 keys][64 queries] blocks
+  static constexpr int SMEM_STAGE = SMEM_DS + 2 * 2 * TILE_BYTES;      // per compute warp: 32 x {lse, delta, descriptor}
+  static constexpr int STAGE_WORDS = 3 * 32;
+  static constexpr int SMEM_LIST = SMEM_STAGE + 16 * STAGE_WORDS * 4;
+  static constexpr int SMEM_TOTAL = SMEM_LIST + 128 * 2;
+  static constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;
+  static constexpr int THREADS = 768;
+  static constexpr uint32_t TM_DK = NBUF * 128, TM_DV = TM_DK + HD, TM_DQ = TM_DV + HD;   // dQ buffer t at TM_DQ + 64 t
+  static_assert(TM_DQ + 2 * HD <= 512, "TMEM budget");
+  static_assert(SMEM_ALLOC <= 232448, "shared memory budget");
+  // registers: 80 per thread at launch; light warps release down to 56, the dQ warps to 64, compute warps take 88
+  static constexpr int REGS_LIGHT = 56, REGS_DQ = 64, REGS_COMPUTE = 88;
+  static_assert(4 * 32 * REGS_LIGHT + 4 * 32 * REGS_DQ + 16 * 32 * REGS_COMPUTE <= 768 * 80, "register pool");
+};
+
+enum : uint32_t {
+  W_U_FIXFULL = 0x401, W_U_RINGEMPTY = 0x402, W_U_RINGFULL = 0x403, W_U_PFULL = 0x404, W_U_SFULL = 0x405,
+  W_U_ACCFULL = 0x406, W_U_M2ISSUED = 0x407, W_U_FIXEMPTY = 0x408, W_U_ACCFREE = 0x409, W_U_DQFULL = 0x40A,
+  W_U_DQEMPTY = 0x40B, W_U_DSEMPTY = 0x40C,
+};
+
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t saddr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+__device__ __forceinline__ void red_add_v4(float* gptr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"l"(gptr), "f"(__uint_as_float(x)), "f"(__uint_as_float(y)), "f"(__uint_as_float(z)), "f"(__uint_as_float(w))
+               : "memory");
+}
+
+template <bool kBf16>
+__global__ void __launch_bounds__(FusedCfg::THREADS, 1)
+attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                      const BwdArgs a) {
+  using C = FusedCfg;
+  constexpr int HD = C::HD;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sFix = smem_u32(smem + C::SMEM_FIX);    // buffer f: K at +0, V at +TILE_BYTES
+  const uint32_t sRing = smem_u32(smem + C::SMEM_RING);  // stage s: Q at +0, dO at +TILE_BYTES
+  const uint32_t sDS = smem_u32(smem + C::SMEM_DS);      // buffer t: block 0 (queries 0-63) at +0, block 1 at +TILE_BYTES
+  uint32_t* sStage = reinterpret_cast<uint32_t*>(smem + C::SMEM_STAGE);
+  uint16_t* sList = reinterpret_cast<uint16_t*>(smem + C::SMEM_LIST);
+
+  __shared__ __align__(8) uint64_t bar_fix_full[C::NFIX], bar_fix_empty[C::NFIX], bar_ring_full[C::STAGES],
+      bar_ring_empty[C::STAGES], bar_s_full[C::NBUF], bar_p_full[C::NBUF], bar_m2_issued[C::NBUF], bar_acc_full, bar_acc_free,
+      bar_dq_full[2], bar_dq_empty[2], bar_ds_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ AbortFlag abortf;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int h0 = blockIdx.x * a.G, b = blockIdx.y;
+  const int nh = min(a.G, a.H - h0);   // this CTA handles heads h0 .. h0 + nh - 1
+  const int kt = a.order[((size_t)b * 3 + 2) * a.NT + blockIdx.z];   // longest lists first
+  const int n = a.bwd_cnt[b * a.NT + kt];
+
+  if (tid == 0) {
+    abortf.v = 0;
+    for (int f = 0; f < C::NFIX; ++f) {
+      mbar_init(smem_u32(&bar_fix_full[f]), 1);
+      mbar_init(smem_u32(&bar_fix_empty[f]), 3);  // all three issuers are done with the head's K and V
+    }
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(smem_u32(&bar_ring_full[s]), 1);
+      mbar_init(smem_u32(&bar_ring_empty[s]), 1);
+    }
+    for (int i = 0; i < C::NBUF; ++i) {
+      mbar_init(smem_u32(&bar_s_full[i]), 2);     // one commit from each of the two M1 issuers
+      mbar_init(smem_u32(&bar_p_full[i]), 256);   // the two warpgroups that share the unit
+      mbar_init(smem_u32(&bar_m2_issued[i]), 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(smem_u32(&bar_dq_full[t]), 1);
+      mbar_init(smem_u32(&bar_dq_empty[t]), 128);  // the dQ warpgroup has read the buffer
+      mbar_init(smem_u32(&bar_ds_empty[t]), 1);    // the dQ product has read the dS^T buffer
+    }
+    mbar_init(smem_u32(&bar_acc_full), 1);
+    mbar_init(smem_u32(&bar_acc_free), 512);       // every compute thread has read its part of dK and dV
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_s), 512);
+    tmem_relinquish();
+  }
+  if (warp == 2) {
+    const uint16_t* glist = a.bwd_list + ((size_t)b * a.NT + kt) * a.NT;
+    for (int e = lane; e < n; e += 32) sList[e] = glist[e];
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = tmem_base_s;
+  const uint16_t* list = sList;
+
+  if (warp < 4) {
+    reg_dealloc<C::REGS_LIGHT>();
+    if (warp == 0 && lane == 0 && n > 0) {
+      // ------------------------------ TMA producer ------------------------------
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      tma_prefetch_desc(&tmDO);
+      int issued = 0, fix_issued = 0;   // ring entries / resident pairs requested so far, over all heads
+      bool ok = true;
+      for (int hh = 0; hh < nh && ok; ++hh) {
+        const int h = h0 + hh, fb = hh % C::NFIX;
+        if (hh >= C::NFIX) {
+          ok = mbar_wait(smem_u32(&bar_fix_empty[fb]), (hh / C::NFIX - 1) & 1, &abortf, a.status, W_U_FIXEMPTY);
+          if (!ok) break;
+        }
+        mbar_arrive_expect_tx(smem_u32(&bar_fix_full[fb]), 2 * C::TILE_BYTES);
+        tma_load_4d(sFix + fb * 2 * C::TILE_BYTES, &tmK, smem_u32(&bar_fix_full[fb]), 0, kt * KD_TILE, h, b);
+        tma_load_4d(sFix + fb * 2 * C::TILE_BYTES + C::TILE_BYTES, &tmV, smem_u32(&bar_fix_full[fb]), 0, kt * KD_TILE, h, b);
+        fix_issued = hh + 1;
+        for (int e = 0; e < n; ++e) {
+          const int s = issued % C::STAGES;
+          const uint32_t ph = (issued / C::STAGES) & 1;
+          const int qt = list[e] & 0xFF;
+          ok = mbar_wait(smem_u32(&bar_ring_empty[s]), ph ^ 1, &abortf, a.status, W_U_RINGEMPTY);
+          if (!ok) break;
+          mbar_arrive_expect_tx(smem_u32(&bar_ring_full[s]), 2 * C::TILE_BYTES);
+          const uint32_t dst = sRing + s * 2 * C::TILE_BYTES;
+          tma_load_4d(dst, &tmQ, smem_u32(&bar_ring_full[s]), 0, qt * KD_TILE, h, b);
+          tma_load_4d(dst + C::TILE_BYTES, &tmDO, smem_u32(&bar_ring_full[s]), 0, qt * KD_TILE, h, b);
+          ++issued;
+        }
+      }
+      if (abortf.v != 0) {   // let the copies in flight land before the CTA exits
+        for (int e = max(0, issued - C::STAGES); e < issued; ++e) drain_wait(smem_u32(&bar_ring_full[e % C::STAGES]), (e / C::STAGES) & 1);
+        for (int f = max(0, fix_issued - C::NFIX); f < fix_issued; ++f) drain_wait(smem_u32(&bar_fix_full[f % C::NFIX]), (f / C::NFIX) & 1);
+      }
+    } else if ((warp == 3 || warp == 2) && lane == 0 && n > 0) {
+      // ---------------- M1 issuers: warp 3: S^T_u = K Q_u^T; warp 2: dP^T_u = V dO_u^T (N = 64 queries) ----------------
+      const bool dp_part = (warp == 2);
+      const uint32_t idesc_m1 = make_idesc_f16(kBf16, 0, 0, KD_TILE, 64);
+      const uint32_t hi = desc_hi_sw128();
+      const uint32_t loRingK = desc_lo_kmajor(sRing);
+      const int U = 2 * n;
+      bool ok = true;
+      int buf = 0, round = 0, stage = 0;   // run on across the heads
+      uint32_t ring_parity = 0;
+      for (int hh = 0; hh < nh && ok; ++hh) {
+        const int fb = hh % C::NFIX;
+        ok = mbar_wait(smem_u32(&bar_fix_full[fb]), (hh / C::NFIX) & 1, &abortf, a.status, W_U_FIXFULL);
+        if (!ok) break;
+        const uint32_t loA = desc_lo_kmajor(sFix + fb * 2 * C::TILE_BYTES + (dp_part ? C::TILE_BYTES : 0));   // V or K
+        uint64_t adesc[HD / 16];
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) adesc[kk] = desc64(loA + koff_kmajor(kk), hi);
+        for (int u = 0; u < U && ok; ++u) {
+          const int i = u & 1;
+          // query rows 64i.. of Q (scores) or dO (dP)
+          const uint32_t blo = loRingK + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4) + (dp_part ? (C::TILE_BYTES >> 4) : 0);
+          uint64_t bdesc[HD / 16];
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk) bdesc[kk] = desc64(blo + koff_kmajor(kk), hi);
+          const uint32_t dst = tbase + buf * 128 + (dp_part ? 64 : 0);
+          if (round > 0) {   // buffer free once the products that read its previous unit have been issued
+            ok = mbar_wait(smem_u32(&bar_m2_issued[buf]), (round - 1) & 1, &abortf, a.status, W_U_M2ISSUED);
+            if (!ok) break;
+          }
+          if (i == 0) {      // first unit of a new entry: its Q and dO tiles must have landed
+            ok = mbar_wait(smem_u32(&bar_ring_full[stage]), ring_parity, &abortf, a.status, W_U_RINGFULL);
+            if (!ok) break;
+          }
+          tc_fence_after_sync();
+          mma_ss64<false>(dst, adesc[0], bdesc[0], idesc_m1);
+#pragma unroll
+          for (int kk = 1; kk < HD / 16; ++kk) mma_ss64<true>(dst, adesc[kk], bdesc[kk], idesc_m1);
+          mma_commit(smem_u32(&bar_s_full[buf]));
+          if (++buf == C::NBUF) { buf = 0; ++round; }
+          if (i == 1 && ++stage == C::STAGES) { stage = 0; ring_parity ^= 1; }
+        }
+        if (ok) mma_commit(smem_u32(&bar_fix_empty[fb]));   // this issuer's products of the head no longer read K / V
+      }
+    } else if (warp == 1 && lane == 0 && n > 0) {
+      // ------- M2 issuer: dV += P^T_u dO_u, dK += dS^T_u Q_u per unit; after a tile's second unit dQ_tile = dS K -------
+      const uint32_t idesc_m2 = make_idesc_f16(kBf16, 0, 1, KD_TILE, HD);   // A from TMEM, B = dO / Q rows, MN-major
+      const uint32_t idesc_m3 = make_idesc_f16(kBf16, 1, 1, KD_TILE, HD);   // A = dS^T in smem read MN-major, B = K rows, MN-major
+      const uint32_t tDK = tbase + C::TM_DK, tDV = tbase + C::TM_DV;
+      const uint32_t hi = desc_hi_sw128();
+      const uint32_t loRingMN = desc_lo_mnmajor(sRing);
+      const uint32_t loDS = desc_lo_mnmajor(sDS);
+      const int U = 2 * n;
+      bool ok = true;
+      int buf = 0, stage = 0;
+      uint32_t round_parity = 0;
+      int tcount = 0;   // query tiles finished so far, over all heads
+      for (int hh = 0; hh < nh && ok; ++hh) {
+        const int fb = hh % C::NFIX;
+        const uint32_t loK = desc_lo_mnmajor(sFix + fb * 2 * C::TILE_BYTES);
+        if (hh > 0) {   // the previous head's dK and dV must have been read out of the accumulators
+          ok = mbar_wait(smem_u32(&bar_acc_free), (hh - 1) & 1, &abortf, a.status, W_U_ACCFREE);
+          if (!ok) break;
+        }
+        for (int u = 0; u < U && ok; ++u) {
+          const int i = u & 1;
+          const uint32_t qb = loRingMN + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
+          const uint32_t dob = qb + (C::TILE_BYTES >> 4);
+          const uint32_t aS = tbase + buf * 128;
+          // 16-bit operands: queries 0-31 of the unit at columns [0,16) of their buffer half, queries 32-63 at [32,48)
+          uint64_t bq[4], bdo[4];
+          uint32_t aop[4];
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            bq[kk] = desc64(qb + koff_mnmajor(kk), hi);
+            bdo[kk] = desc64(dob + koff_mnmajor(kk), hi);
+            aop[kk] = aS + (kk >> 1) * 32 + (kk & 1) * 8;
+          }
+          ok = mbar_wait(smem_u32(&bar_p_full[buf]), round_parity, &abortf, a.status, W_U_PFULL);
+          if (!ok) break;
+          tc_fence_after_sync();
+          mma_ts64_p(tDV, aop[0], bdo[0], idesc_m2, u > 0 ? 1u : 0u);
+#pragma unroll
+          for (int kk = 1; kk < 4; ++kk) mma_ts64<true>(tDV, aop[kk], bdo[kk], idesc_m2);
+          mma_ts64_p(tDK, aop[0] + 64, bq[0], idesc_m2, u > 0 ? 1u : 0u);
+#pragma unroll
+          for (int kk = 1; kk < 4; ++kk) mma_ts64<true>(tDK, aop[kk] + 64, bq[kk], idesc_m2);
+          if (i == 1) mma_commit(smem_u32(&bar_ring_empty[stage]));
+          tc_fence_before_sync();
+          mbar_arrive(smem_u32(&bar_m2_issued[buf]));
+          if (i == 1) {
+            // both units of the tile have arrived on their P-ready barriers, so dS^T of the whole tile is in shared memory
+            const int tb = tcount & 1;
+            if (tcount >= 2) {   // the dQ warpgroup must have read the buffer's previous tile
+              ok = mbar_wait(smem_u32(&bar_dq_empty[tb]), ((tcount >> 1) - 1) & 1, &abortf, a.status, W_U_DQEMPTY);
+              if (!ok) break;
+              tc_fence_after_sync();
+            }
+            const uint32_t tDQ = tbase + C::TM_DQ + tb * HD;
+            const uint32_t alo = loDS + tb * (2 * C::TILE_BYTES >> 4);
+            mma_ss_split(tDQ, alo, loK, hi, idesc_m3, 0u);
+#pragma unroll
+            for (int kk = 1; kk < KD_TILE / 16; ++kk) mma_ss_split(tDQ, alo + koff_mnmajor(kk), loK + koff_mnmajor(kk), hi, idesc_m3, 1u);
+            mma_commit(smem_u32(&bar_dq_full[tb]));
+            mma_commit(smem_u32(&bar_ds_empty[tb]));
+            ++tcount;
+          }
+          if (++buf == C::NBUF) { buf = 0; round_parity ^= 1; }
+          if (i == 1 && ++stage == C::STAGES) stage = 0;
+        }
+        if (ok) {
+          mma_commit(smem_u32(&bar_acc_full));
+          mma_commit(smem_u32(&bar_fix_empty[fb]));   // the dQ products of the head no longer read K
+        }
+      }
+    }
+  } else if (warp < 20) {
+    reg_alloc<C::REGS_COMPUTE>();
+    // ------------------------------ compute warpgroups ------------------------------
+    const int g = (warp - 4) >> 2;   // warpgroup
+    const int i = g >> 1;            // stream: query half (64 queries) of each query tile
+    const int c0 = g & 1;            // which 32 queries of that half
+    const int wq = warp & 3;
+    const int row = wq * 32 + lane;
+    const int kj = kt * KD_TILE + row;   // this thread's key
+    const bool k_valid = kj < a.T;
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    uint32_t* st_buf = sStage + (size_t)(warp - 4) * C::STAGE_WORDS;  // [32 lse][32 delta][32 desc]
+    const float c = a.scale_log2;
+    const uint32_t kdesc = a.desc[(size_t)b * a.Tpad + kj];
+    const int tbw = 2 * i + c0;      // this thread's word of the 128-bit class masks of a query tile
+    // this thread's 64 bytes of a dS^T block row: 16-byte chunks 4 c0 .. 4 c0 + 3, swizzled with the row
+    const uint32_t ds_row = static_cast<uint32_t>(i) * C::TILE_BYTES + static_cast<uint32_t>(row) * 128u;
+    const uint32_t ds_sw = static_cast<uint32_t>(row & 7);
+    bool ok = true;
+
+    // LSE, delta and the descriptor of the next unit's queries are fetched one unit ahead into registers
+    // and handed to the warp through its shared-memory staging buffer
+    float pre_lse = 0.f, pre_delta = 0.f;
+    uint32_t pre_desc = 0u;
+    uint32_t tb_pre[5] = {0u, 0u, 0u, 0u, 0u};   // query-side class masks: sees-prefix, sees-context, sees-in_span, context, same-span armed
+    auto prefetch = [&](uint32_t entry, int h) {
+      if ((entry >> 8) == KD_TILE_PARTIAL) {
+        const uint32_t* tbp = a.tilebits + ((size_t)b * a.NT + (entry & 0xFFu)) * 32;
+        tb_pre[0] = tbp[4 * TB_SEES_PRE + tbw];
+        tb_pre[1] = tbp[4 * TB_SEES_CTX + tbw];
+        tb_pre[2] = tbp[4 * TB_SEES_INS + tbw];
+        tb_pre[3] = tbp[4 * TB_CTX + tbw];
+        tb_pre[4] = tbp[4 * TB_SIDPOS + tbw];
+      }
+      // a query at or beyond the sequence length reads the last row's scalars: its descriptor is 0,
+      // so the tile is PARTIAL and the mask removes it
+      const int q = (entry & 0xFF) * KD_TILE + i * 64 + c0 * 32 + lane;
+      const size_t r = ((size_t)b * a.H + h) * a.T + min(q, a.T - 1);
+      pre_lse = a.lse[r];   // negated where it is used: a negation here would wait for the load
+      pre_delta = a.delta[r];
+      pre_desc = a.desc[(size_t)b * a.Tpad + q];
+    };
+    uint32_t ent_next = n > 0 ? list[0] : 0u;
+    if (n > 0) prefetch(ent_next, h0);
+    int buf = i % C::NBUF;   // this stream's unit u = 2 e + i uses buffer u % NBUF = i, in round e (NBUF = 2)
+    uint32_t rnd = 0;
+    int tcount = 0;
+    const uint32_t sfull0 = smem_u32(&bar_s_full[0]), pfull0 = smem_u32(&bar_p_full[0]);
+    const uint32_t tcol = tbase + lane_base + c0 * 32;   // this thread's 32 columns inside a unit buffer half
+
+    for (int hh = 0; hh < nh && ok; ++hh) {
+      const int h = h0 + hh;
+      for (int e = 0; e < n; ++e) {
+        const uint32_t ent = ent_next;
+        const uint32_t cls = ent >> 8;
+        __syncwarp();
+        st_buf[lane] = __float_as_uint(pre_lse);
+        st_buf[32 + lane] = __float_as_uint(pre_delta);
+        st_buf[64 + lane] = pre_desc;
+        __syncwarp();
+        uint32_t mk = 0xFFFFFFFFu;   // visibility of this key for the 32 queries
+        if (cls == KD_TILE_PARTIAL) {
+          const int i0 = (ent & 0xFF) * KD_TILE + i * 64 + c0 * 32;  // first query handled here
+          key_row_mask<1>(kdesc, kj, i0, &tb_pre[0], &tb_pre[1], &tb_pre[2], &tb_pre[3], &mk);
+          if (tb_pre[4] != 0u && __any_sync(0xffffffffu, (kdesc & TD_INS) != 0u)) {
+            const uint32_t key = span_key_of_key(kdesc);
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const uint4 q4 = *reinterpret_cast<const uint4*>(st_buf + 64 + j);
+              mk |= (span_match_query(key, q4.x) << (j + 0)) | (span_match_query(key, q4.y) << (j + 1)) |
+                    (span_match_query(key, q4.z) << (j + 2)) | (span_match_query(key, q4.w) << (j + 3));
+            }
+          }
+        }
+        // the next entry: of this head or, at the end of the list, the first one again for the next head
+        if (e + 1 < n) {
+          ent_next = list[e + 1];
+          prefetch(ent_next, h);
+        } else if (hh + 1 < nh) {
+          ent_next = list[0];
+          prefetch(ent_next, h + 1);
+        }
+        const uint32_t tS = tcol + buf * 128, tP = tS + 64;
+        const int tb = tcount & 1;
+        const uint32_t ds_base = sDS + tb * (2 * C::TILE_BYTES) + ds_row;
+        ok = mbar_wait(sfull0 + buf * 8, rnd & 1u, &abortf, a.status, W_U_SFULL);
+        if (ok && tcount >= 2)   // the dQ product of the tile that used this dS^T buffer before must have completed
+          ok = mbar_wait(smem_u32(&bar_ds_empty[tb]), ((tcount >> 1) - 1) & 1, &abortf, a.status, W_U_DSEMPTY);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {   // 16 queries at a time
+          uint32_t pk_p[8], pk_ds[8];
+          uint32_t rs[16], rp[16];
+          tmem_ld16(tS + hf * 16, rs);
+          tmem_ld16(tP + hf * 16, rp);
+          tmem_wait_ld();
+          const uint32_t mh = mk >> (hf * 16);
+#pragma unroll
+          for (int j = 0; j < 16; j += 4) {
+            const float4 l4 = *reinterpret_cast<const float4*>(st_buf + hf * 16 + j);        // LSE of 4 queries
+            const float4 d4 = *reinterpret_cast<const float4*>(st_buf + 32 + hf * 16 + j);   // delta of 4 queries
+            const float lw[4] = {l4.x, l4.y, l4.z, l4.w}, dw[4] = {d4.x, d4.y, d4.z, d4.w};
+            float pv[4], ds[4];
+#pragma unroll
+            for (int u2 = 0; u2 < 4; ++u2) pv[u2] = fast_exp2(fmaf(__uint_as_float(rs[j + u2]), c, -lw[u2]));
+            if (cls == KD_TILE_PARTIAL) {   // warp-uniform
+#pragma unroll
+              for (int u2 = 0; u2 < 4; ++u2)
+                if ((mh & (1u << (j + u2))) == 0u) pv[u2] = 0.f;
+            }
+#pragma unroll
+            for (int u2 = 0; u2 < 4; ++u2) ds[u2] = pv[u2] * (__uint_as_float(rp[j + u2]) - dw[u2]);
+            pk_p[j / 2] = pack2<kBf16>(pv[0], pv[1]);
+            pk_p[j / 2 + 1] = pack2<kBf16>(pv[2], pv[3]);
+            pk_ds[j / 2] = pack2<kBf16>(ds[0], ds[1]);
+            pk_ds[j / 2 + 1] = pack2<kBf16>(ds[2], ds[3]);
+          }
+          tmem_st8(tS + hf * 8, pk_p);    // P^T over the start of the scores it was made from
+          tmem_st8(tP + hf * 8, pk_ds);   // dS^T over the start of its dP^T
+          // the same dS^T values as two 16-byte chunks of this key's row of the tile's dS^T block
+          const uint32_t ch = static_cast<uint32_t>(4 * c0 + 2 * hf);
+          st_shared_v4(ds_base + (((ch + 0u) ^ ds_sw) << 4), pk_ds[0], pk_ds[1], pk_ds[2], pk_ds[3]);
+          st_shared_v4(ds_base + (((ch + 1u) ^ ds_sw) << 4), pk_ds[4], pk_ds[5], pk_ds[6], pk_ds[7]);
+        }
+        fence_proxy_async_smem();   // the dQ product reads these shared-memory writes through the async proxy
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(pfull0 + buf * 8);
+        ++rnd;
+        ++tcount;
+      }
+      if (!ok) break;
+
+      // epilogue of this head: warpgroup g stores 16 columns of dK and dV from column 16 g
+      if (n > 0) {
+        ok = mbar_wait(smem_u32(&bar_acc_full), hh & 1, &abortf, a.status, W_U_ACCFULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+      tc_fence_after_sync();
+      uint16_t* krow = reinterpret_cast<uint16_t*>(a.dk) + (size_t)b * a.dk_sb + (size_t)h * a.dk_sh + (size_t)kj * a.dk_st + g * 16;
+      uint16_t* vrow = reinterpret_cast<uint16_t*>(a.dv) + (size_t)b * a.dv_sb + (size_t)h * a.dv_sh + (size_t)kj * a.dv_st + g * 16;
+      uint32_t rk[16], rv[16];
+      if (n > 0) {
+        tmem_ld16(tbase + lane_base + C::TM_DK + g * 16, rk);
+        tmem_ld16(tbase + lane_base + C::TM_DV + g * 16, rv);
+        tmem_wait_ld();
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(&bar_acc_free));   // the next head's first products may overwrite the accumulators
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { rk[j] = 0u; rv[j] = 0u; }
+      }
+      if (k_valid) {
+        store_row16<kBf16>(krow, rk, a.sm_scale);
+        store_row16<kBf16>(vrow, rv, 1.0f);
+      }
+    }
+  } else {
+    reg_dealloc<C::REGS_DQ>();
+    // ------------------------------ dQ warpgroup: TMEM -> fp32 additions in global memory ------------------------------
+    const int wq = warp & 3;
+    const int row = wq * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    bool ok = true;
+    int tcount = 0;
+    for (int hh = 0; hh < nh && ok; ++hh) {
+      const int h = h0 + hh;
+      float* acc_h = a.dq_acc + ((size_t)b * a.H + h) * a.T * HD;
+      for (int e = 0; e < n; ++e) {
+        const int tb = tcount & 1;
+        const int qi = (list[e] & 0xFF) * KD_TILE + row;
+        ok = mbar_wait(smem_u32(&bar_dq_full[tb]), (tcount >> 1) & 1, &abortf, a.status, W_U_DQFULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t tDQ = tbase + lane_base + C::TM_DQ + tb * HD;
+        float* dst = acc_h + (size_t)qi * HD;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          uint32_t r[32];
+          tmem_ld32(tDQ + hf * 32, r);
+          tmem_wait_ld();
+          if (hf == 1) {
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&bar_dq_empty[tb]));   // the product of the tile after next may overwrite the buffer
+          }
+          if (qi < a.T) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) red_add_v4(dst + hf * 32 + j, r[j], r[j + 1], r[j + 2], r[j + 3]);
+          }
+        }
+        ++tcount;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tbase, 512);
+}
+
+// dq[b, h, t, :] = dq_acc[b, h, t, :] * sm_scale in the output dtype; 8 threads per row, 32 bytes in and 16 out each
+template <bool kBf16>
+__global__ void __launch_bounds__(256) attn_bwd_dq_convert_kernel(const BwdArgs a) {
+  constexpr int HD = FusedCfg::HD, TPR = HD / 8;
+  const size_t rows = (size_t)a.B * a.H * a.T;
+  const int sub = threadIdx.x % TPR;
+  for (size_t r = (size_t)blockIdx.x * (256 / TPR) + threadIdx.x / TPR; r < rows; r += (size_t)gridDim.x * (256 / TPR)) {
+    const int t = static_cast<int>(r % a.T);
+    const int h = static_cast<int>((r / a.T) % a.H);
+    const int b = static_cast<int>(r / ((size_t)a.T * a.H));
+    const float4* src = reinterpret_cast<const float4*>(a.dq_acc + r * HD + sub * 8);
+    const float4 x = src[0], y = src[1];
+    uint4 v;
+    v.x = pack2<kBf16>(x.x * a.sm_scale, x.y * a.sm_scale);
+    v.y = pack2<kBf16>(x.z * a.sm_scale, x.w * a.sm_scale);
+    v.z = pack2<kBf16>(y.x * a.sm_scale, y.y * a.sm_scale);
+    v.w = pack2<kBf16>(y.z * a.sm_scale, y.w * a.sm_scale);
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.dq) + (size_t)b * a.dq_sb + (size_t)h * a.dq_sh + (size_t)t * a.dq_st + sub * 8) = v;
+  }
+}
+
+template <bool kBf16>
+static int launch_fused_t(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const CUtensorMap& tmDO,
+                          const BwdArgs& a, dim3 grid, cudaStream_t stream) {
+  using C = FusedCfg;
+  auto kern = attn_bwd_fused_kernel<kBf16>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_ALLOC);
+  if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "fused bwd smem attribute: %s", cudaGetErrorString(e));
+  kern<<<grid, C::THREADS, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
+  const size_t rows = (size_t)a.B * a.H * a.T;
+  const int blocks = static_cast<int>(std::min<size_t>((rows + 31) / 32, size_t(148) * 32));
+  attn_bwd_dq_convert_kernel<kBf16><<<blocks, 256, 0, stream>>>(a);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "fused bwd kernels launch: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+int launch_bwd_fused(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const CUtensorMap& tmDO,
+                     const BwdArgs& a, int dtype, dim3 grid, cudaStream_t stream) {
+  return dtype == KD_BF16 ? launch_fused_t<true>(tmQ, tmK, tmV, tmDO, a, grid, stream)
+                          : launch_fused_t<false>(tmQ, tmK, tmV, tmDO, a, grid, stream);
+}
+
+}  // namespace kd

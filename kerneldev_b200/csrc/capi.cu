@@ -91,6 +91,11 @@ static int check_attn(const kd_attn_params* p, bool backward) {
     return set_error(KD_ERR_ALIGN, "o: pointer and byte strides must be multiples of 16");
   if (backward) {
     if (!p->delta) return set_error(KD_ERR_ARG, "delta scratch is null");
+    if (p->bwd_mode != KD_BWD_SPLIT && p->bwd_mode != KD_BWD_FUSED) return set_error(KD_ERR_ARG, "bwd_mode %d unknown", p->bwd_mode);
+    if (p->bwd_mode == KD_BWD_FUSED) {
+      if (p->D != 64) return set_error(KD_ERR_ARG, "the fused backward (KD_BWD_FUSED) supports head dim 64 only, got %d", p->D);
+      if (!p->dq_acc || (reinterpret_cast<uintptr_t>(p->dq_acc) & 15u)) return set_error(KD_ERR_ARG, "dq_acc scratch is null or not 16-byte aligned");
+    }
     const kd_tensor* outs[3] = {&p->dq, &p->dk, &p->dv};
     for (int i = 0; i < 3; ++i) {
       if (!outs[i]->ptr) return set_error(KD_ERR_ARG, "dq/dk/dv is null");
@@ -177,6 +182,7 @@ int kd_attn_bwd_static(const kd_attn_params* p, void* stream) {
   float* scratch = nullptr;
   if ((rc = static_delta_address((size_t)p->B * p->H * p->T, &scratch)) != 0) return rc;
   q.delta = scratch;
+  q.bwd_mode = KD_BWD_SPLIT;   // the fused backward needs a second, much larger scratch
   if ((rc = check_attn(&q, true)) != 0) return rc;
   return launch_attn_bwd(q, static_cast<cudaStream_t>(stream));
 }
@@ -185,6 +191,12 @@ int kd_workspace_bytes(int32_t B, int32_t H, int32_t T, int32_t D, size_t* bytes
   if (!bytes || B < 1 || H < 1 || T < 1 || D < 1) return set_error(KD_ERR_ARG, "bad workspace query");
   (void)D;
   *bytes = (size_t)B * H * T * sizeof(float);
+  return 0;
+}
+
+int kd_workspace_bytes_fused(int32_t B, int32_t H, int32_t T, int32_t D, size_t* bytes) {
+  if (!bytes || B < 1 || H < 1 || T < 1 || D < 1) return set_error(KD_ERR_ARG, "bad workspace query");
+  *bytes = (size_t)B * H * T * D * sizeof(float);
   return 0;
 }
 

@@ -35,7 +35,7 @@ class HostPipeline:
         return self._stage[key]
 
     def run(self, hq, hk, hv, hdo, ho, hdq, hdk, hdv, lens=None, in_span=None, span_id=None, is_prefix=None,
-            causal=True, sm_scale=None, hadamard_signs=None):
+            causal=True, sm_scale=None, hadamard_signs=None, deterministic=False):
         """hq, hk, hv, hdo: pinned host inputs (B,H,T,D); ho, hdq, hdk, hdv: pinned host outputs of the
         same shape. Metadata tensors are device tensors for the whole batch. Returns after enqueueing;
         synchronise the device (or the copy-out stream) before reading the outputs."""
@@ -62,7 +62,8 @@ class HostPipeline:
             q, k, v = (x.detach().requires_grad_() for x in bufs[:3])
             sl = lambda t: None if t is None else t[lo:hi]
             out = flash_attention(q, k, v, lens=sl(lens), sm_scale=sm_scale, causal=causal, in_span=sl(in_span),
-                                  span_id=sl(span_id), is_prefix=sl(is_prefix), hadamard_signs=hadamard_signs)
+                                  span_id=sl(span_id), is_prefix=sl(is_prefix), hadamard_signs=hadamard_signs,
+                                  deterministic=deterministic)
             out.backward(bufs[3])
             ev = torch.cuda.Event()
             ev.record(cur)

@@ -107,9 +107,11 @@ def _forward(q, k, v, plan: AttentionPlan, sm_scale: float, like_input: bool = F
 
 
 def _backward(q, k, v, o, lse, d_o, plan: AttentionPlan, sm_scale: float, phases: int = 0, bufs=None,
-              like_input: bool = False, deterministic: bool = True):
-    """One kd_attn_bwd call: returns (dQ, dK, dV). ``phases`` selects one of the two backward
-    kernels (see kd_attn_params.bwd_phases); ``bufs`` = (dq, dk, dv, delta) reuses buffers."""
+              like_input: bool = False, deterministic: bool = False):
+    """One kd_attn_bwd call: returns (dQ, dK, dV). ``phases`` selects a part of the backward (see
+    kd_attn_params.bwd_phases); ``bufs`` = (dq, dk, dv, delta[, dq_acc]) reuses buffers.
+    ``deterministic=False`` selects the fused backward where it exists (head_dim 64): one pass over the
+    tiles instead of two, dQ accumulated with fp32 atomics in a (B,H,T,D) scratch."""
     q, k, v, d_o = _usable(q), _usable(k), _usable(v), _usable(d_o)
     B, H, T, D = q.shape
     if bufs is None:
@@ -120,13 +122,21 @@ def _backward(q, k, v, o, lse, d_o, plan: AttentionPlan, sm_scale: float, phases
             dk = torch.empty_like(dq)
             dv = torch.empty_like(dq)
         delta = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
+        dq_acc = None
     else:
-        dq, dk, dv, delta = bufs
+        dq, dk, dv, delta = bufs[:4]
+        dq_acc = bufs[4] if len(bufs) > 4 else None
+    fused = (not deterministic) and D == 64
+    if fused and dq_acc is None:
+        dq_acc = torch.empty((B, H, T, D), dtype=torch.float32, device=q.device)
     p = _params(q, k, v, o, lse, plan, sm_scale)
     p.d_o = _kd_tensor(d_o)
     p.dq, p.dk, p.dv = _kd_tensor(dq), _kd_tensor(dk), _kd_tensor(dv)
     p.delta = delta.data_ptr()
     p.bwd_phases = phases
+    if fused:
+        p.bwd_mode = _capi.KD_BWD_FUSED
+        p.dq_acc = dq_acc.data_ptr()
     stream = torch.cuda.current_stream(q.device).cuda_stream
     plan.poll()
     with torch.cuda.device(q.device):
@@ -239,6 +249,9 @@ def flash_attention(
     "input": O and the gradients take the memory layout of q, k, v. For the model's (B,H,T,D) views
     of (B,T,H,D) memory (model.py:76-78) the ``transpose(1, 2).contiguous()`` after the call
     (model.py:95) and its counterpart in the backward then copy nothing. The drop-in module uses it.
+    deterministic (extension, default False): True forces the two-kernel backward, whose results are
+    bit-identical from run to run; by default head_dim 64 takes the fused backward, which forms S and dP
+    once per tile and adds dQ partials with fp32 atomics (dQ then varies in its last bits between runs).
 
     Returns O, or (O, LSE) with return_lse, or (that, mask[B,H,T,T] bool) with return_attention_mask.
     """

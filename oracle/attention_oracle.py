@@ -155,8 +155,9 @@ def attention_fwd_bwd_operand_rounded(q, k, v, d_o, mask, dtype, sm_scale=None):
 
 def operand_rounding_bounds(q, k, v, d_o, mask, dtype, sm_scale=None):
     """First-order bounds on what rounding the second operand of each product to `dtype` can change:
-    u*|P||V| for O, u*|P|^T|dO| for dV, u*scale*|dS||K| for dQ and u*scale*|dS|^T|Q| for dK, with u the unit
-    roundoff of `dtype` (2^-11 for fp16, 2^-8 for bf16). With N(0,1) inputs these are far below the
+    u*|P||V| for O, u*|P|^T|dO| for dV, scale*(u|dS| + P*u|O||dO|)|K| for dQ and its transpose with |Q| for dK
+    (the second term is the rounding of the stored O that delta = rowsum(O*dO) is formed from), with u the
+    unit roundoff of `dtype` (2^-11 for fp16, 2^-8 for bf16). With N(0,1) inputs these are far below the
     tolerances of the tests; with N(0,20) outliers in K and V single products |dS_ij K_jd| reach the
     hundreds and one rounding of dS_ij moves dQ by more than an absolute 2e-2. Returns (bO, bdQ, bdK, bdV)."""
     u = 2.0 ** -11 if dtype == torch.float16 else 2.0 ** -8
@@ -169,7 +170,9 @@ def operand_rounding_bounds(q, k, v, d_o, mask, dtype, sm_scale=None):
     lse = torch.where(torch.isinf(lse2), torch.zeros_like(lse2), lse2)[..., None]
     p = torch.where(m, torch.exp2(s2 - lse), torch.zeros_like(s2))
     ds = (p * (d_o @ v.transpose(-1, -2) - (o * d_o).sum(-1, keepdim=True))).abs()
-    return (u * (p @ v.abs()), u * scale * (ds @ k.abs()), u * scale * (ds.transpose(-1, -2) @ q.abs()),
+    # delta = rowsum(O*dO) is formed from the stored 16-bit O: its error u*|O||dO| enters dS as P * d(delta)
+    pd = p * (u * (o.abs() * d_o.abs()).sum(-1, keepdim=True))
+    return (u * (p @ v.abs()), scale * ((u * ds + pd) @ k.abs()), scale * ((u * ds + pd).transpose(-1, -2) @ q.abs()),
             u * (p.transpose(-1, -2) @ d_o.abs()))
 
 
