@@ -5,19 +5,29 @@
 
 Workload (default): BASELINE config 2 -- bf16, B=16, H=16, L=4096, D=64, hierarchical mask with
 per-sequence sections drawn from a seed (prefix U[32,256], context U[1024,2048], 4..32 spans of
-16..128 tokens, one MASKQ, PAD) -- on every GPU ("weak" scaling: each rank owns one such batch;
-the (batch, head) pairs are independent, so there is no collective on the data path).
-One step = one forward + one backward over the batch.
+16..128 tokens, one MASKQ, PAD). One step = one forward + one backward over the batch.
+
+Scaling. The (batch, head) pairs of the operator are independent, so there is no collective on the data
+path. The headline `value` is WEAK scaling: every rank owns one config-shaped batch. For N > 1 the line
+also carries `strong`: ONE config-shaped batch split over the ranks by (batch, head) pairs
+(kerneldev_b200.sharding.shard_pairs), aggregate = FLOPs of the whole batch / max time over ranks.
 
 The one JSON line printed by rank 0:
   value      effective TFLOP/s summed over all ranks, inputs resident in HBM. Effective FLOPs =
-             14*D*H*128^2 * (number of non-EMPTY 128x128 mask tiles of the batch), i.e. 4D forward
-             + 10D backward per unmasked pair, recomputation not counted.
+             14*D*H*128^2 * (number of non-EMPTY 128x128 mask tiles of the batch): 4D forward + 10D
+             backward per element of a non-empty tile (BASELINE.json's "unmasked-tile" count; PARTIAL
+             tiles count in full, recomputation is not counted). `flops_exact_pairs` gives the same
+             figure with 14*D*H * (allowed (query, key) pairs) instead.
+  plan       time of the tile classifier (3 launches per new metadata batch) and `value_with_plan`, the
+             headline figure when a new plan is built every step instead of being reused.
   e2e        the same metric through flash_attention() + autograd with HOST (pinned) buffers: every
-             step copies Q, K, V, dO host->device and O, dQ, dK, dV device->host.
+             step copies Q, K, V, dO host->device and O, dQ, dK, dV device->host; `copy_ceiling_ms` is
+             the time of those copies alone (no kernels) at this N.
   roofline   dominant kernel: algorithmic FLOPs per launch / its CUDA-event time, against the
-             measured bf16 peak of MEASURED_PEAKS.json.
-  cpu_baseline  the CPU oracle (dense-masked fp32 torch math) on a bounded sample, on the host cores.
+             measured bf16 peak of MEASURED_PEAKS.json; `dq_accumulate` is the fused backward's dQ
+             reduction traffic per launch and its rate.
+  other_configs  short legs for BASELINE configs 1 and 3 (N = 1 only).
+  cpu_baseline   the CPU oracle (dense-masked fp32 torch math) on a bounded sample, on the host cores.
 
 --impl reference times the CPU restatement of the reference algorithm (oracle/) on the host cores
 for the same workload, metric and unit; it is the only other place this file executes oracle/.
@@ -51,11 +61,7 @@ CONFIGS = {
             name="config3: hierarchical-mask + Hadamard fwd+bwd fp16 B4 H32 L8192 D128"),
 }
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch and per batch row of config 2,
-# from the ncu capture summarised in profiles/attention_kernels_config2_batch4.md (batch 4: 99.7,
-# 136.2 and 159.3 MB); traffic grows in proportion to the number of (batch, head) pairs.
-NCU_TRAFFIC_PER_BATCH_ROW = {"attn_fwd_kernel": 99.7e6 / 4, "attn_bwd_dq_kernel": 136.2e6 / 4,
-                             "attn_bwd_dkdv_kernel": 159.3e6 / 4}
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "attention_kernels_traffic.json")
 
 
 def load_peaks():
@@ -65,6 +71,16 @@ def load_peaks():
             d = json.load(f)
         return d, "measured"
     return dict(FALLBACK_PEAKS), "fallback"
+
+
+def load_traffic():
+    """DRAM bytes per launch and per batch row of config 2 for each kernel, written next to the ncu summary
+    they come from; traffic grows in proportion to the number of (batch, head) pairs."""
+    try:
+        with open(TRAFFIC_FILE) as f:
+            return json.load(f)
+    except Exception:
+        return {}
 
 
 def make_metadata(cfg, seed):
@@ -167,7 +183,7 @@ def time_cpu_oracle(cfg, seed, budget_s, max_heads=None):
             break
     tflops = flops / spent / 1e12
     sample = (f"the first {heads} of {B * H} (batch, head) pairs of the workload, dense-masked fp32 torch math "
-              f"(oracle/attention_oracle.py), {spent:.1f} s")
+              f"(oracle/attention_oracle.py; it executes all L x L pairs and is credited with the non-empty tiles only), {spent:.1f} s")
     return tflops, sample, spent, heads
 
 
@@ -200,11 +216,124 @@ def run_reference(args, cfg):
 # --------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------
+class Workload:
+    """Resident inputs, plan and reusable buffers of one (possibly sharded) batch on one GPU."""
+
+    def __init__(self, cfg, dev, seed, meta_np, rows=None, heads=None):
+        from kerneldev_b200 import generate_hadamard_signs
+        from kerneldev_b200.plan import get_plan
+        self.cfg, self.dev = cfg, dev
+        ins, sid, pre, lens = meta_np
+        if rows is not None and ins is not None:
+            ins, sid, pre, lens = (a[rows[0]:rows[1]] for a in (ins, sid, pre, lens))
+        self.B = cfg["B"] if rows is None else rows[1] - rows[0]
+        self.H = cfg["H"] if heads is None else heads[1] - heads[0]
+        self.L, self.D = cfg["L"], cfg["D"]
+        self.dtype = torch.bfloat16 if cfg["dtype"] == "bf16" else torch.float16
+        tt = lambda a, dt: None if a is None else torch.as_tensor(a, dtype=dt, device=dev)
+        self.meta = dict(in_span=tt(ins, torch.bool), span_id=tt(sid, torch.int64), is_prefix=tt(pre, torch.bool),
+                         lens=tt(lens, torch.int32))
+        g = torch.Generator(device=dev).manual_seed(seed)
+        shape = (self.B, self.H, self.L, self.D)
+        self.q, self.k, self.v, self.do = (torch.randn(shape, generator=g, device=dev, dtype=self.dtype) for _ in range(4))
+        self.signs = None
+        if cfg["hadamard"]:
+            s = generate_hadamard_signs(cfg["H"], self.D, seed=seed, device=dev)
+            self.signs = s if heads is None else s[heads[0]:heads[1]].contiguous()
+        self.sm_scale = self.D ** -0.5
+        self.hier = cfg["hier"]
+        self.plan = self.new_plan()
+        self.nonempty = self.plan.nonempty_tiles()
+        self.f_eff = 14.0 * self.D * self.H * 128.0 * 128.0 * self.nonempty
+        self.bufs = (torch.empty_like(self.q), torch.empty_like(self.q), torch.empty_like(self.q),
+                     torch.empty((self.B, self.H, self.L), dtype=torch.float32, device=dev),
+                     torch.empty(shape, dtype=torch.float32, device=dev) if self.D == 64 else None)
+        self.fused = self.D == 64
+        self.launches_per_step = 4 + (4 if self.signs is not None else 0)
+
+    def new_plan(self, cached=True):
+        from kerneldev_b200.plan import AttentionPlan, get_plan
+        m = self.meta
+        if cached:
+            return get_plan(self.B, self.L, self.dev, m["in_span"], m["span_id"], m["is_prefix"], m["lens"], True, self.hier)
+        return AttentionPlan(self.B, self.L, self.dev, m["in_span"], m["span_id"], m["is_prefix"], m["lens"], True, self.hier)
+
+    def transformed(self):
+        if self.signs is None:
+            return self.q, self.k
+        from kerneldev_b200 import hadamard_transform
+        return hadamard_transform(self.q, self.signs), hadamard_transform(self.k, self.signs)
+
+    def step(self, plan=None):
+        """Forward + backward on resident inputs through the raw C-ABI calls, buffers reused."""
+        from kerneldev_b200.original_kernel import _backward, _forward, _hadamard_call
+        plan = plan or self.plan
+        qq, kk = self.transformed()
+        o, lse = _forward(qq, kk, self.v, plan, self.sm_scale)
+        dq, dk, dv = _backward(qq, kk, self.v, o, lse, self.do, plan, self.sm_scale, 0, self.bufs)
+        if self.signs is not None:
+            dq, dk = _hadamard_call(dq, self.signs, True), _hadamard_call(dk, self.signs, True)
+        return o, lse
+
+    def allowed_pairs(self):
+        """Exact number of allowed (query, key) pairs of the batch (one head), from the plan's dense mask."""
+        total = 0
+        from kerneldev_b200.plan import AttentionPlan
+        m = self.meta
+        for b in range(self.B):
+            sl = lambda t: None if t is None else t[b:b + 1]
+            p = AttentionPlan(1, self.L, self.dev, sl(m["in_span"]), sl(m["span_id"]), sl(m["is_prefix"]), sl(m["lens"]), True, self.hier)
+            total += int(p.dense_mask().sum().item())
+        return total
+
+
+def time_call(fn, iters):
+    fn(); torch.cuda.synchronize()
+    a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b_.record(); torch.cuda.synchronize()
+    return a.elapsed_time(b_) / iters
+
+
+def kernel_times(w, iters):
+    """CUDA-event times of the individual kernels of one step (inputs larger than L2 at the bench sizes)."""
+    from kerneldev_b200.original_kernel import _backward, _forward
+    qq, kk = w.transformed()
+    o, lse = _forward(qq, kk, w.v, w.plan, w.sm_scale)
+    per_pair = w.D * w.H * 128.0 * 128.0 * w.nonempty
+    ms_fwd = time_call(lambda: _forward(qq, kk, w.v, w.plan, w.sm_scale), iters)
+    bw = lambda ph: time_call(lambda: _backward(qq, kk, w.v, o, lse, w.do, w.plan, w.sm_scale, ph, w.bufs), iters)
+    if w.fused:
+        return {
+            # name: (ms, algorithmic FLOPs per launch, executed MMA FLOPs per launch)
+            "attn_fwd_kernel": (ms_fwd, 4 * per_pair, 4 * per_pair),
+            "attn_bwd_delta_kernel": (bw(1), 0.0, 0.0),
+            "attn_bwd_fused_kernel": (bw(2), 10 * per_pair, 10 * per_pair),   # S, dP, dV, dK, dQ (+ the dQ conversion kernel)
+        }
+    return {
+        "attn_fwd_kernel": (ms_fwd, 4 * per_pair, 4 * per_pair),
+        "attn_bwd_dq_kernel": (bw(1), 6 * per_pair, 6 * per_pair),        # delta; S, dP, dQ
+        "attn_bwd_dkdv_kernel": (bw(2), 4 * per_pair, 8 * per_pair),      # dV, dK (+ recomputed S, dP)
+    }
+
+
+def timed_steps(fn, steps, barrier):
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(steps):
+        fn()
+    ev1.record()
+    barrier()
+    return ev0.elapsed_time(ev1)
+
+
 def run_ours(args, cfg):
     import torch.distributed as dist
-    from kerneldev_b200 import flash_attention, generate_hadamard_signs
-    from kerneldev_b200.original_kernel import _backward, _forward
-    from kerneldev_b200.plan import get_plan
+    from kerneldev_b200 import flash_attention  # noqa: F401  (loads the library; fails loudly when it is missing)
+    from kerneldev_b200.sharding import shard_pairs
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -216,145 +345,172 @@ def run_ours(args, cfg):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    B, H, L, D = cfg["B"], cfg["H"], cfg["L"], cfg["D"]
-    dtype = torch.bfloat16 if cfg["dtype"] == "bf16" else torch.float16
-    seed = 1234 + rank                       # Q, K, V, dO differ per rank
-    ins, sid, pre, lens = make_metadata(cfg, 1234)   # same section layout on every rank: equal work per GPU
-    tt = lambda a, dt: None if a is None else torch.as_tensor(a, dtype=dt, device=dev)
-    meta = dict(in_span=tt(ins, torch.bool), span_id=tt(sid, torch.int64), is_prefix=tt(pre, torch.bool),
-                lens=tt(lens, torch.int32))
-    g = torch.Generator(device=dev).manual_seed(seed)
-    q, k, v, do = (torch.randn((B, H, L, D), generator=g, device=dev, dtype=dtype) for _ in range(4))
-    signs = generate_hadamard_signs(H, D, seed=seed, device=dev) if cfg["hadamard"] else None
-    sm_scale = D ** -0.5
-
-    plan = get_plan(B, L, dev, meta["in_span"], meta["span_id"], meta["is_prefix"], meta["lens"], True, cfg["hier"])
-    nonempty = plan.nonempty_tiles()
-    f_eff = effective_flops(cfg, nonempty)
-    f_dense = 14.0 * D * B * H * float(L) * L
-
-    # ---- kernel-level step: inputs resident in HBM, raw C-ABI calls, buffers reused ----------
-    bufs = (torch.empty_like(q), torch.empty_like(q), torch.empty_like(q),
-            torch.empty((B, H, L), dtype=torch.float32, device=dev))
-    if signs is not None:
-        from kerneldev_b200 import hadamard_transform
-
-    def step_resident():
-        if signs is not None:
-            qq, kk = hadamard_transform(q, signs), hadamard_transform(k, signs)
-        else:
-            qq, kk = q, k
-        o, lse = _forward(qq, kk, v, plan, sm_scale)
-        dq, dk, dv = _backward(qq, kk, v, o, lse, do, plan, sm_scale, 0, bufs)
-        if signs is not None:
-            from kerneldev_b200.original_kernel import _hadamard_call
-            dq, dk = _hadamard_call(dq, signs, True), _hadamard_call(dk, signs, True)
-        return o, lse
-
-    launches_per_step = 4 + (4 if signs is not None else 0)   # forward, delta, dQ, dK/dV (+ Hadamard passes)
-
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(x):
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(x):
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    B, H, L, D = cfg["B"], cfg["H"], cfg["L"], cfg["D"]
+    meta_np = make_metadata(cfg, 1234)   # the same section layout on every rank: equal work per GPU
+    w = Workload(cfg, dev, 1234 + rank, meta_np)   # Q, K, V, dO differ per rank
+    f_dense = 14.0 * D * B * H * float(L) * L
+
+    # ---- weak scaling, inputs resident in HBM ---------------------------------------------------
     for _ in range(args.warmup):
-        step_resident()
+        w.step()
     sampler = ClockSampler(local_rank)
     barrier()
     if rank == 0:
         sampler.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    ev0.record()
-    for _ in range(args.steps):
-        step_resident()
-    ev1.record()
-    barrier()
-    ms_total = ev0.elapsed_time(ev1)
-    plan.check_status()
-    t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
-    feff_t = torch.tensor([f_eff], device=dev, dtype=torch.float64)
+    ms_total = timed_steps(w.step, args.steps, barrier)
+    w.plan.check_status()
+    ms_step = max_over_ranks(ms_total) / args.steps
+    f_eff_all = sum_over_ranks(w.f_eff)
+    value = f_eff_all / (ms_step * 1e-3) / 1e12
+
+    # ---- the classifier: alone, and inside the step ("included" next to the "amortised" headline) ----
+    ms_plan = time_call(lambda: w.new_plan(cached=False), max(3, min(args.steps, 10)))
+    ms_with_plan = max_over_ranks(timed_steps(lambda: w.step(w.new_plan(cached=False)), args.steps, barrier)) / args.steps
+
+    # ---- strong scaling: ONE config-shaped batch split over the ranks ---------------------------
+    strong = None
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dist.all_reduce(feff_t, op=dist.ReduceOp.SUM)
-    ms_step = float(t.item()) / args.steps
-    value = float(feff_t.item()) / (ms_step * 1e-3) / 1e12
+        lo, hi = shard_pairs(B, H, rank, world)
+        if lo % H == 0 and hi % H == 0:      # whole batch rows
+            ws = Workload(cfg, dev, 4321, meta_np, rows=(lo // H, hi // H))
+            split = f"{(hi - lo) // H} of {B} batch rows per GPU"
+        else:                                # part of one row's heads; the row's metadata is replicated
+            assert lo // H == (hi - 1) // H, "a rank's pairs must lie in one batch row"
+            ws = Workload(cfg, dev, 4321, meta_np, rows=(lo // H, lo // H + 1), heads=(lo % H, (hi - 1) % H + 1))
+            split = f"{hi - lo} of {H} heads of one batch row per GPU"
+        for _ in range(args.warmup):
+            ws.step()
+        ms_s = max_over_ranks(timed_steps(ws.step, args.steps, barrier)) / args.steps
+        ms_sp = max_over_ranks(timed_steps(lambda: ws.step(ws.new_plan(cached=False)), args.steps, barrier)) / args.steps
+        f_s = sum_over_ranks(ws.f_eff)
+        strong = {"workload": cfg["name"] + " (one batch over all GPUs)", "split": split, "ms_per_step": ms_s,
+                  "value": f_s / (ms_s * 1e-3) / 1e12, "ms_per_step_with_plan": ms_sp,
+                  "value_with_plan": f_s / (ms_sp * 1e-3) / 1e12, "unit": UNIT,
+                  "note": "efficiency = value / (N x the N=1 value of the same line)"}
+        del ws
 
-    # ---- per-kernel times (rank 0's own kernels, CUDA events on the launching stream) --------
-    def time_call(fn, iters):
-        fn(); torch.cuda.synchronize()
-        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(iters):
-            fn()
-        b_.record(); torch.cuda.synchronize()
-        return a.elapsed_time(b_) / iters
-
-    qq, kk = (hadamard_transform(q, signs), hadamard_transform(k, signs)) if signs is not None else (q, k)
-    o, lse = _forward(qq, kk, v, plan, sm_scale)
+    # ---- per-kernel times (rank 0's own kernels, CUDA events on the launching stream) -----------
     it = max(3, min(args.steps, 10))
-    ms_fwd = time_call(lambda: _forward(qq, kk, v, plan, sm_scale), it)
-    ms_dq = time_call(lambda: _backward(qq, kk, v, o, lse, do, plan, sm_scale, 1, bufs), it)
-    ms_dkdv = time_call(lambda: _backward(qq, kk, v, o, lse, do, plan, sm_scale, 2, bufs), it)
-    per_pair = D * H * 128.0 * 128.0 * nonempty
-    kernels = {
-        # name: (ms, algorithmic FLOPs per launch, executed MMA FLOPs per launch)
-        "attn_fwd_kernel": (ms_fwd, 4 * per_pair, 4 * per_pair),
-        "attn_bwd_dq_kernel": (ms_dq, 6 * per_pair, 6 * per_pair),        # S, dP, dQ
-        "attn_bwd_dkdv_kernel": (ms_dkdv, 4 * per_pair, 8 * per_pair),    # dV, dK (+ recomputed S, dP)
-    }
+    kernels = kernel_times(w, it)
     dom = max(kernels, key=lambda n: kernels[n][0])
     peaks, peak_kind = load_peaks()
     peak_tf = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
     peak_sus = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+    peak_hbm = float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
     dom_ms, dom_alg, dom_exec = kernels[dom]
     achieved = dom_alg / (dom_ms * 1e-3) / 1e12
+    traffic = load_traffic().get(dom)
     roofline = {
         "bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
         "frac": achieved / peak_tf,
-        "traffic": (NCU_TRAFFIC_PER_BATCH_ROW[dom] * B) if (args.config == 2) else None,
-        "traffic_note": "bytes per launch: ncu capture at batch 4 scaled to this batch",
+        "traffic": (traffic["dram_bytes_per_batch_row"] * B) if (traffic and args.config == 2) else None,
+        "traffic_note": "bytes per launch: ncu capture at a smaller batch scaled by batch rows (profiles/attention_kernels_traffic.json)",
         "peak_kind": peak_kind + " burst (kernel timed alone)",
         "executed_tflops": dom_exec / (dom_ms * 1e-3) / 1e12,
         "kernels_ms": {n: kernels[n][0] for n in kernels},
         "kernels_algorithmic_tflops": {n: kernels[n][1] / (kernels[n][0] * 1e-3) / 1e12 for n in kernels},
     }
+    if w.fused:
+        red_bytes = w.nonempty * w.H * 128.0 * w.D * 4.0     # one fp32 dQ tile per non-empty tile and head
+        ms_f = kernels["attn_bwd_fused_kernel"][0]
+        roofline["dq_accumulate"] = {
+            "reduce_bytes_per_launch": red_bytes, "GBps": red_bytes / (ms_f * 1e-3) / 1e9,
+            "hbm_peak_GBps": peak_hbm,
+            "note": "fp32 red.global.add traffic of the dQ partials over the fused kernel's time; it is served by L2, "
+                    "HBM sees the scratch once zeroed, once written back and once read by the conversion kernel"}
 
-    # ---- end to end: public API with host buffers ----------------------------------------------
-    hq, hk, hv, hdo = (x.cpu().pin_memory() for x in (q, k, v, do))
-    ho, hdq, hdk, hdv = (torch.empty_like(hq).pin_memory() for _ in range(4))
-    h2d = sum(x.numel() * x.element_size() for x in (hq, hk, hv, hdo))
-    d2h = sum(x.numel() * x.element_size() for x in (ho, hdq, hdk, hdv))
+    # ---- end to end: public API with host buffers ------------------------------------------------
+    e2e = None
+    if not args.kernels_only:
+        from kerneldev_b200.host_io import HostPipeline
+        hq, hk, hv, hdo = (x.cpu().pin_memory() for x in (w.q, w.k, w.v, w.do))
+        ho, hdq, hdk, hdv = (torch.empty_like(hq).pin_memory() for _ in range(4))
+        h2d = sum(x.numel() * x.element_size() for x in (hq, hk, hv, hdo))
+        d2h = sum(x.numel() * x.element_size() for x in (ho, hdq, hdk, hdv))
+        pipe = HostPipeline(dev, chunks=args.e2e_chunks)
 
-    from kerneldev_b200.host_io import HostPipeline
-    pipe = HostPipeline(dev, chunks=args.e2e_chunks)
+        def step_e2e():
+            # public API on host buffers: chunks of the batch are copied in, run through flash_attention +
+            # autograd and copied out on three streams, so PCIe transfers overlap the kernels
+            pipe.run(hq, hk, hv, hdo, ho, hdq, hdk, hdv, causal=True, hadamard_signs=w.signs, **w.meta)
 
-    def step_e2e():
-        # public API on host buffers: chunks of the batch are copied in, run through flash_attention +
-        # autograd and copied out on three streams, so PCIe transfers overlap the kernels
-        pipe.run(hq, hk, hv, hdo, ho, hdq, hdk, hdv, causal=True, hadamard_signs=signs, **meta)
-
-    e2e_steps = max(2, min(args.steps, 5))
-    if args.kernels_only:
-        ms_e2e, e2e_value = None, None
-    else:
+        e2e_steps = max(2, min(args.steps, 5))
         for _ in range(2):
             step_e2e()
-        barrier()
-        ev0.record()
-        for _ in range(e2e_steps):
-            step_e2e()
-        ev1.record()
-        barrier()
-        t = torch.tensor([ev0.elapsed_time(ev1)], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_e2e = float(t.item()) / e2e_steps
-        e2e_value = float(feff_t.item()) / (ms_e2e * 1e-3) / 1e12
+        ms_e2e = max_over_ranks(timed_steps(step_e2e, e2e_steps, barrier)) / e2e_steps
+        # the copies alone, both directions at once, same bytes, no kernels: what the host link allows at this N
+        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        dst = [torch.empty_like(w.q) for _ in range(4)]
+
+        def copies_only():
+            cur = torch.cuda.current_stream(dev)
+            s_in.wait_stream(cur); s_out.wait_stream(cur)
+            with torch.cuda.stream(s_in):
+                for d_, s_ in zip(dst, (hq, hk, hv, hdo)):
+                    d_.copy_(s_, non_blocking=True)
+            with torch.cuda.stream(s_out):
+                for d_, s_ in zip((ho, hdq, hdk, hdv), w.bufs[:3] + (w.q,)):
+                    d_.copy_(s_, non_blocking=True)
+            cur.wait_stream(s_in); cur.wait_stream(s_out)
+
+        copies_only()
+        ms_copy = max_over_ranks(timed_steps(copies_only, e2e_steps, barrier)) / e2e_steps
+        del dst
+        e2e = {"value": f_eff_all / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": ms_e2e, "steps": e2e_steps, "copy_ceiling_ms": ms_copy,
+               "copy_ceiling_over_e2e": ms_copy / ms_e2e,
+               "copy_GBps_per_gpu": (h2d + d2h) / (ms_copy * 1e-3) / 1e9}
+        del hq, hk, hv, hdo, ho, hdq, hdk, hdv, pipe
 
     # the sampler covers the timed region and the per-kernel / end-to-end legs that follow it (all GPU load)
     clocks = sampler.stop() if rank == 0 else None
+
+    # ---- the other BASELINE configurations, short legs (single GPU only) -------------------------
+    other = None
+    pairs_exact = None
+    if rank == 0 and world == 1 and not args.kernels_only:
+        pairs_exact = w.allowed_pairs()
+        nonempty, frac = w.nonempty, w.nonempty / float(B * w.plan.NT * w.plan.NT)
+        stats = w.plan.stats.sum(0).tolist()
+        del w
+        torch.cuda.empty_cache()
+        other = []
+        for cid in sorted(CONFIGS):
+            if cid == args.config:
+                continue
+            c2 = dict(CONFIGS[cid])
+            w2 = Workload(c2, dev, 1234, make_metadata(c2, 1234))
+            for _ in range(3):
+                w2.step()
+            ms2 = timed_steps(w2.step, max(3, min(args.steps, 10)), barrier) / max(3, min(args.steps, 10))
+            k2 = kernel_times(w2, 3)
+            v2 = w2.f_eff / (ms2 * 1e-3) / 1e12
+            other.append({"workload": c2["name"], "dtype": c2["dtype"], "ms_per_step": ms2, "value": v2, "unit": UNIT,
+                          "pct_of_bf16_peak_burst": 100 * v2 / peak_tf, "kernels_ms": {n: k2[n][0] for n in k2},
+                          "nonempty_tiles": w2.nonempty})
+            del w2
+            torch.cuda.empty_cache()
+    else:
+        nonempty, frac = w.nonempty, w.nonempty / float(B * w.plan.NT * w.plan.NT)
+        stats = w.plan.stats.sum(0).tolist()
+
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu_baseline and not args.kernels_only:
@@ -367,18 +523,25 @@ def run_ours(args, cfg):
             "dtype": cfg["dtype"], "data": "synthetic",
             "config": {"workload": cfg["name"], "per_gpu_batch": B, "heads": H, "seq_len": L, "head_dim": D,
                        "sharding": "one config-shaped batch per GPU, (batch, head) pairs independent, no collective",
-                       "l2": "inputs larger than L2 (Q, K, V, dO are %d MB each)" % (q.numel() * 2 // 2 ** 20),
-                       "nonempty_tile_fraction": nonempty / float(B * plan.NT * plan.NT)},
+                       "l2": "inputs larger than L2 (Q, K, V, dO are %d MB each)" % (B * H * L * D * 2 // 2 ** 20),
+                       "backward": "fused (dQ accumulated in fp32 with atomics)" if D == 64 else "two kernels (dQ, dK/dV)",
+                       "nonempty_tile_fraction": frac, "full_tiles": stats[0], "partial_tiles": stats[1]},
             "per_gpu_tflops": per_gpu,
             "pct_of_bf16_peak": {"burst": 100 * per_gpu / peak_tf, "sustained": 100 * per_gpu / peak_sus, "peaks": peak_kind},
             "dense_equivalent_tflops": f_dense * world / (ms_step * 1e-3) / 1e12,
+            "flops_exact_pairs": None if pairs_exact is None else {
+                "allowed_pairs": pairs_exact, "share_of_nonempty_tile_area": pairs_exact / (nonempty * 16384.0),
+                "tflops": 14.0 * D * H * pairs_exact / (ms_step * 1e-3) / 1e12},
             "tokens_per_s": B * L * world / (ms_step * 1e-3),
-            "e2e": None if e2e_value is None else {
-                "value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": ms_e2e, "steps": e2e_steps},
-            "gpu_launches": launches_per_step * args.steps,
+            "plan": {"classifier_ms": ms_plan, "ms_per_step_with_plan": ms_with_plan,
+                     "value_with_plan": f_eff_all / (ms_with_plan * 1e-3) / 1e12,
+                     "note": "headline reuses the plan (one per metadata batch, shared by heads and layers); value_with_plan builds it every step"},
+            "strong": strong,
+            "e2e": e2e,
+            "gpu_launches": (4 + (4 if cfg["hadamard"] else 0)) * args.steps,
             "clocks": clocks,
             "roofline": roofline,
+            "other_configs": other,
             "cpu_baseline": cpu,
         }
         print(json.dumps(line), flush=True)
@@ -395,7 +558,7 @@ def main():
     ap.add_argument("--config", type=int, default=2, choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch size (profiling on a small case)")
-    ap.add_argument("--kernels-only", action="store_true", help="skip the end-to-end and CPU legs (profiling)")
+    ap.add_argument("--kernels-only", action="store_true", help="skip the end-to-end, other-config and CPU legs (profiling)")
     ap.add_argument("--e2e-chunks", type=int, default=8, help="batch chunks of the host-buffer pipeline in the end-to-end leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

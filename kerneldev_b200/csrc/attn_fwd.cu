@@ -24,6 +24,9 @@
 // sm_scale*log2(e), exp2, LSE = m + log2(l)); rows without any visible key give O = 0 and
 // LSE = -inf.
 #include "attn_common.cuh"
+#ifdef KD_TEST_DROP_LOAD
+#include <stdlib.h>
+#endif
 
 namespace kd {
 
@@ -40,6 +43,9 @@ struct FwdArgs {
   void* o;
   int64_t o_sb, o_sh, o_st;
   float* lse;
+#ifdef KD_TEST_DROP_LOAD
+  int test_drop_load;   // wait time-out test build: the producer of CTA (0,0,0) leaves out its first K tile load
+#endif
 };
 
 template <int HD>
@@ -257,6 +263,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         return true;
       };
       int k_cnt = 0, v_cnt = 0, q_loaded = 0;   // tiles issued so far, over all heads
+      int k_dropped = -1;                       // index of a K tile that was never requested (test builds only)
       ok = load_q(0);
       q_loaded = 1;
       for (int hh = 0; hh < nh && ok; ++hh) {
@@ -267,6 +274,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         for (int e = 0; e < n && ok; ++e) {
           const int kt = sList[e] & 0xFF;
+#ifdef KD_TEST_DROP_LOAD
+          // Test build only: this one K tile is never requested (no copy, no expected bytes), so the S issuer's
+          // bounded wait for it runs out and the CTA has to unwind. Nothing is left in flight for the stage.
+          if (a.test_drop_load && hh == 0 && e == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+            k_dropped = k_cnt++;
+          } else
+#endif
           {
             const int s = k_cnt % C::KST;
             ok = mbar_wait(smem_u32(&bar_k_empty[s]), ((k_cnt / C::KST) & 1) ^ 1, &abortf, a.status, W_F_KEMPTY);
@@ -293,7 +307,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       if (abortf.v != 0) {
         // unwinding: let every copy already in flight land (bounded) before the CTA exits
-        for (int e = max(0, k_cnt - C::KST); e < k_cnt; ++e) drain_wait(smem_u32(&bar_k_full[e % C::KST]), (e / C::KST) & 1);
+        for (int e = max(0, k_cnt - C::KST); e < k_cnt; ++e)
+          if (e != k_dropped) drain_wait(smem_u32(&bar_k_full[e % C::KST]), (e / C::KST) & 1);
         for (int e = max(0, v_cnt - C::VST); e < v_cnt; ++e) drain_wait(smem_u32(&bar_v_full[e % C::VST]), (e / C::VST) & 1);
         for (int hh = max(0, q_loaded - C::NQ); hh < q_loaded; ++hh) drain_wait(smem_u32(&bar_q_full[hh % C::NQ]), (hh / C::NQ) & 1);
       }
@@ -637,6 +652,10 @@ static int launch_fwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
   a.order = pv.order; a.tilebits = pv.tilebits;
   a.o = p.o.ptr; a.o_sb = p.o.stride_b; a.o_sh = p.o.stride_h; a.o_st = p.o.stride_t;
   a.lse = p.lse;
+#ifdef KD_TEST_DROP_LOAD
+  const char* drop = getenv("KD_TEST_DROP_LOAD");
+  a.test_drop_load = (drop != nullptr && atoi(drop) != 0) ? 1 : 0;
+#endif
   auto kern = attn_fwd_kernel<HD, kBf16>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_ALLOC);
   if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "fwd smem attribute: %s", cudaGetErrorString(e));
