@@ -10,10 +10,12 @@
 //     dQ_tile = dS K                                  (dS^T is also written to shared memory, which the
 //                                                      tensor core reads as an MN-major A operand)
 // 5 products and one exponential pass. dK and dV stay in TMEM for the whole key tile; the dQ partial of
-// every tile is added to an fp32 scratch (B,H,T,64) with red.global.add.v4.f32 (the additions of
-// different key tiles arrive in no fixed order, so dQ is not bit-reproducible from run to run) and a
-// bandwidth-bound kernel converts the scratch to the output dtype afterwards. The delta kernel, which
-// runs first anyway, zeroes the scratch.
+// every tile is added to an fp32 scratch (B,H,T,64) by a TMA bulk reduction (cp.reduce.async.bulk.tensor
+// .add, fp32 adds performed in L2 on whole 128-byte lines; the additions of different key tiles arrive in
+// no fixed order, so dQ is not bit-reproducible from run to run) and a bandwidth-bound kernel converts
+// the scratch to the output dtype afterwards. The delta kernel, which runs first anyway, zeroes the
+// scratch. The dQ tile is staged for the reduction in the shared-memory buffer its own dS^T came from,
+// which the dQ product has finished reading by then.
 //
 // 768 threads: warp 0 TMA producer; warp 3 / warp 2 issue S^T / dP^T per 64-query unit (N = 64);
 // warp 1 issues the accumulating products and dQ; warps 4-19 are four compute warpgroups (two per unit,
@@ -45,8 +47,8 @@ struct FusedCfg {
   static constexpr uint32_t TM_DK = NBUF * 128, TM_DV = TM_DK + HD, TM_DQ = TM_DV + HD;   // dQ buffer t at TM_DQ + 64 t
   static_assert(TM_DQ + 2 * HD <= 512, "TMEM budget");
   static_assert(SMEM_ALLOC <= 232448, "shared memory budget");
-  // registers: 80 per thread at launch; light warps release down to 56, the dQ warps to 64, compute warps take 88
-  static constexpr int REGS_LIGHT = 56, REGS_DQ = 64, REGS_COMPUTE = 88;
+  // registers: 80 per thread at launch; light warps release down to 56, the dQ warps to 72, compute warps take 88
+  static constexpr int REGS_LIGHT = 56, REGS_DQ = 72, REGS_COMPUTE = 88;
   static_assert(4 * 32 * REGS_LIGHT + 4 * 32 * REGS_DQ + 16 * 32 * REGS_COMPUTE <= 768 * 80, "register pool");
 };
 
@@ -64,17 +66,12 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8])
 __device__ __forceinline__ void st_shared_v4(uint32_t saddr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
-__device__ __forceinline__ void red_add_v4(float* gptr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
-               ::"l"(gptr), "f"(__uint_as_float(x)), "f"(__uint_as_float(y)), "f"(__uint_as_float(z)), "f"(__uint_as_float(w))
-               : "memory");
-}
 
 template <bool kBf16>
 __global__ void __launch_bounds__(FusedCfg::THREADS, 1)
 attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
-                      const BwdArgs a) {
+                      const __grid_constant__ CUtensorMap tmAcc, const BwdArgs a) {
   using C = FusedCfg;
   constexpr int HD = C::HD;
   extern __shared__ uint8_t smem_raw[];
@@ -115,7 +112,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     for (int t = 0; t < 2; ++t) {
       mbar_init(smem_u32(&bar_dq_full[t]), 1);
       mbar_init(smem_u32(&bar_dq_empty[t]), 128);  // the dQ warpgroup has read the buffer
-      mbar_init(smem_u32(&bar_ds_empty[t]), 1);    // the dQ product has read the dS^T buffer
+      mbar_init(smem_u32(&bar_ds_empty[t]), 1);    // the dS^T buffer is free: its dQ product and the reduction staged in it are done
     }
     mbar_init(smem_u32(&bar_acc_full), 1);
     mbar_init(smem_u32(&bar_acc_free), 512);       // every compute thread has read its part of dK and dV
@@ -272,11 +269,12 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             }
             const uint32_t tDQ = tbase + C::TM_DQ + tb * HD;
             const uint32_t alo = loDS + tb * (2 * C::TILE_BYTES >> 4);
+#ifndef KD_X_NO_DQ
             mma_ss_split(tDQ, alo, loK, hi, idesc_m3, 0u);
 #pragma unroll
             for (int kk = 1; kk < KD_TILE / 16; ++kk) mma_ss_split(tDQ, alo + koff_mnmajor(kk), loK + koff_mnmajor(kk), hi, idesc_m3, 1u);
+#endif
             mma_commit(smem_u32(&bar_dq_full[tb]));
-            mma_commit(smem_u32(&bar_ds_empty[tb]));
             ++tcount;
           }
           if (++buf == C::NBUF) { buf = 0; round_parity ^= 1; }
@@ -412,8 +410,10 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           tmem_st8(tP + hf * 8, pk_ds);   // dS^T over the start of its dP^T
           // the same dS^T values as two 16-byte chunks of this key's row of the tile's dS^T block
           const uint32_t ch = static_cast<uint32_t>(4 * c0 + 2 * hf);
+#ifndef KD_X_NO_DS
           st_shared_v4(ds_base + (((ch + 0u) ^ ds_sw) << 4), pk_ds[0], pk_ds[1], pk_ds[2], pk_ds[3]);
           st_shared_v4(ds_base + (((ch + 1u) ^ ds_sw) << 4), pk_ds[4], pk_ds[5], pk_ds[6], pk_ds[7]);
+#endif
         }
         fence_proxy_async_smem();   // the dQ product reads these shared-memory writes through the async proxy
         tmem_wait_st();
@@ -451,24 +451,28 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
   } else {
     reg_dealloc<C::REGS_DQ>();
-    // ------------------------------ dQ warpgroup: TMEM -> fp32 additions in global memory ------------------------------
+    // ------------------------------ dQ warpgroup: TMEM -> shared memory -> bulk reduction into the fp32 scratch ------------------------------
     const int wq = warp & 3;
     const int row = wq * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    const uint32_t st_row = static_cast<uint32_t>(row) * 128u, st_sw = static_cast<uint32_t>(row & 7);
+    const bool leader = (warp == 20 && lane == 0);
+    if (leader) tma_prefetch_desc(&tmAcc);
     bool ok = true;
     int tcount = 0;
     for (int hh = 0; hh < nh && ok; ++hh) {
-      const int h = h0 + hh;
-      float* acc_h = a.dq_acc + ((size_t)b * a.H + h) * a.T * HD;
+      const int bh = b * a.H + h0 + hh;
       for (int e = 0; e < n; ++e) {
         const int tb = tcount & 1;
-        const int qi = (list[e] & 0xFF) * KD_TILE + row;
+        const int q0 = (list[e] & 0xFF) * KD_TILE;
         ok = mbar_wait(smem_u32(&bar_dq_full[tb]), (tcount >> 1) & 1, &abortf, a.status, W_U_DQFULL);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
+        // the dQ product was the last reader of this tile's dS^T buffer: its 32 KB now stage the dQ tile as two
+        // [128 rows][32 floats] boxes in the 128-byte-swizzled layout the tensor map expects
+        const uint32_t stage = sDS + tb * (2 * C::TILE_BYTES);
         const uint32_t tDQ = tbase + lane_base + C::TM_DQ + tb * HD;
-        float* dst = acc_h + (size_t)qi * HD;
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
           uint32_t r[32];
@@ -476,16 +480,30 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           tmem_wait_ld();
           if (hf == 1) {
             tc_fence_before_sync();
-            mbar_arrive(smem_u32(&bar_dq_empty[tb]));   // the product of the tile after next may overwrite the buffer
+            mbar_arrive(smem_u32(&bar_dq_empty[tb]));   // the product of the tile after next may overwrite the TMEM buffer
           }
-          if (qi < a.T) {
+#ifndef KD_X_NO_RED
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) red_add_v4(dst + hf * 32 + j, r[j], r[j + 1], r[j + 2], r[j + 3]);
-          }
+          for (int cch = 0; cch < 8; ++cch)
+            st_shared_v4(stage + hf * C::TILE_BYTES + st_row + ((static_cast<uint32_t>(cch) ^ st_sw) << 4), r[4 * cch], r[4 * cch + 1],
+                         r[4 * cch + 2], r[4 * cch + 3]);
+#endif
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(1, 128);
+        if (leader) {
+#ifndef KD_X_NO_RED
+          tma_reduce_add_3d(&tmAcc, stage, 0, q0, bh);
+          tma_reduce_add_3d(&tmAcc, stage + C::TILE_BYTES, 32, q0, bh);
+          bulk_commit_group();
+          bulk_wait_group_read0();
+#endif
+          mbar_arrive(smem_u32(&bar_ds_empty[tb]));    // compute warps may write the tile after next's dS^T here
         }
         ++tcount;
       }
     }
+    if (leader) bulk_wait_group0();
   }
 
   tc_fence_before_sync();
@@ -518,10 +536,13 @@ template <bool kBf16>
 static int launch_fused_t(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const CUtensorMap& tmDO,
                           const BwdArgs& a, dim3 grid, cudaStream_t stream) {
   using C = FusedCfg;
+  CUtensorMap tmAcc;
+  int rc = encode_tensor_map_f32_rows(&tmAcc, a.dq_acc, a.B * a.H, a.T, C::HD, KD_TILE, "dq_acc");
+  if (rc != 0) return rc;
   auto kern = attn_bwd_fused_kernel<kBf16>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_ALLOC);
   if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "fused bwd smem attribute: %s", cudaGetErrorString(e));
-  kern<<<grid, C::THREADS, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, a);
+  kern<<<grid, C::THREADS, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, tmAcc, a);
   const size_t rows = (size_t)a.B * a.H * a.T;
   const int blocks = static_cast<int>(std::min<size_t>((rows + 31) / 32, size_t(148) * 32));
   attn_bwd_dq_convert_kernel<kBf16><<<blocks, 256, 0, stream>>>(a);

@@ -61,6 +61,20 @@ int encode_tensor_map(CUtensorMap* out, const kd_tensor& t, int B, int H, int T,
   return 0;
 }
 
+int encode_tensor_map_f32_rows(CUtensorMap* out, float* base, int slices, int T, int D, int box_rows, const char* name) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return set_error(KD_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+  if (base == nullptr || (reinterpret_cast<uintptr_t>(base) & 15u) != 0) return set_error(KD_ERR_ALIGN, "%s: null or not 16-byte aligned", name);
+  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)T, (cuuint64_t)slices};
+  cuuint64_t strides[2] = {(cuuint64_t)D * 4, (cuuint64_t)D * 4 * (cuuint64_t)T};
+  cuuint32_t box[3] = {32, (cuuint32_t)box_rows, 1};
+  cuuint32_t es[3] = {1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(KD_ERR_ARG, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", name, (int)r);
+  return 0;
+}
+
 static int check_device() {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);

@@ -55,6 +55,10 @@ int set_error(int code, const char* fmt, ...);
 int encode_tensor_map(CUtensorMap* out, const kd_tensor& t, int B, int H, int T, int D, int dtype,
                       int box_rows, const char* name);
 
+// 3-D tensor map over a contiguous fp32 (rows, T, D) array with box (32 elements along D, `box_rows` rows of
+// one slice), 128-byte swizzle: the target of the fused backward's bulk reductions of dQ tiles.
+int encode_tensor_map_f32_rows(CUtensorMap* out, float* base, int slices, int T, int D, int box_rows, const char* name);
+
 int launch_classify(const kd_meta& m, void* plan, cudaStream_t stream);
 int launch_mask_dense(const void* plan, int B, int T, uint8_t* out, cudaStream_t stream);
 int launch_attn_fwd(const kd_attn_params& p, cudaStream_t stream);

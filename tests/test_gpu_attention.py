@@ -354,7 +354,7 @@ def test_outlier_inputs_without_hadamard_config3_distribution():
     q, k, v, do = _outlier_inputs(B, H, T, D, dtype, seed=5)
     got = run_op(q, k, v, do, ins, sid, pre, lens)
     mask = ao.dense_mask(T, ins, sid, pre, lens)
-    qc, kc, vc, doc = (x.cpu() for x in (q, k, v, do))
+    qc, kc, vc, doc = (x.detach().cpu() for x in (q, k, v, do))
     ref = ao.attention_fwd_bwd(qc, kc, vc, doc, mask)
     assert_lse_close(got[1], ref[1])
     _check_with_operand_bound("fp32 oracle", got, ref, ao.operand_rounding_bounds(qc, kc, vc, doc, mask, dtype), 1e-4)
