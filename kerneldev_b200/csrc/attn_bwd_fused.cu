@@ -4,25 +4,28 @@
 // worker (original_kernel.py:1173-1336, :1339-1525) and so forms S = Q K^T, dP = dO V^T and the
 // exponentials twice per tile: 7 matrix products and two exponential passes. This kernel is key-tile
 // major like the dK/dV worker and forms them once: per (query tile, key tile)
-//     S^T = K Q^T, dP^T = V dO^T                      (smem x smem -> TMEM)
+//     S^T = K Q^T, dP^T = V dO^T                           (smem x smem -> TMEM, N = 128 queries)
 //     P^T = exp2(S^T c - LSE), dS^T = P^T (dP^T - delta)   (compute warps; 16-bit results)
-//     dV += P^T dO, dK += dS^T Q                      (P^T, dS^T read from TMEM as the A operand)
-//     dQ_tile = dS K                                  (dS^T is also written to shared memory, which the
-//                                                      tensor core reads as an MN-major A operand)
+//     dV += P^T dO                                         (P^T read from TMEM as the A operand)
+//     dK += dS^T Q,  dQ_tile = dS K                        (dS^T written to shared memory once and read by
+//                                                           the tensor core K-major for dK, MN-major for dQ)
 // 5 products and one exponential pass. dK and dV stay in TMEM for the whole key tile; the dQ partial of
 // every tile is added to an fp32 scratch (B,H,T,64) by a TMA bulk reduction (cp.reduce.async.bulk.tensor
 // .add, fp32 adds performed in L2 on whole 128-byte lines; the additions of different key tiles arrive in
 // no fixed order, so dQ is not bit-reproducible from run to run) and a bandwidth-bound kernel converts
 // the scratch to the output dtype afterwards. The delta kernel, which runs first anyway, zeroes the
 // scratch. The dQ tile is staged for the reduction in the shared-memory buffer its own dS^T came from,
-// which the dQ product has finished reading by then.
+// which the products have finished reading by then.
 //
-// 768 threads: warp 0 TMA producer; warp 3 / warp 2 issue S^T / dP^T per 64-query unit (N = 64);
-// warp 1 issues the accumulating products and dQ; warps 4-19 are four compute warpgroups (two per unit,
-// 32 query columns each, as in the two-kernel backward); warps 20-23 move finished dQ tiles from TMEM to
-// global memory. TMEM: two unit buffers (64 columns S^T + 64 columns dP^T each), dK, dV, two dQ buffers.
-// A unit's products keep the tensor pipe busy for about as long as its arithmetic keeps the compute
-// warps, so two unit buffers are enough to overlap them.
+// Pipeline. P^T has its own TMEM columns and dS^T goes to shared memory, so the S^T / dP^T columns are free
+// again as soon as the compute warps have LOADED them: the products of the next tile are issued then and run
+// while the compute warps do this tile's arithmetic, and the accumulating products of this tile run while
+// they work on the next one. Every TMEM region is therefore single-buffered (S^T 128 + dP^T 128 + P^T 64 +
+// dK 64 + dV 64 + dQ 64 = 512 columns); only dS^T in shared memory is double-buffered.
+//
+// 768 threads: warp 0 TMA producer; warp 3 / warp 2 issue S^T / dP^T; warp 1 issues dV, dK and dQ;
+// warps 4-19 are four compute warpgroups (32 query columns each, a key row per thread); warps 20-23 move
+// finished dQ tiles from TMEM to the scratch.
 #include <algorithm>
 
 #include "attn_bwd.cuh"
@@ -32,9 +35,9 @@ namespace kd {
 struct FusedCfg {
   static constexpr int HD = 64;
   static constexpr int TILE_BYTES = KD_TILE * HD * 2;
-  static constexpr int NBUF = 2;                     // unit buffers in TMEM
-  static constexpr int STAGES = 2;                   // ring of streamed (Q, dO) tile pairs
-  static constexpr int NFIX = 2;                     // resident (K, V) pairs: the next head's load while this head runs
+  static constexpr int STAGES = 3;                   // ring of streamed (Q, dO) tile pairs: a stage is held from its TMA load until
+                                                     // the tile's dV and dK products have completed, about two tile periods
+  static constexpr int NFIX = 1;                     // resident (K, V) pair
   static constexpr int SMEM_FIX = 0;
   static constexpr int SMEM_RING = SMEM_FIX + NFIX * 2 * TILE_BYTES;
   static constexpr int SMEM_DS = SMEM_RING + STAGES * 2 * TILE_BYTES;   // 2 x dS^T of a query tile: two [128 keys][64 queries] blocks
@@ -44,8 +47,8 @@ struct FusedCfg {
   static constexpr int SMEM_TOTAL = SMEM_LIST + 128 * 2;
   static constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;
   static constexpr int THREADS = 768;
-  static constexpr uint32_t TM_DK = NBUF * 128, TM_DV = TM_DK + HD, TM_DQ = TM_DV + HD;   // dQ buffer t at TM_DQ + 64 t
-  static_assert(TM_DQ + 2 * HD <= 512, "TMEM budget");
+  static constexpr uint32_t TM_S = 0, TM_DP = 128, TM_PT = 256, TM_DK = 320, TM_DV = 384, TM_DQ = 448;
+  static_assert(TM_DQ + HD <= 512, "TMEM budget");
   static_assert(SMEM_ALLOC <= 232448, "shared memory budget");
   // registers: 80 per thread at launch; light warps release down to 56, the dQ warps to 72, compute warps take 88
   static constexpr int REGS_LIGHT = 56, REGS_DQ = 72, REGS_COMPUTE = 88;
@@ -54,8 +57,8 @@ struct FusedCfg {
 
 enum : uint32_t {
   W_U_FIXFULL = 0x401, W_U_RINGEMPTY = 0x402, W_U_RINGFULL = 0x403, W_U_PFULL = 0x404, W_U_SFULL = 0x405,
-  W_U_ACCFULL = 0x406, W_U_M2ISSUED = 0x407, W_U_FIXEMPTY = 0x408, W_U_ACCFREE = 0x409, W_U_DQFULL = 0x40A,
-  W_U_DQEMPTY = 0x40B, W_U_DSEMPTY = 0x40C,
+  W_U_ACCFULL = 0x406, W_U_SPFREE = 0x407, W_U_FIXEMPTY = 0x408, W_U_ACCFREE = 0x409, W_U_DQFULL = 0x40A,
+  W_U_DQEMPTY = 0x40B, W_U_DSEMPTY = 0x40C, W_U_PTFREE = 0x40D,
 };
 
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
@@ -83,8 +86,8 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   uint16_t* sList = reinterpret_cast<uint16_t*>(smem + C::SMEM_LIST);
 
   __shared__ __align__(8) uint64_t bar_fix_full[C::NFIX], bar_fix_empty[C::NFIX], bar_ring_full[C::STAGES],
-      bar_ring_empty[C::STAGES], bar_s_full[C::NBUF], bar_p_full[C::NBUF], bar_m2_issued[C::NBUF], bar_acc_full, bar_acc_free,
-      bar_dq_full[2], bar_dq_empty[2], bar_ds_empty[2];
+      bar_ring_empty[C::STAGES], bar_s_full, bar_sp_free, bar_p_full, bar_pt_free, bar_acc_full, bar_acc_free,
+      bar_dq_full, bar_dq_empty, bar_ds_empty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ AbortFlag abortf;
 
@@ -104,18 +107,18 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       mbar_init(smem_u32(&bar_ring_full[s]), 1);
       mbar_init(smem_u32(&bar_ring_empty[s]), 1);
     }
-    for (int i = 0; i < C::NBUF; ++i) {
-      mbar_init(smem_u32(&bar_s_full[i]), 2);     // one commit from each of the two M1 issuers
-      mbar_init(smem_u32(&bar_p_full[i]), 256);   // the two warpgroups that share the unit
-      mbar_init(smem_u32(&bar_m2_issued[i]), 1);
-    }
-    for (int t = 0; t < 2; ++t) {
-      mbar_init(smem_u32(&bar_dq_full[t]), 1);
-      mbar_init(smem_u32(&bar_dq_empty[t]), 128);  // the dQ warpgroup has read the buffer
-      mbar_init(smem_u32(&bar_ds_empty[t]), 1);    // the dS^T buffer is free: its dQ product and the reduction staged in it are done
-    }
+    mbar_init(smem_u32(&bar_s_full), 2);       // one commit from each of the two M1 issuers
+    // the warps of a role arrive once each (lane 0, after a warp-wide sync): hundreds of single-thread arrivals on one
+    // barrier would serialise in the shared-memory atomic unit
+    mbar_init(smem_u32(&bar_sp_free), 16);     // every compute warp has loaded its S^T and dP^T columns
+    mbar_init(smem_u32(&bar_p_full), 16);      // P^T is in TMEM and dS^T in shared memory
+    mbar_init(smem_u32(&bar_pt_free), 1);      // the dV product has read P^T
+    mbar_init(smem_u32(&bar_dq_full), 1);
+    mbar_init(smem_u32(&bar_dq_empty), 4);     // the dQ warps have read the dQ tile out of TMEM
+    mbar_init(smem_u32(&bar_ds_empty[0]), 1);  // a dS^T buffer is free: its products and the reduction staged in it are done
+    mbar_init(smem_u32(&bar_ds_empty[1]), 1);
     mbar_init(smem_u32(&bar_acc_full), 1);
-    mbar_init(smem_u32(&bar_acc_free), 512);       // every compute thread has read its part of dK and dV
+    mbar_init(smem_u32(&bar_acc_free), 16);    // every compute warp has read its part of dK and dV
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -170,14 +173,14 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         for (int f = max(0, fix_issued - C::NFIX); f < fix_issued; ++f) drain_wait(smem_u32(&bar_fix_full[f % C::NFIX]), (f / C::NFIX) & 1);
       }
     } else if ((warp == 3 || warp == 2) && lane == 0 && n > 0) {
-      // ---------------- M1 issuers: warp 3: S^T_u = K Q_u^T; warp 2: dP^T_u = V dO_u^T (N = 64 queries) ----------------
+      // ---------------- M1 issuers: warp 3: S^T = K Q^T; warp 2: dP^T = V dO^T (N = 128 queries) ----------------
       const bool dp_part = (warp == 2);
-      const uint32_t idesc_m1 = make_idesc_f16(kBf16, 0, 0, KD_TILE, 64);
+      const uint32_t idesc_m1 = make_idesc_f16(kBf16, 0, 0, KD_TILE, KD_TILE);
       const uint32_t hi = desc_hi_sw128();
       const uint32_t loRingK = desc_lo_kmajor(sRing);
-      const int U = 2 * n;
+      const uint32_t dst = tbase + (dp_part ? C::TM_DP : C::TM_S);
       bool ok = true;
-      int buf = 0, round = 0, stage = 0;   // run on across the heads
+      int t = 0, stage = 0;   // tiles so far and ring stage, running on across the heads
       uint32_t ring_parity = 0;
       for (int hh = 0; hh < nh && ok; ++hh) {
         const int fb = hh % C::NFIX;
@@ -187,45 +190,37 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         uint64_t adesc[HD / 16];
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) adesc[kk] = desc64(loA + koff_kmajor(kk), hi);
-        for (int u = 0; u < U && ok; ++u) {
-          const int i = u & 1;
-          // query rows 64i.. of Q (scores) or dO (dP)
-          const uint32_t blo = loRingK + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4) + (dp_part ? (C::TILE_BYTES >> 4) : 0);
+        for (int e = 0; e < n && ok; ++e) {
+          const uint32_t blo = loRingK + stage * (2 * C::TILE_BYTES >> 4) + (dp_part ? (C::TILE_BYTES >> 4) : 0);   // Q or dO
           uint64_t bdesc[HD / 16];
 #pragma unroll
           for (int kk = 0; kk < HD / 16; ++kk) bdesc[kk] = desc64(blo + koff_kmajor(kk), hi);
-          const uint32_t dst = tbase + buf * 128 + (dp_part ? 64 : 0);
-          if (round > 0) {   // buffer free once the products that read its previous unit have been issued
-            ok = mbar_wait(smem_u32(&bar_m2_issued[buf]), (round - 1) & 1, &abortf, a.status, W_U_M2ISSUED);
+          if (t > 0) {   // the compute warps must have loaded the previous tile's S^T and dP^T
+            ok = mbar_wait(smem_u32(&bar_sp_free), (t - 1) & 1, &abortf, a.status, W_U_SPFREE);
             if (!ok) break;
           }
-          if (i == 0) {      // first unit of a new entry: its Q and dO tiles must have landed
-            ok = mbar_wait(smem_u32(&bar_ring_full[stage]), ring_parity, &abortf, a.status, W_U_RINGFULL);
-            if (!ok) break;
-          }
+          ok = mbar_wait(smem_u32(&bar_ring_full[stage]), ring_parity, &abortf, a.status, W_U_RINGFULL);
+          if (!ok) break;
           tc_fence_after_sync();
           mma_ss64<false>(dst, adesc[0], bdesc[0], idesc_m1);
 #pragma unroll
           for (int kk = 1; kk < HD / 16; ++kk) mma_ss64<true>(dst, adesc[kk], bdesc[kk], idesc_m1);
-          mma_commit(smem_u32(&bar_s_full[buf]));
-          if (++buf == C::NBUF) { buf = 0; ++round; }
-          if (i == 1 && ++stage == C::STAGES) { stage = 0; ring_parity ^= 1; }
+          mma_commit(smem_u32(&bar_s_full));
+          ++t;
+          if (++stage == C::STAGES) { stage = 0; ring_parity ^= 1; }
         }
         if (ok) mma_commit(smem_u32(&bar_fix_empty[fb]));   // this issuer's products of the head no longer read K / V
       }
     } else if (warp == 1 && lane == 0 && n > 0) {
-      // ------- M2 issuer: dV += P^T_u dO_u, dK += dS^T_u Q_u per unit; after a tile's second unit dQ_tile = dS K -------
-      const uint32_t idesc_m2 = make_idesc_f16(kBf16, 0, 1, KD_TILE, HD);   // A from TMEM, B = dO / Q rows, MN-major
-      const uint32_t idesc_m3 = make_idesc_f16(kBf16, 1, 1, KD_TILE, HD);   // A = dS^T in smem read MN-major, B = K rows, MN-major
-      const uint32_t tDK = tbase + C::TM_DK, tDV = tbase + C::TM_DV;
+      // ------- M2 issuer: per tile dV += P^T dO (A from TMEM), dK += dS^T Q and dQ_tile = dS K (A from shared memory) -------
+      const uint32_t idesc_dv = make_idesc_f16(kBf16, 0, 1, KD_TILE, HD);   // B = dO rows, MN-major
+      const uint32_t idesc_dk = make_idesc_f16(kBf16, 0, 1, KD_TILE, HD);   // A = dS^T rows (keys) K-major, B = Q rows, MN-major
+      const uint32_t idesc_dq = make_idesc_f16(kBf16, 1, 1, KD_TILE, HD);   // A = dS^T read MN-major (M = queries), B = K rows, MN-major
+      const uint32_t tDK = tbase + C::TM_DK, tDV = tbase + C::TM_DV, tDQ = tbase + C::TM_DQ, tPT = tbase + C::TM_PT;
       const uint32_t hi = desc_hi_sw128();
       const uint32_t loRingMN = desc_lo_mnmajor(sRing);
-      const uint32_t loDS = desc_lo_mnmajor(sDS);
-      const int U = 2 * n;
       bool ok = true;
-      int buf = 0, stage = 0;
-      uint32_t round_parity = 0;
-      int tcount = 0;   // query tiles finished so far, over all heads
+      int t = 0, stage = 0;
       for (int hh = 0; hh < nh && ok; ++hh) {
         const int fb = hh % C::NFIX;
         const uint32_t loK = desc_lo_mnmajor(sFix + fb * 2 * C::TILE_BYTES);
@@ -233,52 +228,34 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           ok = mbar_wait(smem_u32(&bar_acc_free), (hh - 1) & 1, &abortf, a.status, W_U_ACCFREE);
           if (!ok) break;
         }
-        for (int u = 0; u < U && ok; ++u) {
-          const int i = u & 1;
-          const uint32_t qb = loRingMN + stage * (2 * C::TILE_BYTES >> 4) + i * (64 * 128 >> 4);
+        for (int e = 0; e < n && ok; ++e) {
+          const int tb = t & 1;
+          const uint32_t qb = loRingMN + stage * (2 * C::TILE_BYTES >> 4);
           const uint32_t dob = qb + (C::TILE_BYTES >> 4);
-          const uint32_t aS = tbase + buf * 128;
-          // 16-bit operands: queries 0-31 of the unit at columns [0,16) of their buffer half, queries 32-63 at [32,48)
-          uint64_t bq[4], bdo[4];
-          uint32_t aop[4];
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            bq[kk] = desc64(qb + koff_mnmajor(kk), hi);
-            bdo[kk] = desc64(dob + koff_mnmajor(kk), hi);
-            aop[kk] = aS + (kk >> 1) * 32 + (kk & 1) * 8;
-          }
-          ok = mbar_wait(smem_u32(&bar_p_full[buf]), round_parity, &abortf, a.status, W_U_PFULL);
+          const uint32_t dsK = desc_lo_kmajor(sDS + tb * (2 * C::TILE_BYTES));     // dS^T as [keys][queries]: K-major A of dK
+          const uint32_t dsMN = desc_lo_mnmajor(sDS + tb * (2 * C::TILE_BYTES));   // the same bytes as MN-major A of dQ
+          ok = mbar_wait(smem_u32(&bar_p_full), t & 1, &abortf, a.status, W_U_PFULL);
           if (!ok) break;
           tc_fence_after_sync();
-          mma_ts64_p(tDV, aop[0], bdo[0], idesc_m2, u > 0 ? 1u : 0u);
+          mma_ts_split(tDV, tPT, dob, hi, idesc_dv, e > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 1; kk < 4; ++kk) mma_ts64<true>(tDV, aop[kk], bdo[kk], idesc_m2);
-          mma_ts64_p(tDK, aop[0] + 64, bq[0], idesc_m2, u > 0 ? 1u : 0u);
+          for (int kk = 1; kk < KD_TILE / 16; ++kk) mma_ts_split(tDV, tPT + kk * 8, dob + koff_mnmajor(kk), hi, idesc_dv, 1u);
+          mma_commit(smem_u32(&bar_pt_free));
+          mma_ss_split(tDK, dsK, qb, hi, idesc_dk, e > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 1; kk < 4; ++kk) mma_ts64<true>(tDK, aop[kk] + 64, bq[kk], idesc_m2);
-          if (i == 1) mma_commit(smem_u32(&bar_ring_empty[stage]));
-          tc_fence_before_sync();
-          mbar_arrive(smem_u32(&bar_m2_issued[buf]));
-          if (i == 1) {
-            // both units of the tile have arrived on their P-ready barriers, so dS^T of the whole tile is in shared memory
-            const int tb = tcount & 1;
-            if (tcount >= 2) {   // the dQ warpgroup must have read the buffer's previous tile
-              ok = mbar_wait(smem_u32(&bar_dq_empty[tb]), ((tcount >> 1) - 1) & 1, &abortf, a.status, W_U_DQEMPTY);
-              if (!ok) break;
-              tc_fence_after_sync();
-            }
-            const uint32_t tDQ = tbase + C::TM_DQ + tb * HD;
-            const uint32_t alo = loDS + tb * (2 * C::TILE_BYTES >> 4);
-#ifndef KD_X_NO_DQ
-            mma_ss_split(tDQ, alo, loK, hi, idesc_m3, 0u);
-#pragma unroll
-            for (int kk = 1; kk < KD_TILE / 16; ++kk) mma_ss_split(tDQ, alo + koff_mnmajor(kk), loK + koff_mnmajor(kk), hi, idesc_m3, 1u);
-#endif
-            mma_commit(smem_u32(&bar_dq_full[tb]));
-            ++tcount;
+          for (int kk = 1; kk < KD_TILE / 16; ++kk) mma_ss_split(tDK, dsK + koff_kmajor(kk), qb + koff_mnmajor(kk), hi, idesc_dk, 1u);
+          mma_commit(smem_u32(&bar_ring_empty[stage]));
+          if (t > 0) {   // the dQ warpgroup must have read the previous tile's dQ out of TMEM
+            ok = mbar_wait(smem_u32(&bar_dq_empty), (t - 1) & 1, &abortf, a.status, W_U_DQEMPTY);
+            if (!ok) break;
+            tc_fence_after_sync();
           }
-          if (++buf == C::NBUF) { buf = 0; round_parity ^= 1; }
-          if (i == 1 && ++stage == C::STAGES) stage = 0;
+          mma_ss_split(tDQ, dsMN, loK, hi, idesc_dq, 0u);
+#pragma unroll
+          for (int kk = 1; kk < KD_TILE / 16; ++kk) mma_ss_split(tDQ, dsMN + koff_mnmajor(kk), loK + koff_mnmajor(kk), hi, idesc_dq, 1u);
+          mma_commit(smem_u32(&bar_dq_full));
+          ++t;
+          if (++stage == C::STAGES) stage = 0;
         }
         if (ok) {
           mma_commit(smem_u32(&bar_acc_full));
@@ -289,9 +266,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   } else if (warp < 20) {
     reg_alloc<C::REGS_COMPUTE>();
     // ------------------------------ compute warpgroups ------------------------------
-    const int g = (warp - 4) >> 2;   // warpgroup
-    const int i = g >> 1;            // stream: query half (64 queries) of each query tile
-    const int c0 = g & 1;            // which 32 queries of that half
+    const int g = (warp - 4) >> 2;   // warpgroup = 32 query columns of every tile
     const int wq = warp & 3;
     const int row = wq * 32 + lane;
     const int kj = kt * KD_TILE + row;   // this thread's key
@@ -300,13 +275,12 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     uint32_t* st_buf = sStage + (size_t)(warp - 4) * C::STAGE_WORDS;  // [32 lse][32 delta][32 desc]
     const float c = a.scale_log2;
     const uint32_t kdesc = a.desc[(size_t)b * a.Tpad + kj];
-    const int tbw = 2 * i + c0;      // this thread's word of the 128-bit class masks of a query tile
-    // this thread's 64 bytes of a dS^T block row: 16-byte chunks 4 c0 .. 4 c0 + 3, swizzled with the row
-    const uint32_t ds_row = static_cast<uint32_t>(i) * C::TILE_BYTES + static_cast<uint32_t>(row) * 128u;
+    // this thread's 64 bytes of its key's row in dS^T block g / 2: 16-byte chunks 4 (g % 2) .. + 3, swizzled with the row
+    const uint32_t ds_row = static_cast<uint32_t>(g >> 1) * C::TILE_BYTES + static_cast<uint32_t>(row) * 128u;
     const uint32_t ds_sw = static_cast<uint32_t>(row & 7);
     bool ok = true;
 
-    // LSE, delta and the descriptor of the next unit's queries are fetched one unit ahead into registers
+    // LSE, delta and the descriptor of the next tile's queries are fetched one tile ahead into registers
     // and handed to the warp through its shared-memory staging buffer
     float pre_lse = 0.f, pre_delta = 0.f;
     uint32_t pre_desc = 0u;
@@ -314,15 +288,15 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     auto prefetch = [&](uint32_t entry, int h) {
       if ((entry >> 8) == KD_TILE_PARTIAL) {
         const uint32_t* tbp = a.tilebits + ((size_t)b * a.NT + (entry & 0xFFu)) * 32;
-        tb_pre[0] = tbp[4 * TB_SEES_PRE + tbw];
-        tb_pre[1] = tbp[4 * TB_SEES_CTX + tbw];
-        tb_pre[2] = tbp[4 * TB_SEES_INS + tbw];
-        tb_pre[3] = tbp[4 * TB_CTX + tbw];
-        tb_pre[4] = tbp[4 * TB_SIDPOS + tbw];
+        tb_pre[0] = tbp[4 * TB_SEES_PRE + g];
+        tb_pre[1] = tbp[4 * TB_SEES_CTX + g];
+        tb_pre[2] = tbp[4 * TB_SEES_INS + g];
+        tb_pre[3] = tbp[4 * TB_CTX + g];
+        tb_pre[4] = tbp[4 * TB_SIDPOS + g];
       }
       // a query at or beyond the sequence length reads the last row's scalars: its descriptor is 0,
       // so the tile is PARTIAL and the mask removes it
-      const int q = (entry & 0xFF) * KD_TILE + i * 64 + c0 * 32 + lane;
+      const int q = (entry & 0xFF) * KD_TILE + g * 32 + lane;
       const size_t r = ((size_t)b * a.H + h) * a.T + min(q, a.T - 1);
       pre_lse = a.lse[r];   // negated where it is used: a negation here would wait for the load
       pre_delta = a.delta[r];
@@ -330,11 +304,11 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     };
     uint32_t ent_next = n > 0 ? list[0] : 0u;
     if (n > 0) prefetch(ent_next, h0);
-    int buf = i % C::NBUF;   // this stream's unit u = 2 e + i uses buffer u % NBUF = i, in round e (NBUF = 2)
-    uint32_t rnd = 0;
-    int tcount = 0;
-    const uint32_t sfull0 = smem_u32(&bar_s_full[0]), pfull0 = smem_u32(&bar_p_full[0]);
-    const uint32_t tcol = tbase + lane_base + c0 * 32;   // this thread's 32 columns inside a unit buffer half
+    int t = 0;   // tiles so far, over all heads
+    const uint32_t tS = tbase + lane_base + C::TM_S + g * 32, tP = tbase + lane_base + C::TM_DP + g * 32;
+    const uint32_t tPT = tbase + lane_base + C::TM_PT + g * 16;
+    const uint32_t b_sfull = smem_u32(&bar_s_full), b_spfree = smem_u32(&bar_sp_free), b_pfull = smem_u32(&bar_p_full),
+                   b_ptfree = smem_u32(&bar_pt_free);
 
     for (int hh = 0; hh < nh && ok; ++hh) {
       const int h = h0 + hh;
@@ -348,7 +322,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         __syncwarp();
         uint32_t mk = 0xFFFFFFFFu;   // visibility of this key for the 32 queries
         if (cls == KD_TILE_PARTIAL) {
-          const int i0 = (ent & 0xFF) * KD_TILE + i * 64 + c0 * 32;  // first query handled here
+          const int i0 = (ent & 0xFF) * KD_TILE + g * 32;  // first query handled here
           key_row_mask<1>(kdesc, kj, i0, &tb_pre[0], &tb_pre[1], &tb_pre[2], &tb_pre[3], &mk);
           if (tb_pre[4] != 0u && __any_sync(0xffffffffu, (kdesc & TD_INS) != 0u)) {
             const uint32_t key = span_key_of_key(kdesc);
@@ -368,12 +342,9 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           ent_next = list[0];
           prefetch(ent_next, h + 1);
         }
-        const uint32_t tS = tcol + buf * 128, tP = tS + 64;
-        const int tb = tcount & 1;
+        const int tb = t & 1;
         const uint32_t ds_base = sDS + tb * (2 * C::TILE_BYTES) + ds_row;
-        ok = mbar_wait(sfull0 + buf * 8, rnd & 1u, &abortf, a.status, W_U_SFULL);
-        if (ok && tcount >= 2)   // the dQ product of the tile that used this dS^T buffer before must have completed
-          ok = mbar_wait(smem_u32(&bar_ds_empty[tb]), ((tcount >> 1) - 1) & 1, &abortf, a.status, W_U_DSEMPTY);
+        ok = mbar_wait(b_sfull, t & 1, &abortf, a.status, W_U_SFULL);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
@@ -385,6 +356,11 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           tmem_ld16(tS + hf * 16, rs);
           tmem_ld16(tP + hf * 16, rp);
           tmem_wait_ld();
+          if (hf == 1) {   // both halves are in registers: the next tile's S^T and dP^T may overwrite the columns
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(b_spfree);
+          }
           const uint32_t mh = mk >> (hf * 16);
 #pragma unroll
           for (int j = 0; j < 16; j += 4) {
@@ -406,21 +382,27 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             pk_ds[j / 2] = pack2<kBf16>(ds[0], ds[1]);
             pk_ds[j / 2 + 1] = pack2<kBf16>(ds[2], ds[3]);
           }
-          tmem_st8(tS + hf * 8, pk_p);    // P^T over the start of the scores it was made from
-          tmem_st8(tP + hf * 8, pk_ds);   // dS^T over the start of its dP^T
-          // the same dS^T values as two 16-byte chunks of this key's row of the tile's dS^T block
-          const uint32_t ch = static_cast<uint32_t>(4 * c0 + 2 * hf);
-#ifndef KD_X_NO_DS
+          if (hf == 0) {
+            // P^T and dS^T may leave the registers once the products that read their previous contents are done:
+            // the previous tile's dV, and the dK / dQ / reduction of the tile before that
+            if (t > 0) ok = mbar_wait(b_ptfree, (t - 1) & 1, &abortf, a.status, W_U_PTFREE);
+            if (ok && t >= 2) ok = mbar_wait(smem_u32(&bar_ds_empty[tb]), ((t >> 1) - 1) & 1, &abortf, a.status, W_U_DSEMPTY);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+          }
+          tmem_st8(tPT + hf * 8, pk_p);
+          const uint32_t ch = static_cast<uint32_t>(4 * (g & 1) + 2 * hf);
           st_shared_v4(ds_base + (((ch + 0u) ^ ds_sw) << 4), pk_ds[0], pk_ds[1], pk_ds[2], pk_ds[3]);
           st_shared_v4(ds_base + (((ch + 1u) ^ ds_sw) << 4), pk_ds[4], pk_ds[5], pk_ds[6], pk_ds[7]);
-#endif
         }
-        fence_proxy_async_smem();   // the dQ product reads these shared-memory writes through the async proxy
+        if (!ok) break;
+        fence_proxy_async_smem();   // the dK and dQ products read these shared-memory writes through the async proxy
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(pfull0 + buf * 8);
-        ++rnd;
-        ++tcount;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(b_pfull);
+        ++t;
       }
       if (!ok) break;
 
@@ -439,7 +421,8 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         tmem_ld16(tbase + lane_base + C::TM_DV + g * 16, rv);
         tmem_wait_ld();
         tc_fence_before_sync();
-        mbar_arrive(smem_u32(&bar_acc_free));   // the next head's first products may overwrite the accumulators
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_acc_free));   // the next head's first products may overwrite the accumulators
       } else {
 #pragma unroll
         for (int j = 0; j < 16; ++j) { rk[j] = 0u; rv[j] = 0u; }
@@ -458,21 +441,22 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const uint32_t st_row = static_cast<uint32_t>(row) * 128u, st_sw = static_cast<uint32_t>(row & 7);
     const bool leader = (warp == 20 && lane == 0);
     if (leader) tma_prefetch_desc(&tmAcc);
+    const uint32_t tDQ = tbase + lane_base + C::TM_DQ;
     bool ok = true;
-    int tcount = 0;
+    int t = 0;
     for (int hh = 0; hh < nh && ok; ++hh) {
       const int bh = b * a.H + h0 + hh;
       for (int e = 0; e < n; ++e) {
-        const int tb = tcount & 1;
+        const int tb = t & 1;
         const int q0 = (list[e] & 0xFF) * KD_TILE;
-        ok = mbar_wait(smem_u32(&bar_dq_full[tb]), (tcount >> 1) & 1, &abortf, a.status, W_U_DQFULL);
+        ok = mbar_wait(smem_u32(&bar_dq_full), t & 1, &abortf, a.status, W_U_DQFULL);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
-        // the dQ product was the last reader of this tile's dS^T buffer: its 32 KB now stage the dQ tile as two
-        // [128 rows][32 floats] boxes in the 128-byte-swizzled layout the tensor map expects
+        // The dQ product was the last reader of this tile's dS^T buffer (the dK product was issued before it by the same
+        // thread): its 32 KB now stage the dQ tile as two [128 rows][32 floats] boxes in the 128-byte-swizzled layout the
+        // tensor map expects.
         const uint32_t stage = sDS + tb * (2 * C::TILE_BYTES);
-        const uint32_t tDQ = tbase + lane_base + C::TM_DQ + tb * HD;
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
           uint32_t r[32];
@@ -480,27 +464,24 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           tmem_wait_ld();
           if (hf == 1) {
             tc_fence_before_sync();
-            mbar_arrive(smem_u32(&bar_dq_empty[tb]));   // the product of the tile after next may overwrite the TMEM buffer
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_dq_empty));   // the next tile's dQ product may overwrite the TMEM columns
           }
-#ifndef KD_X_NO_RED
 #pragma unroll
           for (int cch = 0; cch < 8; ++cch)
             st_shared_v4(stage + hf * C::TILE_BYTES + st_row + ((static_cast<uint32_t>(cch) ^ st_sw) << 4), r[4 * cch], r[4 * cch + 1],
                          r[4 * cch + 2], r[4 * cch + 3]);
-#endif
         }
         fence_proxy_async_smem();
         named_bar_sync(1, 128);
         if (leader) {
-#ifndef KD_X_NO_RED
           tma_reduce_add_3d(&tmAcc, stage, 0, q0, bh);
           tma_reduce_add_3d(&tmAcc, stage + C::TILE_BYTES, 32, q0, bh);
           bulk_commit_group();
           bulk_wait_group_read0();
-#endif
           mbar_arrive(smem_u32(&bar_ds_empty[tb]));    // compute warps may write the tile after next's dS^T here
         }
-        ++tcount;
+        ++t;
       }
     }
     if (leader) bulk_wait_group0();
