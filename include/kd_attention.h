@@ -17,7 +17,9 @@
  *    reported through the 32-bit status word at plan offset `off_status`; it stays 0 on success.
  *  - Tensors are (B, H, T, D) with arbitrary element strides for b, h and t and unit stride
  *    along D; base pointers and the byte strides must be multiples of 16.
- *  - dtype: KD_F16 or KD_BF16; D: 64 or 128.
+ *  - dtype: KD_F16 or KD_BF16; D: a multiple of 16 from 16 to 128 (the reference accepts 16, 32, 64, 128 and
+ *    256, original_kernel.py:1720). Head dims below 64 run on the 64-wide kernels and those from 80 to 112 on
+ *    the 128-wide ones: TMA fills the missing tile columns with zeros, which changes no product.
  */
 #ifndef KD_ATTENTION_H_
 #define KD_ATTENTION_H_

@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const BwdArgs a) {
     const size_t r = base + threadIdx.x / TPR;
     const bool live = r < rows;
     float acc = 0.f;
-    if (live) {
+    if (live && sub * 8 < a.d_real) {
       const int t = static_cast<int>(r % a.T);
       const int h = static_cast<int>((r / a.T) % a.H);
       const int b = static_cast<int>(r / ((size_t)a.T * a.H));
@@ -148,11 +148,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     for (int i = 0; i < C::NBUF; ++i) {
       mbar_init(smem_u32(&bar_s_full[i]), 2);     // one commit from each of the two M1 issuers
-      mbar_init(smem_u32(&bar_p_full[i]), 128 * C::NSUB);   // the warpgroups that share the unit
+      mbar_init(smem_u32(&bar_p_full[i]), 4 * C::NSUB);   // one arrival per warp of the warpgroups that share the unit
       mbar_init(smem_u32(&bar_m2_issued[i]), 1);
     }
     mbar_init(smem_u32(&bar_acc_full), 1);
-    mbar_init(smem_u32(&bar_acc_free), 256 * C::NSUB);      // every compute thread has read its part of dQ
+    mbar_init(smem_u32(&bar_acc_free), 8 * C::NSUB);      // every compute warp has read its part of dQ
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -430,7 +430,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(pfull0 + buf * 8);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(pfull0 + buf * 8);
         buf += 2;
         if (buf >= C::NBUF) { buf -= C::NBUF; ++rnd; }
       }
@@ -455,7 +456,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         tmem_wait_ld();
         tc_fence_before_sync();
-        mbar_arrive(smem_u32(&bar_acc_free));   // the next head's first product may overwrite the accumulator
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_acc_free));   // the next head's first product may overwrite the accumulator
       } else {
 #pragma unroll
         for (int cb = 0; cb < EC / ECH; ++cb)
@@ -465,8 +467,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (q_valid) {
 #pragma unroll
         for (int cb = 0; cb < EC / ECH; ++cb) {
-          if constexpr (ECH == 16) store_row16<kBf16>(drow + cb * ECH, r[cb], a.sm_scale);
-          else store_row32<kBf16>(drow + cb * ECH, r[cb], a.sm_scale);
+          if constexpr (ECH == 16) store_row16_upto<kBf16>(drow + cb * ECH, r[cb], a.sm_scale, g * EC + cb * ECH, a.d_real);
+          else store_row32_upto<kBf16>(drow + cb * ECH, r[cb], a.sm_scale, g * EC + cb * ECH, a.d_real);
         }
       }
     }
@@ -518,11 +520,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
     for (int i = 0; i < C::NBUF; ++i) {
       mbar_init(smem_u32(&bar_s_full[i]), 2);     // one commit from each of the two M1 issuers
-      mbar_init(smem_u32(&bar_p_full[i]), 128 * C::NSUB);   // the warpgroups that share the unit
+      mbar_init(smem_u32(&bar_p_full[i]), 4 * C::NSUB);   // one arrival per warp of the warpgroups that share the unit
       mbar_init(smem_u32(&bar_m2_issued[i]), 1);
     }
     mbar_init(smem_u32(&bar_acc_full), 1);
-    mbar_init(smem_u32(&bar_acc_free), 256 * C::NSUB);      // every compute thread has read its part of dK and dV
+    mbar_init(smem_u32(&bar_acc_free), 8 * C::NSUB);      // every compute warp has read its part of dK and dV
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -833,7 +835,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(pfull0 + buf * 8);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(pfull0 + buf * 8);
         buf += 2;
         if (buf >= C::NBUF) { buf -= C::NBUF; ++rnd; }
       }
@@ -864,7 +867,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           tmem_wait_ld();
           if (cb == EC / ECH - 1) {
             tc_fence_before_sync();
-            mbar_arrive(smem_u32(&bar_acc_free));   // the next head's first products may overwrite the accumulators
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_acc_free));   // the next head's first products may overwrite the accumulators
           }
         } else {
 #pragma unroll
@@ -872,11 +876,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         if (k_valid) {
           if constexpr (ECH == 16) {
-            store_row16<kBf16>(krow + cb * ECH, rk, a.sm_scale);
-            store_row16<kBf16>(vrow + cb * ECH, rv, 1.0f);
+            store_row16_upto<kBf16>(krow + cb * ECH, rk, a.sm_scale, g * EC + cb * ECH, a.d_real);
+            store_row16_upto<kBf16>(vrow + cb * ECH, rv, 1.0f, g * EC + cb * ECH, a.d_real);
           } else {
-            store_row32<kBf16>(krow + cb * ECH, rk, a.sm_scale);
-            store_row32<kBf16>(vrow + cb * ECH, rv, 1.0f);
+            store_row32_upto<kBf16>(krow + cb * ECH, rk, a.sm_scale, g * EC + cb * ECH, a.d_real);
+            store_row32_upto<kBf16>(vrow + cb * ECH, rv, 1.0f, g * EC + cb * ECH, a.d_real);
           }
         }
       }
@@ -899,6 +903,7 @@ static int launch_bwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
   if ((rc = encode_tensor_map(&tmDO, p.d_o, p.B, p.H, p.T, p.D, p.dtype, KD_TILE, "do")) != 0) return rc;
   BwdArgs a;
   a.B = p.B; a.H = p.H; a.T = p.T; a.NT = L.NT; a.NP = L.NP; a.Tpad = L.NT * KD_TILE;
+  a.d_real = p.D;
   a.scale_log2 = p.sm_scale * 1.4426950408889634f;
   a.sm_scale = p.sm_scale;
   a.G = heads_per_cta(p.B, p.H, L.NT, p.heads_per_cta);
@@ -986,9 +991,8 @@ int launch_attn_bwd(const kd_attn_params& p, cudaStream_t stream) {
   if (kd_plan_layout_get(p.B, p.T, &L) != 0) return KD_ERR_ARG;
   PlanView pv = make_plan_view(const_cast<void*>(p.plan), L);
   if (!p.d_o.ptr) return set_error(KD_ERR_ARG, "d_o is null");
-  if (p.D == 64) return p.dtype == KD_BF16 ? launch_bwd_t<64, true>(p, L, pv, stream) : launch_bwd_t<64, false>(p, L, pv, stream);
-  if (p.D == 128) return p.dtype == KD_BF16 ? launch_bwd_t<128, true>(p, L, pv, stream) : launch_bwd_t<128, false>(p, L, pv, stream);
-  return set_error(KD_ERR_ARG, "head dim %d not supported (64 or 128)", p.D);
+  if (p.D <= 64) return p.dtype == KD_BF16 ? launch_bwd_t<64, true>(p, L, pv, stream) : launch_bwd_t<64, false>(p, L, pv, stream);
+  return p.dtype == KD_BF16 ? launch_bwd_t<128, true>(p, L, pv, stream) : launch_bwd_t<128, false>(p, L, pv, stream);
 }
 
 }  // namespace kd

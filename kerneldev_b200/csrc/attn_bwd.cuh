@@ -7,6 +7,7 @@ namespace kd {
 struct BwdArgs {
   int B, H, T, NT, NP, Tpad;
   int G;             // heads per CTA
+  int d_real;        // head dim of the tensors (a multiple of 16, <= HD); TMA zero-fills the tile columns beyond it
   float scale_log2;  // sm_scale * log2(e)
   float sm_scale;
   const uint32_t* desc;

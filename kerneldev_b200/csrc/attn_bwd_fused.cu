@@ -428,8 +428,8 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         for (int j = 0; j < 16; ++j) { rk[j] = 0u; rv[j] = 0u; }
       }
       if (k_valid) {
-        store_row16<kBf16>(krow, rk, a.sm_scale);
-        store_row16<kBf16>(vrow, rv, 1.0f);
+        store_row16_upto<kBf16>(krow, rk, a.sm_scale, g * 16, a.d_real);
+        store_row16_upto<kBf16>(vrow, rv, 1.0f, g * 16, a.d_real);
       }
     }
   } else {
@@ -502,6 +502,7 @@ __global__ void __launch_bounds__(256) attn_bwd_dq_convert_kernel(const BwdArgs 
     const int t = static_cast<int>(r % a.T);
     const int h = static_cast<int>((r / a.T) % a.H);
     const int b = static_cast<int>(r / ((size_t)a.T * a.H));
+    if (sub * 8 >= a.d_real) continue;
     const float4* src = reinterpret_cast<const float4*>(a.dq_acc + r * HD + sub * 8);
     const float4 x = src[0], y = src[1];
     uint4 v;

@@ -129,6 +129,29 @@ __device__ __forceinline__ void store_row16(uint16_t* dst, const uint32_t (&r)[1
   }
 }
 
+// 32 (or 16) accumulator columns starting at column `col` of a row whose real width is d_real (a multiple
+// of 16): the columns at or beyond d_real belong to the zero-filled part of a tile and are not stored.
+template <bool kBf16>
+__device__ __forceinline__ void store_row32_upto(uint16_t* dst, const uint32_t (&r)[32], float f, int col, int d_real) {
+  if (col + 32 <= d_real) {
+    store_row32<kBf16>(dst, r, f);
+  } else if (col < d_real) {   // 16 columns left
+#pragma unroll
+    for (int j = 0; j < 16; j += 8) {
+      uint4 v;
+      v.x = pack2<kBf16>(__uint_as_float(r[j + 0]) * f, __uint_as_float(r[j + 1]) * f);
+      v.y = pack2<kBf16>(__uint_as_float(r[j + 2]) * f, __uint_as_float(r[j + 3]) * f);
+      v.z = pack2<kBf16>(__uint_as_float(r[j + 4]) * f, __uint_as_float(r[j + 5]) * f);
+      v.w = pack2<kBf16>(__uint_as_float(r[j + 6]) * f, __uint_as_float(r[j + 7]) * f);
+      *reinterpret_cast<uint4*>(dst + j) = v;
+    }
+  }
+}
+template <bool kBf16>
+__device__ __forceinline__ void store_row16_upto(uint16_t* dst, const uint32_t (&r)[16], float f, int col, int d_real) {
+  if (col < d_real) store_row16<kBf16>(dst, r, f);
+}
+
 // Heads a CTA handles one after the other (they share the plan's work list, so the list staging,
 // the TMEM allocation and the pipeline fill are paid once): as many as keeps about per_sm CTAs per SM,
 // at most g_max (the longest-first dispatch order keeps the SMs balanced with that few). Measured

@@ -33,6 +33,7 @@ namespace kd {
 struct FwdArgs {
   int B, H, T, NT, NP, Tpad;
   int G;             // heads handled one after the other by a CTA (they share the pair's work list)
+  int d_real;        // head dim of the tensors (a multiple of 16, <= HD); TMA zero-fills the tile columns beyond it
   float scale_log2;  // sm_scale * log2(e)
   const uint32_t* desc;
   const uint32_t* tilebits;   // [B][NT][8][4] class masks of every 128-token tile
@@ -143,13 +144,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // phase of the barriers it waits on, which is what makes a parity wait sound
       mbar_init(smem_u32(&bar_s_full[2 * s]), 1);
       mbar_init(smem_u32(&bar_s_full[2 * s + 1]), 1);
-      mbar_init(smem_u32(&bar_p_full[s]), 128);
+      mbar_init(smem_u32(&bar_p_full[s]), 4);   // one arrival per softmax warp (lane 0, after a warp-wide sync)
       mbar_init(smem_u32(&bar_pv_issued[s]), 1);
     }
     mbar_init(smem_u32(&bar_pv_done[0]), 1);
     mbar_init(smem_u32(&bar_pv_done[1]), 1);
-    mbar_init(smem_u32(&bar_o_free[0]), 128);
-    mbar_init(smem_u32(&bar_o_free[1]), 128);
+    mbar_init(smem_u32(&bar_o_free[0]), 4);
+    mbar_init(smem_u32(&bar_o_free[1]), 4);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -590,7 +591,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(smem_u32(&bar_p_full[buf]));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_p_full[buf]));
       ++nact;
       ++pv_seen;
     }
@@ -623,9 +625,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (cb == HD / 32 - 1 && nact > 0) {
           // this thread's share of O_i has been read out: the next head's first product may overwrite it
           tc_fence_before_sync();
-          mbar_arrive(smem_u32(&bar_o_free[i]));
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bar_o_free[i]));
         }
-        if (tile_valid && qi < a.T) store_row32<kBf16>(orow + cb * 32, r, inv_l);
+        if (tile_valid && qi < a.T) store_row32_upto<kBf16>(orow + cb * 32, r, inv_l, cb * 32, a.d_real);
       }
     }
     }  // heads
@@ -646,6 +649,7 @@ static int launch_fwd_t(const kd_attn_params& p, const kd_plan_layout& L, const 
   if ((rc = encode_tensor_map(&tmV, p.v, p.B, p.H, p.T, p.D, p.dtype, KD_TILE, "v")) != 0) return rc;
   FwdArgs a;
   a.B = p.B; a.H = p.H; a.T = p.T; a.NT = L.NT; a.NP = L.NP; a.Tpad = L.NT * KD_TILE;
+  a.d_real = p.D;
   a.scale_log2 = p.sm_scale * 1.4426950408889634f;
   a.G = heads_per_cta(p.B, p.H, L.NP, p.heads_per_cta, 3, 4);
   a.desc = pv.desc; a.fwd_cnt = pv.fwd_cnt; a.fwd_list = pv.fwd_list; a.status = pv.status;
@@ -670,9 +674,9 @@ int launch_attn_fwd(const kd_attn_params& p, cudaStream_t stream) {
   kd_plan_layout L;
   if (kd_plan_layout_get(p.B, p.T, &L) != 0) return KD_ERR_ARG;
   PlanView pv = make_plan_view(const_cast<void*>(p.plan), L);
-  if (p.D == 64) return p.dtype == KD_BF16 ? launch_fwd_t<64, true>(p, L, pv, stream) : launch_fwd_t<64, false>(p, L, pv, stream);
-  if (p.D == 128) return p.dtype == KD_BF16 ? launch_fwd_t<128, true>(p, L, pv, stream) : launch_fwd_t<128, false>(p, L, pv, stream);
-  return set_error(KD_ERR_ARG, "head dim %d not supported (64 or 128)", p.D);
+  // head dims below the tile width run on the next wider instantiation: TMA zero-fills the missing columns
+  if (p.D <= 64) return p.dtype == KD_BF16 ? launch_fwd_t<64, true>(p, L, pv, stream) : launch_fwd_t<64, false>(p, L, pv, stream);
+  return p.dtype == KD_BF16 ? launch_fwd_t<128, true>(p, L, pv, stream) : launch_fwd_t<128, false>(p, L, pv, stream);
 }
 
 }  // namespace kd

@@ -47,6 +47,8 @@ int encode_tensor_map(CUtensorMap* out, const kd_tensor& t, int B, int H, int T,
   if (st <= 0 || (st & 15) || (H > 1 && (sh <= 0 || (sh & 15))) || (B > 1 && (sb <= 0 || (sb & 15))))
     return set_error(KD_ERR_ALIGN, "tensor %s: byte strides (%lld, %lld, %lld) must be positive multiples of 16",
                      name, (long long)sb, (long long)sh, (long long)st);
+  // the box is 64 elements wide whatever D is: for D < 64 (or the second box of 64 < D < 128) the elements
+  // beyond the tensor are filled with zeros, which leaves every product of the kernels unchanged
   cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)T, (cuuint64_t)H, (cuuint64_t)B};
   // a stride of a size-1 dimension is never used for addressing but must still be valid
   cuuint64_t strides[3] = {(cuuint64_t)st, (cuuint64_t)(H > 1 ? sh : st * T), (cuuint64_t)(B > 1 ? sb : (H > 1 ? sh * H : st * T))};
@@ -92,7 +94,7 @@ static int check_device() {
 static int check_attn(const kd_attn_params* p, bool backward) {
   if (!p) return set_error(KD_ERR_ARG, "params is null");
   if (p->B < 1 || p->H < 1 || p->T < 1) return set_error(KD_ERR_ARG, "bad shape B=%d H=%d T=%d", p->B, p->H, p->T);
-  if (p->D != 64 && p->D != 128) return set_error(KD_ERR_ARG, "head dim %d not supported (64 or 128)", p->D);
+  if (p->D < 16 || p->D > 128 || (p->D % 16) != 0) return set_error(KD_ERR_ARG, "head dim %d not supported (a multiple of 16 from 16 to 128)", p->D);
   if (p->dtype != KD_F16 && p->dtype != KD_BF16) return set_error(KD_ERR_ARG, "dtype %d not supported (fp16 or bf16)", p->dtype);
   if (p->T > 128 * KD_TILE) return set_error(KD_ERR_LIMIT, "T=%d exceeds the maximum of %d tokens", p->T, 128 * KD_TILE);
   if (p->H > 65535 || p->B > 65535) return set_error(KD_ERR_LIMIT, "B and H must not exceed 65535");
@@ -107,7 +109,7 @@ static int check_attn(const kd_attn_params* p, bool backward) {
     if (!p->delta) return set_error(KD_ERR_ARG, "delta scratch is null");
     if (p->bwd_mode != KD_BWD_SPLIT && p->bwd_mode != KD_BWD_FUSED) return set_error(KD_ERR_ARG, "bwd_mode %d unknown", p->bwd_mode);
     if (p->bwd_mode == KD_BWD_FUSED) {
-      if (p->D != 64) return set_error(KD_ERR_ARG, "the fused backward (KD_BWD_FUSED) supports head dim 64 only, got %d", p->D);
+      if (p->D > 64) return set_error(KD_ERR_ARG, "the fused backward (KD_BWD_FUSED) supports head dims up to 64 only, got %d", p->D);
       if (!p->dq_acc || (reinterpret_cast<uintptr_t>(p->dq_acc) & 15u)) return set_error(KD_ERR_ARG, "dq_acc scratch is null or not 16-byte aligned");
     }
     const kd_tensor* outs[3] = {&p->dq, &p->dk, &p->dv};
@@ -210,7 +212,8 @@ int kd_workspace_bytes(int32_t B, int32_t H, int32_t T, int32_t D, size_t* bytes
 
 int kd_workspace_bytes_fused(int32_t B, int32_t H, int32_t T, int32_t D, size_t* bytes) {
   if (!bytes || B < 1 || H < 1 || T < 1 || D < 1) return set_error(KD_ERR_ARG, "bad workspace query");
-  *bytes = (size_t)B * H * T * D * sizeof(float);
+  (void)D;   // rows of the scratch are as wide as the kernel's tile (64 columns) whatever the head dim
+  *bytes = (size_t)B * H * T * 64 * sizeof(float);
   return 0;
 }
 
@@ -218,7 +221,7 @@ int kd_hadamard(const kd_tensor* x, const kd_tensor* y, int32_t B, int32_t H, in
                 int32_t dtype, const float* signs, int32_t inverse, void* stream) {
   if (!x || !x->ptr || !y || !y->ptr) return set_error(KD_ERR_ARG, "x / y is null");
   if (B < 1 || H < 1 || T < 1) return set_error(KD_ERR_ARG, "bad shape B=%d H=%d T=%d", B, H, T);
-  if (D != 64 && D != 128) return set_error(KD_ERR_ARG, "head dim %d not supported (64 or 128)", D);
+  if (D != 16 && D != 32 && D != 64 && D != 128) return set_error(KD_ERR_ARG, "head dim %d not supported (16, 32, 64 or 128)", D);
   if (dtype != KD_F16 && dtype != KD_BF16) return set_error(KD_ERR_ARG, "dtype %d not supported", dtype);
   if ((reinterpret_cast<uintptr_t>(x->ptr) & 15u) || ((x->stride_t * 2) & 15) || ((x->stride_h * 2) & 15) || ((x->stride_b * 2) & 15))
     return set_error(KD_ERR_ALIGN, "x: pointer and byte strides must be multiples of 16");

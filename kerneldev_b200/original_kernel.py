@@ -13,7 +13,8 @@ Differences from the reference, all deliberate:
     metadata is given (original_kernel.py:1202-1204, :1368-1371);
   * a query row that sees no key gets O = 0, LSE = -inf and no gradient (the reference's default
     path produces NaN there, original_kernel.py:554-561);
-  * CUDA sm_100 only, fp16 / bf16, head_dim 64 or 128. There is no Triton, no autotuning and no
+  * CUDA sm_100 only, fp16 / bf16, head_dim a multiple of 16 up to 128 (the reference also takes 256 and
+    fp32 tensors). There is no Triton, no autotuning and no
     CPU path: unsupported inputs raise.
 ``autotune``, ``prescale_qk`` and ``precision`` are accepted and ignored.
 """
@@ -60,9 +61,9 @@ def _check_inputs(q, k, v):
     if not q.is_cuda:
         raise RuntimeError("flash_attention runs on CUDA sm_100 devices only; there is no CPU path")
     if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
-        raise ValueError("q, k, v must share dtype float16 or bfloat16")
-    if q.shape[-1] not in (64, 128):
-        raise ValueError(f"head_dim {q.shape[-1]} is not supported (64 or 128)")
+        raise ValueError("q, k, v must share dtype float16, bfloat16 or float32")
+    if q.shape[-1] % 16 != 0 or not 16 <= q.shape[-1] <= 128:
+        raise ValueError(f"head_dim {q.shape[-1]} is not supported (a multiple of 16 from 16 to 128)")
     if not (k.device == q.device and v.device == q.device):
         raise ValueError("q, k, v must be on the same device")
 
@@ -110,7 +111,7 @@ def _backward(q, k, v, o, lse, d_o, plan: AttentionPlan, sm_scale: float, phases
               like_input: bool = False, deterministic: bool = False):
     """One kd_attn_bwd call: returns (dQ, dK, dV). ``phases`` selects a part of the backward (see
     kd_attn_params.bwd_phases); ``bufs`` = (dq, dk, dv, delta[, dq_acc]) reuses buffers.
-    ``deterministic=False`` selects the fused backward where it exists (head_dim 64): one pass over the
+    ``deterministic=False`` selects the fused backward where it exists (head_dim <= 64): one pass over the
     tiles instead of two, dQ accumulated with fp32 atomics in a (B,H,T,D) scratch."""
     q, k, v, d_o = _usable(q), _usable(k), _usable(v), _usable(d_o)
     B, H, T, D = q.shape
@@ -126,9 +127,9 @@ def _backward(q, k, v, o, lse, d_o, plan: AttentionPlan, sm_scale: float, phases
     else:
         dq, dk, dv, delta = bufs[:4]
         dq_acc = bufs[4] if len(bufs) > 4 else None
-    fused = (not deterministic) and D == 64
-    if fused and dq_acc is None:
-        dq_acc = torch.empty((B, H, T, D), dtype=torch.float32, device=q.device)
+    fused = (not deterministic) and D <= 64
+    if fused and dq_acc is None:   # rows as wide as the kernel's tile (kd_workspace_bytes_fused)
+        dq_acc = torch.empty((B, H, T, 64), dtype=torch.float32, device=q.device)
     p = _params(q, k, v, o, lse, plan, sm_scale)
     p.d_o = _kd_tensor(d_o)
     p.dq, p.dk, p.dv = _kd_tensor(dq), _kd_tensor(dk), _kd_tensor(dv)
@@ -204,8 +205,8 @@ def generate_hadamard_signs(n_heads: int, head_dim: int, seed: int = 0, device="
 def hadamard_transform(x: torch.Tensor, signs: torch.Tensor | None = None) -> torch.Tensor:
     """``WHT(x * signs[h]) / sqrt(D)`` over the last dimension of a (B, H, T, D) tensor, with the
     Walsh-Hadamard matrix in natural (Sylvester) order; differentiable."""
-    if x.dim() != 4 or x.shape[-1] not in (64, 128) or x.dtype not in _DTYPES or not x.is_cuda:
-        raise ValueError("hadamard_transform expects a CUDA (B, H, T, D) fp16/bf16 tensor with D in {64, 128}")
+    if x.dim() != 4 or x.shape[-1] not in (16, 32, 64, 128) or x.dtype not in _DTYPES or not x.is_cuda:
+        raise ValueError("hadamard_transform expects a CUDA (B, H, T, D) fp16/bf16 tensor with D in {16, 32, 64, 128}")
     if signs is not None:
         if signs.shape != (x.shape[1], x.shape[3]):
             raise ValueError("signs must have shape (heads, head_dim)")
@@ -250,11 +251,29 @@ def flash_attention(
     of (B,T,H,D) memory (model.py:76-78) the ``transpose(1, 2).contiguous()`` after the call
     (model.py:95) and its counterpart in the backward then copy nothing. The drop-in module uses it.
     deterministic (extension, default False): True forces the two-kernel backward, whose results are
-    bit-identical from run to run; by default head_dim 64 takes the fused backward, which forms S and dP
+    bit-identical from run to run; by default head_dim <= 64 takes the fused backward, which forms S and dP
     once per tile and adds dQ partials with fp32 atomics (dQ then varies in its last bits between runs).
+
+    float32 q, k, v (the reference's default ``precision="tf32"`` path, original_kernel.py:2106): the tensors
+    are rounded to float16 operands -- the 10-bit mantissa tf32 keeps -- the products accumulate in fp32 as
+    everywhere, and O and the gradients come back as float32. Values must lie inside float16's range
+    (|x| < 65504; tf32 keeps fp32's exponent). ``precision="ieee"`` with float32 tensors is not supported.
 
     Returns O, or (O, LSE) with return_lse, or (that, mask[B,H,T,T] bool) with return_attention_mask.
     """
+    if q.dtype is torch.float32 and k.dtype is torch.float32 and v.dtype is torch.float32:
+        if precision == "ieee":
+            raise ValueError("float32 inputs with precision='ieee' are not supported: the tensor cores take 16-bit operands here "
+                             "(precision='tf32' rounds the operands to tf32's 10-bit mantissa)")
+        res = flash_attention(q.to(torch.float16), k.to(torch.float16), v.to(torch.float16), lens, sm_scale, causal, autotune,
+                              return_lse, prescale_qk, precision, attention_mask, in_span, span_id, is_prefix,
+                              return_attention_mask, hadamard_signs, out_layout, deterministic)
+        widen = lambda x: x.to(torch.float32) if torch.is_tensor(x) and x.dtype is torch.float16 else x
+        if return_attention_mask:
+            first, mask = res
+            first = tuple(widen(x) for x in first) if isinstance(first, tuple) else widen(first)
+            return first, mask
+        return tuple(widen(x) for x in res) if isinstance(res, tuple) else widen(res)
     _check_inputs(q, k, v)
     B, H, T, D = q.shape
     if sm_scale is None:

@@ -197,9 +197,14 @@ def test_unsupported_inputs_raise():
     from kerneldev_b200 import flash_attention
     q = torch.randn(1, 1, 128, 64, device=DEV, dtype=torch.bfloat16)
     with pytest.raises(ValueError):
-        flash_attention(q.float(), q.float(), q.float())
+        flash_attention(q.float(), q.float(), q.float(), precision="ieee")
     with pytest.raises(ValueError):
-        flash_attention(q[..., :32], q[..., :32], q[..., :32])
+        flash_attention(q.float(), q, q)   # mixed dtypes
+    with pytest.raises(ValueError):
+        flash_attention(q[..., :24], q[..., :24], q[..., :24])   # head dim not a multiple of 16
+    q256 = torch.randn(1, 1, 128, 256, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        flash_attention(q256, q256, q256)
     with pytest.raises(ValueError):
         flash_attention(q, q, q, sm_scale=-1.0)
     with pytest.raises(ValueError):
@@ -541,3 +546,60 @@ def test_fused_backward_full_size_config2():
         mask = ao.dense_mask(T, ins[b:b + 1], sid[b:b + 1], pre[b:b + 1], lens[b:b + 1])
         sl = lambda x: x[b:b + 1, h:h + 1].cpu()
         compare(sl(q), sl(k), sl(v), sl(do), mask, tuple(x[b:b + 1, h:h + 1].contiguous() for x in got))
+
+
+@pytest.mark.parametrize("D,dtype", [(32, torch.bfloat16), (16, torch.float16), (48, torch.bfloat16), (96, torch.float16), (112, torch.bfloat16)])
+@pytest.mark.parametrize("deterministic", [False, True])
+def test_head_dims_below_the_tile_width(D, dtype, deterministic):
+    """The reference takes head dims 16, 32, 64, 128 and 256 (original_kernel.py:1720). Dims that are not 64 or
+    128 run on the next wider kernels with the missing tile columns zero-filled by TMA; outputs have the real
+    width. Both backward forms where they exist (fused for D <= 64)."""
+    B, H, T = 2, 3, 333
+    ins, sid, pre = random_meta(D, B, T)
+    lens = np.array([T, T - 50], np.int32)
+    q, k, v, do = rand_inputs(B, H, T, D, dtype, seed=D)
+    got = run_op(q, k, v, do, ins, sid, pre, lens, deterministic=deterministic)
+    assert got[0].shape == (B, H, T, D) and got[2].shape == (B, H, T, D)
+    compare(q, k, v, do, ao.dense_mask(T, ins, sid, pre, lens), got)
+
+
+def test_hadamard_path_head_dim_32():
+    from kerneldev_b200 import generate_hadamard_signs
+    B, H, T, D, dtype = 1, 2, 300, 32, torch.bfloat16
+    signs = generate_hadamard_signs(H, D, seed=1, device=DEV)
+    q, k, v, do = rand_inputs(B, H, T, D, dtype, seed=32)
+    got = run_op(q, k, v, do, hadamard_signs=signs)
+    compare(q, k, v, do, ao.dense_mask(T, causal=True), got)
+
+
+@pytest.mark.parametrize("D", [64, 32, 128])
+def test_float32_inputs_with_tf32_class_operands(D):
+    """float32 tensors with the reference's default precision="tf32": operands rounded to a 10-bit mantissa (here as
+    float16), fp32 accumulation, float32 outputs and gradients; against the fp32 oracle at the 16-bit tolerance."""
+    from kerneldev_b200 import flash_attention
+    B, H, T = 2, 2, 300
+    ins, sid, pre = random_meta(5 + D, B, T)
+    q, k, v, do = rand_inputs(B, H, T, D, torch.float32, seed=D + 1)
+    qg, kg, vg = (x.to(DEV).requires_grad_() for x in (q, k, v))
+    o, lse = flash_attention(qg, kg, vg, return_lse=True, in_span=_t(ins, torch.bool), span_id=_t(sid, torch.int64), is_prefix=_t(pre, torch.bool))
+    o.backward(do.to(DEV))
+    assert o.dtype == torch.float32 and qg.grad.dtype == torch.float32 and lse.dtype == torch.float32
+    ro, rlse, rdq, rdk, rdv = ao.attention_fwd_bwd(q, k, v, do, ao.dense_mask(T, ins, sid, pre))
+    assert_lse_close(lse, rlse)
+    for nm, g, r in (("O", o, ro), ("dQ", qg.grad, rdq), ("dK", kg.grad, rdk), ("dV", vg.grad, rdv)):
+        assert_close(nm, g, r)
+
+
+def test_growing_sequence_as_generate_calls_it():
+    """GPTModel.generate has no KV cache: it calls the model on the whole sequence after every new token
+    (model.py:316-355), so the operator sees T, T+1, T+2, ... with T_q = T_k each time, a new plan per length, most
+    lengths not a multiple of the tile. The last row's output is what the next token is sampled from."""
+    from kerneldev_b200 import flash_attention
+    B, H, D = 1, 4, 64
+    g = torch.Generator().manual_seed(9)
+    full = [torch.randn((B, H, 140, D), generator=g).to(torch.bfloat16) for _ in range(3)]
+    for T in (1, 2, 5, 127, 128, 129, 130, 140):
+        q, k, v = (x[:, :, :T].contiguous() for x in full)
+        o = flash_attention(q.to(DEV), k.to(DEV), v.to(DEV), causal=True)
+        ro, _ = ao.attention_forward(q, k, v, ao.dense_mask(T, causal=True))
+        assert_close(f"O at T={T}", o, ro)

@@ -46,7 +46,7 @@ def test_entry_points_reject_bad_arguments_before_touching_cuda():
     from kerneldev_b200 import _capi
     lib = _capi.load()
     p = _capi.KdAttnParams()
-    p.B, p.H, p.T, p.D = 1, 1, 128, 32          # unsupported head dim
+    p.B, p.H, p.T, p.D = 1, 1, 128, 256         # unsupported head dim
     p.dtype, p.sm_scale = _capi.KD_BF16, 0.1
     assert lib.kd_attn_fwd(ctypes.byref(p), None) == -1
     assert b"head dim" in lib.kd_last_error()
