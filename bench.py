@@ -433,7 +433,7 @@ def run_ours(args, cfg):
         roofline["dq_accumulate"] = {
             "reduce_bytes_per_launch": red_bytes, "GBps": red_bytes / (ms_f * 1e-3) / 1e9,
             "hbm_peak_GBps": peak_hbm,
-            "note": "fp32 red.global.add traffic of the dQ partials over the fused kernel's time; it is served by L2, "
+            "note": "fp32 bytes of the dQ tiles the TMA bulk reductions add into the scratch, over the fused kernel's time; the adds run in L2, "
                     "HBM sees the scratch once zeroed, once written back and once read by the conversion kernel"}
 
     # ---- end to end: public API with host buffers ------------------------------------------------
