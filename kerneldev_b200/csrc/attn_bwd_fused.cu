@@ -23,9 +23,10 @@
 // they work on the next one. Every TMEM region is therefore single-buffered (S^T 128 + dP^T 128 + P^T 64 +
 // dK 64 + dV 64 + dQ 64 = 512 columns); only dS^T in shared memory is double-buffered.
 //
-// 768 threads: warp 0 TMA producer; warp 3 / warp 2 issue S^T / dP^T; warp 1 issues dV, dK and dQ;
-// warps 4-19 are four compute warpgroups (32 query columns each, a key row per thread); warps 20-23 move
-// finished dQ tiles from TMEM to the scratch.
+// 768 threads: warp 0 TMA producer; warp 3 issues S^T and dP^T; warp 1 issues dV and warp 2 dK and dQ
+// (24 products per tile from one thread would make that thread the slowest stage); warps 4-19 are four
+// compute warpgroups (32 query columns each, a key row per thread); warps 20-23 move finished dQ tiles
+// from TMEM to the scratch.
 #include <algorithm>
 
 #include "attn_bwd.cuh"
@@ -52,7 +53,9 @@ struct FusedCfg {
   static_assert(SMEM_ALLOC <= 232448, "shared memory budget");
   // registers: 80 per thread at launch; light warps release down to 56, the dQ warps to 72, compute warps take 88
   static constexpr int REGS_LIGHT = 56, REGS_DQ = 72, REGS_COMPUTE = 88;
-  static_assert(4 * 32 * REGS_LIGHT + 4 * 32 * REGS_DQ + 16 * 32 * REGS_COMPUTE <= 768 * 80, "register pool");
+  static constexpr int REGS_LAUNCH = 80;             // per thread at launch: 6 warps per scheduler x 32 x 80 fit its 16384 registers
+  static_assert(4 * 32 * REGS_LIGHT + 4 * 32 * REGS_DQ + 16 * 32 * REGS_COMPUTE <= THREADS * REGS_LAUNCH, "register pool");
+  static_assert(THREADS == 768, "a 25th warp would put 7 warps on one scheduler and cut the launch count to 72 registers");
 };
 
 enum : uint32_t {
@@ -101,13 +104,13 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     abortf.v = 0;
     for (int f = 0; f < C::NFIX; ++f) {
       mbar_init(smem_u32(&bar_fix_full[f]), 1);
-      mbar_init(smem_u32(&bar_fix_empty[f]), 3);  // all three issuers are done with the head's K and V
+      mbar_init(smem_u32(&bar_fix_empty[f]), 2);  // the M1 issuer and the dK / dQ issuer are done with the head's K and V
     }
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(smem_u32(&bar_ring_full[s]), 1);
-      mbar_init(smem_u32(&bar_ring_empty[s]), 1);
+      mbar_init(smem_u32(&bar_ring_empty[s]), 2);   // the dV issuer and the dK / dQ issuer are done with the stage
     }
-    mbar_init(smem_u32(&bar_s_full), 2);       // one commit from each of the two M1 issuers
+    mbar_init(smem_u32(&bar_s_full), 1);       // S^T and dP^T of a tile are in TMEM
     // the warps of a role arrive once each (lane 0, after a warp-wide sync): hundreds of single-thread arrivals on one
     // barrier would serialise in the shared-memory atomic unit
     mbar_init(smem_u32(&bar_sp_free), 16);     // every compute warp has loaded its S^T and dP^T columns
@@ -117,7 +120,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     mbar_init(smem_u32(&bar_dq_empty), 4);     // the dQ warps have read the dQ tile out of TMEM
     mbar_init(smem_u32(&bar_ds_empty[0]), 1);  // a dS^T buffer is free: its products and the reduction staged in it are done
     mbar_init(smem_u32(&bar_ds_empty[1]), 1);
-    mbar_init(smem_u32(&bar_acc_full), 1);
+    mbar_init(smem_u32(&bar_acc_full), 2);       // both accumulating issuers have committed the head's last products
     mbar_init(smem_u32(&bar_acc_free), 16);    // every compute warp has read its part of dK and dV
     fence_barrier_init();
   }
@@ -172,13 +175,12 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         for (int e = max(0, issued - C::STAGES); e < issued; ++e) drain_wait(smem_u32(&bar_ring_full[e % C::STAGES]), (e / C::STAGES) & 1);
         for (int f = max(0, fix_issued - C::NFIX); f < fix_issued; ++f) drain_wait(smem_u32(&bar_fix_full[f % C::NFIX]), (f / C::NFIX) & 1);
       }
-    } else if ((warp == 3 || warp == 2) && lane == 0 && n > 0) {
-      // ---------------- M1 issuers: warp 3: S^T = K Q^T; warp 2: dP^T = V dO^T (N = 128 queries) ----------------
-      const bool dp_part = (warp == 2);
+    } else if (warp == 3 && lane == 0 && n > 0) {
+      // ---------------- M1 issuer: S^T = K Q^T, then dP^T = V dO^T (N = 128 queries each) ----------------
       const uint32_t idesc_m1 = make_idesc_f16(kBf16, 0, 0, KD_TILE, KD_TILE);
       const uint32_t hi = desc_hi_sw128();
       const uint32_t loRingK = desc_lo_kmajor(sRing);
-      const uint32_t dst = tbase + (dp_part ? C::TM_DP : C::TM_S);
+      const uint32_t tS = tbase + C::TM_S, tDP = tbase + C::TM_DP;
       bool ok = true;
       int t = 0, stage = 0;   // tiles so far and ring stage, running on across the heads
       uint32_t ring_parity = 0;
@@ -186,15 +188,9 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const int fb = hh % C::NFIX;
         ok = mbar_wait(smem_u32(&bar_fix_full[fb]), (hh / C::NFIX) & 1, &abortf, a.status, W_U_FIXFULL);
         if (!ok) break;
-        const uint32_t loA = desc_lo_kmajor(sFix + fb * 2 * C::TILE_BYTES + (dp_part ? C::TILE_BYTES : 0));   // V or K
-        uint64_t adesc[HD / 16];
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) adesc[kk] = desc64(loA + koff_kmajor(kk), hi);
+        const uint32_t loK = desc_lo_kmajor(sFix + fb * 2 * C::TILE_BYTES), loV = loK + (C::TILE_BYTES >> 4);
         for (int e = 0; e < n && ok; ++e) {
-          const uint32_t blo = loRingK + stage * (2 * C::TILE_BYTES >> 4) + (dp_part ? (C::TILE_BYTES >> 4) : 0);   // Q or dO
-          uint64_t bdesc[HD / 16];
-#pragma unroll
-          for (int kk = 0; kk < HD / 16; ++kk) bdesc[kk] = desc64(blo + koff_kmajor(kk), hi);
+          const uint32_t qlo = loRingK + stage * (2 * C::TILE_BYTES >> 4), dolo = qlo + (C::TILE_BYTES >> 4);
           if (t > 0) {   // the compute warps must have loaded the previous tile's S^T and dP^T
             ok = mbar_wait(smem_u32(&bar_sp_free), (t - 1) & 1, &abortf, a.status, W_U_SPFREE);
             if (!ok) break;
@@ -202,9 +198,12 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           ok = mbar_wait(smem_u32(&bar_ring_full[stage]), ring_parity, &abortf, a.status, W_U_RINGFULL);
           if (!ok) break;
           tc_fence_after_sync();
-          mma_ss64<false>(dst, adesc[0], bdesc[0], idesc_m1);
+          mma_ss64<false>(tS, desc64(loK, hi), desc64(qlo, hi), idesc_m1);
 #pragma unroll
-          for (int kk = 1; kk < HD / 16; ++kk) mma_ss64<true>(dst, adesc[kk], bdesc[kk], idesc_m1);
+          for (int kk = 1; kk < HD / 16; ++kk) mma_ss64<true>(tS, desc64(loK + koff_kmajor(kk), hi), desc64(qlo + koff_kmajor(kk), hi), idesc_m1);
+          mma_ss64<false>(tDP, desc64(loV, hi), desc64(dolo, hi), idesc_m1);
+#pragma unroll
+          for (int kk = 1; kk < HD / 16; ++kk) mma_ss64<true>(tDP, desc64(loV + koff_kmajor(kk), hi), desc64(dolo + koff_kmajor(kk), hi), idesc_m1);
           mma_commit(smem_u32(&bar_s_full));
           ++t;
           if (++stage == C::STAGES) { stage = 0; ring_parity ^= 1; }
@@ -212,28 +211,20 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (ok) mma_commit(smem_u32(&bar_fix_empty[fb]));   // this issuer's products of the head no longer read K / V
       }
     } else if (warp == 1 && lane == 0 && n > 0) {
-      // ------- M2 issuer: per tile dV += P^T dO (A from TMEM), dK += dS^T Q and dQ_tile = dS K (A from shared memory) -------
+      // ------- dV issuer: per tile dV += P^T dO (A from TMEM) -------
       const uint32_t idesc_dv = make_idesc_f16(kBf16, 0, 1, KD_TILE, HD);   // B = dO rows, MN-major
-      const uint32_t idesc_dk = make_idesc_f16(kBf16, 0, 1, KD_TILE, HD);   // A = dS^T rows (keys) K-major, B = Q rows, MN-major
-      const uint32_t idesc_dq = make_idesc_f16(kBf16, 1, 1, KD_TILE, HD);   // A = dS^T read MN-major (M = queries), B = K rows, MN-major
-      const uint32_t tDK = tbase + C::TM_DK, tDV = tbase + C::TM_DV, tDQ = tbase + C::TM_DQ, tPT = tbase + C::TM_PT;
+      const uint32_t tDV = tbase + C::TM_DV, tPT = tbase + C::TM_PT;
       const uint32_t hi = desc_hi_sw128();
       const uint32_t loRingMN = desc_lo_mnmajor(sRing);
       bool ok = true;
       int t = 0, stage = 0;
       for (int hh = 0; hh < nh && ok; ++hh) {
-        const int fb = hh % C::NFIX;
-        const uint32_t loK = desc_lo_mnmajor(sFix + fb * 2 * C::TILE_BYTES);
         if (hh > 0) {   // the previous head's dK and dV must have been read out of the accumulators
           ok = mbar_wait(smem_u32(&bar_acc_free), (hh - 1) & 1, &abortf, a.status, W_U_ACCFREE);
           if (!ok) break;
         }
         for (int e = 0; e < n && ok; ++e) {
-          const int tb = t & 1;
-          const uint32_t qb = loRingMN + stage * (2 * C::TILE_BYTES >> 4);
-          const uint32_t dob = qb + (C::TILE_BYTES >> 4);
-          const uint32_t dsK = desc_lo_kmajor(sDS + tb * (2 * C::TILE_BYTES));     // dS^T as [keys][queries]: K-major A of dK
-          const uint32_t dsMN = desc_lo_mnmajor(sDS + tb * (2 * C::TILE_BYTES));   // the same bytes as MN-major A of dQ
+          const uint32_t dob = loRingMN + stage * (2 * C::TILE_BYTES >> 4) + (C::TILE_BYTES >> 4);
           ok = mbar_wait(smem_u32(&bar_p_full), t & 1, &abortf, a.status, W_U_PFULL);
           if (!ok) break;
           tc_fence_after_sync();
@@ -241,10 +232,40 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
           for (int kk = 1; kk < KD_TILE / 16; ++kk) mma_ts_split(tDV, tPT + kk * 8, dob + koff_mnmajor(kk), hi, idesc_dv, 1u);
           mma_commit(smem_u32(&bar_pt_free));
+          mma_commit(smem_u32(&bar_ring_empty[stage]));   // one of two: dO of the stage is no longer read
+          ++t;
+          if (++stage == C::STAGES) stage = 0;
+        }
+        if (ok) mma_commit(smem_u32(&bar_acc_full));
+      }
+    } else if (warp == 2 && lane == 0 && n > 0) {
+      // ------- dK / dQ issuer: per tile dK += dS^T Q and dQ_tile = dS K (A = dS^T from shared memory) -------
+      const uint32_t idesc_dk = make_idesc_f16(kBf16, 0, 1, KD_TILE, HD);   // A = dS^T rows (keys) K-major, B = Q rows, MN-major
+      const uint32_t idesc_dq = make_idesc_f16(kBf16, 1, 1, KD_TILE, HD);   // A = dS^T read MN-major (M = queries), B = K rows, MN-major
+      const uint32_t tDK = tbase + C::TM_DK, tDQ = tbase + C::TM_DQ;
+      const uint32_t hi = desc_hi_sw128();
+      const uint32_t loRingMN = desc_lo_mnmajor(sRing);
+      bool ok = true;
+      int t = 0, stage = 0;
+      for (int hh = 0; hh < nh && ok; ++hh) {
+        const int fb = hh % C::NFIX;
+        const uint32_t loK = desc_lo_mnmajor(sFix + fb * 2 * C::TILE_BYTES);
+        if (hh > 0) {
+          ok = mbar_wait(smem_u32(&bar_acc_free), (hh - 1) & 1, &abortf, a.status, W_U_ACCFREE);
+          if (!ok) break;
+        }
+        for (int e = 0; e < n && ok; ++e) {
+          const int tb = t & 1;
+          const uint32_t qb = loRingMN + stage * (2 * C::TILE_BYTES >> 4);
+          const uint32_t dsK = desc_lo_kmajor(sDS + tb * (2 * C::TILE_BYTES));     // dS^T as [keys][queries]: K-major A of dK
+          const uint32_t dsMN = desc_lo_mnmajor(sDS + tb * (2 * C::TILE_BYTES));   // the same bytes as MN-major A of dQ
+          ok = mbar_wait(smem_u32(&bar_p_full), t & 1, &abortf, a.status, W_U_PFULL);
+          if (!ok) break;
+          tc_fence_after_sync();
           mma_ss_split(tDK, dsK, qb, hi, idesc_dk, e > 0 ? 1u : 0u);
 #pragma unroll
           for (int kk = 1; kk < KD_TILE / 16; ++kk) mma_ss_split(tDK, dsK + koff_kmajor(kk), qb + koff_mnmajor(kk), hi, idesc_dk, 1u);
-          mma_commit(smem_u32(&bar_ring_empty[stage]));
+          mma_commit(smem_u32(&bar_ring_empty[stage]));   // two of two: Q of the stage is no longer read
           if (t > 0) {   // the dQ warpgroup must have read the previous tile's dQ out of TMEM
             ok = mbar_wait(smem_u32(&bar_dq_empty), (t - 1) & 1, &abortf, a.status, W_U_DQEMPTY);
             if (!ok) break;
@@ -253,7 +274,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           mma_ss_split(tDQ, dsMN, loK, hi, idesc_dq, 0u);
 #pragma unroll
           for (int kk = 1; kk < KD_TILE / 16; ++kk) mma_ss_split(tDQ, dsMN + koff_mnmajor(kk), loK + koff_mnmajor(kk), hi, idesc_dq, 1u);
-          mma_commit(smem_u32(&bar_dq_full));
+          mma_commit(smem_u32(&bar_dq_full));   // issued after the dK product by the same thread: it covers both
           ++t;
           if (++stage == C::STAGES) stage = 0;
         }
@@ -524,6 +545,16 @@ static int launch_fused_t(const CUtensorMap& tmQ, const CUtensorMap& tmK, const 
   auto kern = attn_bwd_fused_kernel<kBf16>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_ALLOC);
   if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "fused bwd smem attribute: %s", cudaGetErrorString(e));
+  // The warps re-divide the registers the CTA was launched with; a request beyond that pool would block for ever,
+  // so a build whose per-thread count is below the one the division assumes is refused here.
+  static int launch_regs = 0;
+  if (launch_regs == 0) {
+    cudaFuncAttributes fa;
+    e = cudaFuncGetAttributes(&fa, kern);
+    if (e != cudaSuccess) return set_error(KD_ERR_DEVICE, "fused bwd attributes: %s", cudaGetErrorString(e));
+    launch_regs = fa.numRegs;
+  }
+  if (launch_regs < C::REGS_LAUNCH) return set_error(KD_ERR_DEVICE, "fused bwd was built with %d registers per thread, needs %d", launch_regs, C::REGS_LAUNCH);
   kern<<<grid, C::THREADS, C::SMEM_ALLOC, stream>>>(tmQ, tmK, tmV, tmDO, tmAcc, a);
   const size_t rows = (size_t)a.B * a.H * a.T;
   const int blocks = static_cast<int>(std::min<size_t>((rows + 31) / 32, size_t(148) * 32));
