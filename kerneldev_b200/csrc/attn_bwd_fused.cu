@@ -42,9 +42,11 @@ struct FusedCfg {
   static constexpr int SMEM_FIX = 0;
   static constexpr int SMEM_RING = SMEM_FIX + NFIX * 2 * TILE_BYTES;
   static constexpr int SMEM_DS = SMEM_RING + STAGES * 2 * TILE_BYTES;   // 2 x dS^T of a query tile: two [128 keys][64 queries] blocks
-  static constexpr int SMEM_STAGE = SMEM_DS + 2 * 2 * TILE_BYTES;      // per compute warp: 32 x {lse, delta, descriptor}
-  static constexpr int STAGE_WORDS = 3 * 32;
-  static constexpr int SMEM_LIST = SMEM_STAGE + 16 * STAGE_WORDS * 4;
+  // per ring stage, beside the tiles: LSE, delta and token descriptor of the stage's 128 queries and the 32 mask words of
+  // the query tile, copied there by the producer warp
+  static constexpr int SIDE_WORDS = 3 * KD_TILE + 32;
+  static constexpr int SMEM_SIDE = SMEM_DS + 2 * 2 * TILE_BYTES;
+  static constexpr int SMEM_LIST = SMEM_SIDE + STAGES * SIDE_WORDS * 4;
   static constexpr int SMEM_TOTAL = SMEM_LIST + 128 * 2;
   static constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;
   static constexpr int THREADS = 768;
@@ -61,7 +63,7 @@ struct FusedCfg {
 enum : uint32_t {
   W_U_FIXFULL = 0x401, W_U_RINGEMPTY = 0x402, W_U_RINGFULL = 0x403, W_U_PFULL = 0x404, W_U_SFULL = 0x405,
   W_U_ACCFULL = 0x406, W_U_SPFREE = 0x407, W_U_FIXEMPTY = 0x408, W_U_ACCFREE = 0x409, W_U_DQFULL = 0x40A,
-  W_U_DQEMPTY = 0x40B, W_U_DSEMPTY = 0x40C, W_U_PTFREE = 0x40D,
+  W_U_DQEMPTY = 0x40B, W_U_DSEMPTY = 0x40C, W_U_PTFREE = 0x40D, W_U_SFULL1 = 0x40E, W_U_SPFREE1 = 0x40F,
 };
 
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
@@ -85,11 +87,11 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const uint32_t sFix = smem_u32(smem + C::SMEM_FIX);    // buffer f: K at +0, V at +TILE_BYTES
   const uint32_t sRing = smem_u32(smem + C::SMEM_RING);  // stage s: Q at +0, dO at +TILE_BYTES
   const uint32_t sDS = smem_u32(smem + C::SMEM_DS);      // buffer t: block 0 (queries 0-63) at +0, block 1 at +TILE_BYTES
-  uint32_t* sStage = reinterpret_cast<uint32_t*>(smem + C::SMEM_STAGE);
+  uint32_t* sSide = reinterpret_cast<uint32_t*>(smem + C::SMEM_SIDE);
   uint16_t* sList = reinterpret_cast<uint16_t*>(smem + C::SMEM_LIST);
 
   __shared__ __align__(8) uint64_t bar_fix_full[C::NFIX], bar_fix_empty[C::NFIX], bar_ring_full[C::STAGES],
-      bar_ring_empty[C::STAGES], bar_s_full, bar_sp_free, bar_p_full, bar_pt_free, bar_acc_full, bar_acc_free,
+      bar_ring_empty[C::STAGES], bar_s_full[2], bar_sp_free[2], bar_p_full, bar_pt_free, bar_acc_full, bar_acc_free,
       bar_dq_full, bar_dq_empty, bar_ds_empty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ AbortFlag abortf;
@@ -107,13 +109,16 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       mbar_init(smem_u32(&bar_fix_empty[f]), 2);  // the M1 issuer and the dK / dQ issuer are done with the head's K and V
     }
     for (int s = 0; s < C::STAGES; ++s) {
-      mbar_init(smem_u32(&bar_ring_full[s]), 1);
+      mbar_init(smem_u32(&bar_ring_full[s]), 2);    // the TMA loads (with their byte count) and the producer warp's own copies
       mbar_init(smem_u32(&bar_ring_empty[s]), 2);   // the dV issuer and the dK / dQ issuer are done with the stage
     }
-    mbar_init(smem_u32(&bar_s_full), 1);       // S^T and dP^T of a tile are in TMEM
+    // S^T and dP^T are produced and released in two halves of 64 query columns
+    mbar_init(smem_u32(&bar_s_full[0]), 1);
+    mbar_init(smem_u32(&bar_s_full[1]), 1);
     // the warps of a role arrive once each (lane 0, after a warp-wide sync): hundreds of single-thread arrivals on one
     // barrier would serialise in the shared-memory atomic unit
-    mbar_init(smem_u32(&bar_sp_free), 16);     // every compute warp has loaded its S^T and dP^T columns
+    mbar_init(smem_u32(&bar_sp_free[0]), 16);  // every compute warp has loaded its S^T and dP^T columns of the half
+    mbar_init(smem_u32(&bar_sp_free[1]), 16);
     mbar_init(smem_u32(&bar_p_full), 16);      // P^T is in TMEM and dS^T in shared memory
     mbar_init(smem_u32(&bar_pt_free), 1);      // the dV product has read P^T
     mbar_init(smem_u32(&bar_dq_full), 1);
@@ -140,47 +145,78 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
   if (warp < 4) {
     reg_dealloc<C::REGS_LIGHT>();
-    if (warp == 0 && lane == 0 && n > 0) {
-      // ------------------------------ TMA producer ------------------------------
-      tma_prefetch_desc(&tmQ);
-      tma_prefetch_desc(&tmK);
-      tma_prefetch_desc(&tmV);
-      tma_prefetch_desc(&tmDO);
+    if (warp == 0 && n > 0) {
+      // ------------------------------ producer warp ------------------------------
+      // lane 0 issues the TMA loads; all lanes copy the per-query scalars of the stage (4 queries each) and the tile's
+      // mask words (one each) with plain loads, so that the compute warps find everything about a tile in shared memory
+      if (lane == 0) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        tma_prefetch_desc(&tmDO);
+      }
       int issued = 0, fix_issued = 0;   // ring entries / resident pairs requested so far, over all heads
       bool ok = true;
       for (int hh = 0; hh < nh && ok; ++hh) {
         const int h = h0 + hh, fb = hh % C::NFIX;
-        if (hh >= C::NFIX) {
-          ok = mbar_wait(smem_u32(&bar_fix_empty[fb]), (hh / C::NFIX - 1) & 1, &abortf, a.status, W_U_FIXEMPTY);
-          if (!ok) break;
+        if (lane == 0) {
+          if (hh >= C::NFIX) ok = mbar_wait(smem_u32(&bar_fix_empty[fb]), (hh / C::NFIX - 1) & 1, &abortf, a.status, W_U_FIXEMPTY);
+          if (ok) {
+            mbar_arrive_expect_tx(smem_u32(&bar_fix_full[fb]), 2 * C::TILE_BYTES);
+            tma_load_4d(sFix + fb * 2 * C::TILE_BYTES, &tmK, smem_u32(&bar_fix_full[fb]), 0, kt * KD_TILE, h, b);
+            tma_load_4d(sFix + fb * 2 * C::TILE_BYTES + C::TILE_BYTES, &tmV, smem_u32(&bar_fix_full[fb]), 0, kt * KD_TILE, h, b);
+            fix_issued = hh + 1;
+          }
         }
-        mbar_arrive_expect_tx(smem_u32(&bar_fix_full[fb]), 2 * C::TILE_BYTES);
-        tma_load_4d(sFix + fb * 2 * C::TILE_BYTES, &tmK, smem_u32(&bar_fix_full[fb]), 0, kt * KD_TILE, h, b);
-        tma_load_4d(sFix + fb * 2 * C::TILE_BYTES + C::TILE_BYTES, &tmV, smem_u32(&bar_fix_full[fb]), 0, kt * KD_TILE, h, b);
-        fix_issued = hh + 1;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        const float* lse_row = a.lse + ((size_t)b * a.H + h) * a.T;
+        const float* delta_row = a.delta + ((size_t)b * a.H + h) * a.T;
         for (int e = 0; e < n; ++e) {
           const int s = issued % C::STAGES;
           const uint32_t ph = (issued / C::STAGES) & 1;
           const int qt = list[e] & 0xFF;
-          ok = mbar_wait(smem_u32(&bar_ring_empty[s]), ph ^ 1, &abortf, a.status, W_U_RINGEMPTY);
+          // the scalars are requested before the wait for the stage: the wait covers their latency
+          // (a query at or beyond the sequence length reads the last row's scalars: its descriptor is 0, so the tile is
+          // PARTIAL and the mask removes it)
+          const int q = qt * KD_TILE + 4 * lane;
+          float4 l4, d4;
+          l4.x = lse_row[min(q + 0, a.T - 1)]; l4.y = lse_row[min(q + 1, a.T - 1)];
+          l4.z = lse_row[min(q + 2, a.T - 1)]; l4.w = lse_row[min(q + 3, a.T - 1)];
+          d4.x = delta_row[min(q + 0, a.T - 1)]; d4.y = delta_row[min(q + 1, a.T - 1)];
+          d4.z = delta_row[min(q + 2, a.T - 1)]; d4.w = delta_row[min(q + 3, a.T - 1)];
+          const uint4 c4 = *reinterpret_cast<const uint4*>(a.desc + (size_t)b * a.Tpad + q);   // the descriptor rows are padded to whole tiles
+          const uint32_t tbw = a.tilebits[((size_t)b * a.NT + qt) * 32 + lane];
+          if (lane == 0) {
+            ok = mbar_wait(smem_u32(&bar_ring_empty[s]), ph ^ 1, &abortf, a.status, W_U_RINGEMPTY);
+            if (ok) {
+              mbar_arrive_expect_tx(smem_u32(&bar_ring_full[s]), 2 * C::TILE_BYTES);
+              const uint32_t dst = sRing + s * 2 * C::TILE_BYTES;
+              tma_load_4d(dst, &tmQ, smem_u32(&bar_ring_full[s]), 0, qt * KD_TILE, h, b);
+              tma_load_4d(dst + C::TILE_BYTES, &tmDO, smem_u32(&bar_ring_full[s]), 0, qt * KD_TILE, h, b);
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
           if (!ok) break;
-          mbar_arrive_expect_tx(smem_u32(&bar_ring_full[s]), 2 * C::TILE_BYTES);
-          const uint32_t dst = sRing + s * 2 * C::TILE_BYTES;
-          tma_load_4d(dst, &tmQ, smem_u32(&bar_ring_full[s]), 0, qt * KD_TILE, h, b);
-          tma_load_4d(dst + C::TILE_BYTES, &tmDO, smem_u32(&bar_ring_full[s]), 0, qt * KD_TILE, h, b);
+          uint32_t* side = sSide + s * C::SIDE_WORDS;
+          *reinterpret_cast<float4*>(side + 4 * lane) = l4;
+          *reinterpret_cast<float4*>(side + KD_TILE + 4 * lane) = d4;
+          *reinterpret_cast<uint4*>(side + 2 * KD_TILE + 4 * lane) = c4;
+          side[3 * KD_TILE + lane] = tbw;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bar_ring_full[s]));
           ++issued;
         }
       }
-      if (abortf.v != 0) {   // let the copies in flight land before the CTA exits
+      if (lane == 0 && abortf.v != 0) {   // let the copies in flight land before the CTA exits
         for (int e = max(0, issued - C::STAGES); e < issued; ++e) drain_wait(smem_u32(&bar_ring_full[e % C::STAGES]), (e / C::STAGES) & 1);
         for (int f = max(0, fix_issued - C::NFIX); f < fix_issued; ++f) drain_wait(smem_u32(&bar_fix_full[f % C::NFIX]), (f / C::NFIX) & 1);
       }
     } else if (warp == 3 && lane == 0 && n > 0) {
-      // ---------------- M1 issuer: S^T = K Q^T, then dP^T = V dO^T (N = 128 queries each) ----------------
-      const uint32_t idesc_m1 = make_idesc_f16(kBf16, 0, 0, KD_TILE, KD_TILE);
+      // ------- M1 issuer: per half of 64 queries, S^T = K Q^T and dP^T = V dO^T into columns 64 half .. 64 half + 63 -------
+      const uint32_t idesc_m1 = make_idesc_f16(kBf16, 0, 0, KD_TILE, KD_TILE / 2);
       const uint32_t hi = desc_hi_sw128();
       const uint32_t loRingK = desc_lo_kmajor(sRing);
-      const uint32_t tS = tbase + C::TM_S, tDP = tbase + C::TM_DP;
       bool ok = true;
       int t = 0, stage = 0;   // tiles so far and ring stage, running on across the heads
       uint32_t ring_parity = 0;
@@ -190,21 +226,28 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (!ok) break;
         const uint32_t loK = desc_lo_kmajor(sFix + fb * 2 * C::TILE_BYTES), loV = loK + (C::TILE_BYTES >> 4);
         for (int e = 0; e < n && ok; ++e) {
-          const uint32_t qlo = loRingK + stage * (2 * C::TILE_BYTES >> 4), dolo = qlo + (C::TILE_BYTES >> 4);
-          if (t > 0) {   // the compute warps must have loaded the previous tile's S^T and dP^T
-            ok = mbar_wait(smem_u32(&bar_sp_free), (t - 1) & 1, &abortf, a.status, W_U_SPFREE);
-            if (!ok) break;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            // rows 64 half .. of the stage's Q and dO tiles (128 bytes per row)
+            const uint32_t qlo = loRingK + stage * (2 * C::TILE_BYTES >> 4) + half * (C::TILE_BYTES >> 5), dolo = qlo + (C::TILE_BYTES >> 4);
+            const uint32_t tS = tbase + C::TM_S + half * 64, tDP = tbase + C::TM_DP + half * 64;
+            if (t > 0) {   // the compute warps must have loaded the previous tile's columns of this half
+              ok = mbar_wait(smem_u32(&bar_sp_free[half]), (t - 1) & 1, &abortf, a.status, half ? W_U_SPFREE1 : W_U_SPFREE);
+              if (!ok) break;
+            }
+            if (half == 0) {
+              ok = mbar_wait(smem_u32(&bar_ring_full[stage]), ring_parity, &abortf, a.status, W_U_RINGFULL);
+              if (!ok) break;
+            }
+            tc_fence_after_sync();
+            mma_ss64<false>(tS, desc64(loK, hi), desc64(qlo, hi), idesc_m1);
+#pragma unroll
+            for (int kk = 1; kk < HD / 16; ++kk) mma_ss64<true>(tS, desc64(loK + koff_kmajor(kk), hi), desc64(qlo + koff_kmajor(kk), hi), idesc_m1);
+            mma_ss64<false>(tDP, desc64(loV, hi), desc64(dolo, hi), idesc_m1);
+#pragma unroll
+            for (int kk = 1; kk < HD / 16; ++kk) mma_ss64<true>(tDP, desc64(loV + koff_kmajor(kk), hi), desc64(dolo + koff_kmajor(kk), hi), idesc_m1);
+            mma_commit(smem_u32(&bar_s_full[half]));
           }
-          ok = mbar_wait(smem_u32(&bar_ring_full[stage]), ring_parity, &abortf, a.status, W_U_RINGFULL);
-          if (!ok) break;
-          tc_fence_after_sync();
-          mma_ss64<false>(tS, desc64(loK, hi), desc64(qlo, hi), idesc_m1);
-#pragma unroll
-          for (int kk = 1; kk < HD / 16; ++kk) mma_ss64<true>(tS, desc64(loK + koff_kmajor(kk), hi), desc64(qlo + koff_kmajor(kk), hi), idesc_m1);
-          mma_ss64<false>(tDP, desc64(loV, hi), desc64(dolo, hi), idesc_m1);
-#pragma unroll
-          for (int kk = 1; kk < HD / 16; ++kk) mma_ss64<true>(tDP, desc64(loV + koff_kmajor(kk), hi), desc64(dolo + koff_kmajor(kk), hi), idesc_m1);
-          mma_commit(smem_u32(&bar_s_full));
           ++t;
           if (++stage == C::STAGES) { stage = 0; ring_parity ^= 1; }
         }
@@ -287,106 +330,87 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   } else if (warp < 20) {
     reg_alloc<C::REGS_COMPUTE>();
     // ------------------------------ compute warpgroups ------------------------------
-    const int g = (warp - 4) >> 2;   // warpgroup = 32 query columns of every tile
+    // warpgroup g handles queries 16 g .. 16 g + 15 (first half of the tile's columns) and 64 + 16 g .. 64 + 16 g + 15 (second
+    // half): every warp is done with the first 64 columns of S^T and dP^T after its first pair of loads, so the next tile's
+    // products for those columns are issued while this tile's arithmetic is still running
+    const int g = (warp - 4) >> 2;
     const int wq = warp & 3;
     const int row = wq * 32 + lane;
     const int kj = kt * KD_TILE + row;   // this thread's key
     const bool k_valid = kj < a.T;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
-    uint32_t* st_buf = sStage + (size_t)(warp - 4) * C::STAGE_WORDS;  // [32 lse][32 delta][32 desc]
     const float c = a.scale_log2;
     const uint32_t kdesc = a.desc[(size_t)b * a.Tpad + kj];
-    // this thread's 64 bytes of its key's row in dS^T block g / 2: 16-byte chunks 4 (g % 2) .. + 3, swizzled with the row
-    const uint32_t ds_row = static_cast<uint32_t>(g >> 1) * C::TILE_BYTES + static_cast<uint32_t>(row) * 128u;
+    // this thread's bytes of its key's row in dS^T: 16-byte chunks 2 g, 2 g + 1 of block 0 and of block 1, swizzled with the row
+    const uint32_t ds_row = static_cast<uint32_t>(row) * 128u;
     const uint32_t ds_sw = static_cast<uint32_t>(row & 7);
     bool ok = true;
 
-    // LSE, delta and the descriptor of the next tile's queries are fetched one tile ahead into registers
-    // and handed to the warp through its shared-memory staging buffer
-    float pre_lse = 0.f, pre_delta = 0.f;
-    uint32_t pre_desc = 0u;
-    uint32_t tb_pre[5] = {0u, 0u, 0u, 0u, 0u};   // query-side class masks: sees-prefix, sees-context, sees-in_span, context, same-span armed
-    auto prefetch = [&](uint32_t entry, int h) {
-      if ((entry >> 8) == KD_TILE_PARTIAL) {
-        const uint32_t* tbp = a.tilebits + ((size_t)b * a.NT + (entry & 0xFFu)) * 32;
-        tb_pre[0] = tbp[4 * TB_SEES_PRE + g];
-        tb_pre[1] = tbp[4 * TB_SEES_CTX + g];
-        tb_pre[2] = tbp[4 * TB_SEES_INS + g];
-        tb_pre[3] = tbp[4 * TB_CTX + g];
-        tb_pre[4] = tbp[4 * TB_SIDPOS + g];
-      }
-      // a query at or beyond the sequence length reads the last row's scalars: its descriptor is 0,
-      // so the tile is PARTIAL and the mask removes it
-      const int q = (entry & 0xFF) * KD_TILE + g * 32 + lane;
-      const size_t r = ((size_t)b * a.H + h) * a.T + min(q, a.T - 1);
-      pre_lse = a.lse[r];   // negated where it is used: a negation here would wait for the load
-      pre_delta = a.delta[r];
-      pre_desc = a.desc[(size_t)b * a.Tpad + q];
-    };
-    uint32_t ent_next = n > 0 ? list[0] : 0u;
-    if (n > 0) prefetch(ent_next, h0);
+    const uint32_t tb_sel = (g & 1) ? 0x7632u : 0x5410u;   // bits 0-15: queries 16 g .. of the tile, bits 16-31: queries 64 + 16 g ..
+    int stage = 0;
+    uint32_t ring_parity = 0;
     int t = 0;   // tiles so far, over all heads
-    const uint32_t tS = tbase + lane_base + C::TM_S + g * 32, tP = tbase + lane_base + C::TM_DP + g * 32;
-    const uint32_t tPT = tbase + lane_base + C::TM_PT + g * 16;
-    const uint32_t b_sfull = smem_u32(&bar_s_full), b_spfree = smem_u32(&bar_sp_free), b_pfull = smem_u32(&bar_p_full),
+    const uint32_t tS = tbase + lane_base + C::TM_S + g * 16, tP = tbase + lane_base + C::TM_DP + g * 16;   // + 64 for the second half
+    const uint32_t tPT = tbase + lane_base + C::TM_PT + g * 8;                                                // + 32 for the second half
+    const uint32_t b_sfull = smem_u32(&bar_s_full[0]), b_spfree = smem_u32(&bar_sp_free[0]), b_pfull = smem_u32(&bar_p_full),
                    b_ptfree = smem_u32(&bar_pt_free);
 
     for (int hh = 0; hh < nh && ok; ++hh) {
       const int h = h0 + hh;
       for (int e = 0; e < n; ++e) {
-        const uint32_t ent = ent_next;
+        const uint32_t ent = list[e];
         const uint32_t cls = ent >> 8;
-        __syncwarp();
-        st_buf[lane] = __float_as_uint(pre_lse);
-        st_buf[32 + lane] = __float_as_uint(pre_delta);
-        st_buf[64 + lane] = pre_desc;
-        __syncwarp();
+        // the stage's scalars and mask words were written by the producer warp before its arrival on this barrier
+        ok = mbar_wait(smem_u32(&bar_ring_full[stage]), ring_parity, &abortf, a.status, W_U_RINGFULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const uint32_t* side = sSide + stage * C::SIDE_WORDS + g * 16;   // this warpgroup's first group of 16 queries; the second is 64 on
+        if (++stage == C::STAGES) { stage = 0; ring_parity ^= 1; }
         uint32_t mk = 0xFFFFFFFFu;   // visibility of this key for the 32 queries
         if (cls == KD_TILE_PARTIAL) {
-          const int i0 = (ent & 0xFF) * KD_TILE + g * 32;  // first query handled here
-          key_row_mask<1>(kdesc, kj, i0, &tb_pre[0], &tb_pre[1], &tb_pre[2], &tb_pre[3], &mk);
-          if (tb_pre[4] != 0u && __any_sync(0xffffffffu, (kdesc & TD_INS) != 0u)) {
-            const uint32_t key = span_key_of_key(kdesc);
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              const uint4 q4 = *reinterpret_cast<const uint4*>(st_buf + 64 + j);
-              mk |= (span_match_query(key, q4.x) << (j + 0)) | (span_match_query(key, q4.y) << (j + 1)) |
-                    (span_match_query(key, q4.z) << (j + 2)) | (span_match_query(key, q4.w) << (j + 3));
+          // query-side class masks: the two words that hold this warpgroup's groups of 16 queries, combined into one
+          const uint32_t* tbw = side - g * 16 + 3 * KD_TILE + (g >> 1);
+          auto two_groups = [&](int k) { return __byte_perm(tbw[4 * k], tbw[4 * k + 2], tb_sel); };
+          const int i0 = (ent & 0xFF) * KD_TILE + g * 16;  // first query of the first group; the second starts 64 later
+          const uint32_t causal = (~low_bits(kj - i0) & 0xFFFFu) | (~low_bits(kj - i0 - 64) << 16);   // queries i >= this key
+          mk = key_row_mask_word(kdesc, causal, two_groups(TB_SEES_PRE), two_groups(TB_SEES_CTX), two_groups(TB_SEES_INS), two_groups(TB_CTX));
+          if (two_groups(TB_SIDPOS) != 0u) {
+            // "same span": lane L holds the descriptor of query number L of this warpgroup; one round per distinct span among
+            // the warp's 32 keys, each a ballot over the queries
+            const uint32_t qd_lane = side[2 * KD_TILE + (lane & 15) + (lane >> 4) * 64];
+            const uint32_t my_key = span_key_of_key(kdesc);
+            uint32_t todo = __ballot_sync(0xffffffffu, (kdesc & TD_INS) != 0u);
+            while (todo != 0u) {
+              const uint32_t kk = __shfl_sync(0xffffffffu, my_key, __ffs(todo) - 1);
+              const uint32_t hit = __ballot_sync(0xffffffffu, span_match_query(kk, qd_lane) != 0u);
+              const bool mine = (my_key == kk);
+              if (mine) mk |= hit;
+              todo &= ~__ballot_sync(0xffffffffu, mine);
             }
           }
         }
-        // the next entry: of this head or, at the end of the list, the first one again for the next head
-        if (e + 1 < n) {
-          ent_next = list[e + 1];
-          prefetch(ent_next, h);
-        } else if (hh + 1 < nh) {
-          ent_next = list[0];
-          prefetch(ent_next, h + 1);
-        }
         const int tb = t & 1;
         const uint32_t ds_base = sDS + tb * (2 * C::TILE_BYTES) + ds_row;
-        ok = mbar_wait(b_sfull, t & 1, &abortf, a.status, W_U_SFULL);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after_sync();
-
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {   // 16 queries at a time
+        for (int hf = 0; hf < 2; ++hf) {   // 16 queries at a time: one group of each half of the tile's columns
           uint32_t pk_p[8], pk_ds[8];
           uint32_t rs[16], rp[16];
-          tmem_ld16(tS + hf * 16, rs);
-          tmem_ld16(tP + hf * 16, rp);
+          ok = mbar_wait(b_sfull + hf * 8, t & 1, &abortf, a.status, hf ? W_U_SFULL1 : W_U_SFULL);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+          tmem_ld16(tS + hf * 64, rs);
+          tmem_ld16(tP + hf * 64, rp);
           tmem_wait_ld();
-          if (hf == 1) {   // both halves are in registers: the next tile's S^T and dP^T may overwrite the columns
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(b_spfree);
-          }
+          // the values are in registers: the next tile's S^T and dP^T may overwrite this half's columns
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(b_spfree + hf * 8);
           const uint32_t mh = mk >> (hf * 16);
 #pragma unroll
           for (int j = 0; j < 16; j += 4) {
-            const float4 l4 = *reinterpret_cast<const float4*>(st_buf + hf * 16 + j);        // LSE of 4 queries
-            const float4 d4 = *reinterpret_cast<const float4*>(st_buf + 32 + hf * 16 + j);   // delta of 4 queries
+            const float4 l4 = *reinterpret_cast<const float4*>(side + hf * 64 + j);             // LSE of 4 queries
+            const float4 d4 = *reinterpret_cast<const float4*>(side + KD_TILE + hf * 64 + j);   // delta of 4 queries
             const float lw[4] = {l4.x, l4.y, l4.z, l4.w}, dw[4] = {d4.x, d4.y, d4.z, d4.w};
             float pv[4], ds[4];
 #pragma unroll
@@ -412,10 +436,10 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             if (!ok) break;
             tc_fence_after_sync();
           }
-          tmem_st8(tPT + hf * 8, pk_p);
-          const uint32_t ch = static_cast<uint32_t>(4 * (g & 1) + 2 * hf);
-          st_shared_v4(ds_base + (((ch + 0u) ^ ds_sw) << 4), pk_ds[0], pk_ds[1], pk_ds[2], pk_ds[3]);
-          st_shared_v4(ds_base + (((ch + 1u) ^ ds_sw) << 4), pk_ds[4], pk_ds[5], pk_ds[6], pk_ds[7]);
+          tmem_st8(tPT + hf * 32, pk_p);
+          const uint32_t ch = static_cast<uint32_t>(2 * g);
+          st_shared_v4(ds_base + hf * C::TILE_BYTES + (((ch + 0u) ^ ds_sw) << 4), pk_ds[0], pk_ds[1], pk_ds[2], pk_ds[3]);
+          st_shared_v4(ds_base + hf * C::TILE_BYTES + (((ch + 1u) ^ ds_sw) << 4), pk_ds[4], pk_ds[5], pk_ds[6], pk_ds[7]);
         }
         if (!ok) break;
         fence_proxy_async_smem();   // the dK and dQ products read these shared-memory writes through the async proxy

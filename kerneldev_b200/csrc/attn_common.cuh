@@ -55,6 +55,13 @@ __device__ __forceinline__ void mma_ss_split(uint32_t d_tmem, uint32_t alo, uint
 // out back to back with no address arithmetic between them: that thread shares its scheduler with
 // busy compute warps, and every dependent instruction in its path costs it 10-20 cycles.
 __device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; }
+// maximum of three floats in one instruction (sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <bool kAccumulate>
 __device__ __forceinline__ void mma_ss64(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
   asm volatile(

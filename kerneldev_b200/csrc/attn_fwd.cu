@@ -60,8 +60,7 @@ struct FwdCfg {
   static constexpr int SMEM_Q = 0;
   static constexpr int SMEM_K = SMEM_Q + NQ * 2 * TILE_BYTES;
   static constexpr int SMEM_V = SMEM_K + KST * TILE_BYTES;
-  static constexpr int SMEM_KDESC = SMEM_V + VST * TILE_BYTES;     // per softmax warp: the descriptors of its keys (4 KB in all)
-  static constexpr int SMEM_LIST = SMEM_KDESC + 8 * KD_TILE * 4;   // the pair's work list (<= 128 entries)
+  static constexpr int SMEM_LIST = SMEM_V + VST * TILE_BYTES;      // the pair's work list (<= 128 entries)
   static constexpr int SMEM_UNITS = SMEM_LIST + 128 * 2;           // unit list (<= 256 units)
   static constexpr int SMEM_CMD = SMEM_UNITS + 256 * 2;            // 256 x {S command, P V command} (uint4 each)
   static constexpr int SMEM_WCMD = SMEM_CMD + 256 * 2 * 16;        // 2 x 256 softmax commands (u32 each)
@@ -104,7 +103,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t sQ = smem_u32(smem + C::SMEM_Q);
   const uint32_t sK = smem_u32(smem + C::SMEM_K);
   const uint32_t sV = smem_u32(smem + C::SMEM_V);
-  uint32_t* sKdesc = reinterpret_cast<uint32_t*>(smem + C::SMEM_KDESC);
   uint16_t* sList = reinterpret_cast<uint16_t*>(smem + C::SMEM_LIST);
   uint16_t* sUnits = reinterpret_cast<uint16_t*>(smem + C::SMEM_UNITS);
   uint4* sCmd = reinterpret_cast<uint4*>(smem + C::SMEM_CMD);   // [u][0] = S command, [u][1] = P V command
@@ -426,7 +424,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int qtile = 2 * pair + i;
     const int qi = qtile * KD_TILE + row;  // token index of this thread's query
     const bool tile_valid = qtile < a.NT;
-    uint32_t* kd_buf = sKdesc + (size_t)(warp - 4) * CW;   // this warp's copy of its keys' descriptors
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
     const uint32_t tO = tbase + lane_base + (i == 0 ? C::TM_O0 : C::TM_O1);   // this thread's row of O
     const float c = a.scale_log2;
@@ -434,8 +431,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t qd = tile_valid ? a.desc[(size_t)b * a.Tpad + qi] : 0u;
     bool ok = true;
 
-    // Key descriptors of PARTIAL tiles are fetched one unit ahead into registers, so their
-    // global-memory latency overlaps the previous tile's softmax.
+    // Key descriptors (lane L holds keys L, 32 + L, ...) and class masks of PARTIAL tiles are fetched one unit ahead
+    // into registers, so their global-memory latency overlaps the previous tile's softmax.
     const int n_own = n_own_s[i];
     const uint32_t* wcmd = sWcmd + i * 256;
     uint32_t kd_pre[NW];
@@ -473,20 +470,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       int buf = wcmd_buf(cmd) + buf_off;
       if (buf >= C::NBUF) buf -= C::NBUF;
       const uint32_t tS = tbase + lane_base + buf * 128;
-      uint32_t tb[3][NW];
-      if (cls == KD_TILE_PARTIAL) {
-        __syncwarp();
-#pragma unroll
-        for (int w = 0; w < NW; ++w) {
-          kd_buf[w * 32 + lane] = kd_pre[w];
-          tb[0][w] = tb_pre[0][w]; tb[1][w] = tb_pre[1][w]; tb[2][w] = tb_pre[2][w];
-        }
-        __syncwarp();
-      }
-      if (k + 1 < n_own || hh + 1 < nh) {   // the next head walks the same list again
-        cmd_next = wcmd[k + 1 < n_own ? k + 1 : 0];
-        prefetch_kd(cmd_next);
-      }
       ok = mbar_wait(smem_u32(&bar_s_full[2 * buf + i]), (sfull_par >> buf) & 1u, &abortf, a.status, W_F_SFULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -507,33 +490,48 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         // operations; only the "same span" term needs the individual key descriptors.
         const int j0 = kt * KD_TILE;
         uint32_t mk[NW];
-        query_row_mask<NW>(qd, qi, j0, tb[0], tb[1], tb[2], mk);
+        query_row_mask<NW>(qd, qi, j0, tb_pre[0], tb_pre[1], tb_pre[2], mk);
         uint32_t any_ins = 0u;
 #pragma unroll
-        for (int w = 0; w < NW; ++w) any_ins |= tb[2][w];
-        if (any_ins != 0u && __any_sync(0xffffffffu, (qd & TD_SIDPOS) != 0u)) {
-          const uint32_t key = span_key_of_query(qd);
+        for (int w = 0; w < NW; ++w) any_ins |= tb_pre[2][w];
+        // "same span": one round per distinct span among the warp's 32 queries; a ballot over the lanes' key descriptors
+        // gives the keys of that span, 32 at a time
+        const uint32_t my_key = span_key_of_query(qd);
+        uint32_t todo = (any_ins != 0u) ? __ballot_sync(0xffffffffu, (qd & TD_SIDPOS) != 0u) : 0u;
+        while (todo != 0u) {
+          const uint32_t kq = __shfl_sync(0xffffffffu, my_key, __ffs(todo) - 1);
+          const bool mine = (my_key == kq);
 #pragma unroll
-          for (int j = 0; j < CW; j += 4) {
-            const uint4 k4 = *reinterpret_cast<const uint4*>(kd_buf + j);
-            mk[j >> 5] |= (span_match_key(key, k4.x) << ((j + 0) & 31)) | (span_match_key(key, k4.y) << ((j + 1) & 31)) |
-                          (span_match_key(key, k4.z) << ((j + 2) & 31)) | (span_match_key(key, k4.w) << ((j + 3) & 31));
+          for (int w = 0; w < NW; ++w) {
+            const uint32_t hit = __ballot_sync(0xffffffffu, span_match_key(kq, kd_pre[w]) != 0u);
+            if (mine) mk[w] |= hit;
           }
+          todo &= ~__ballot_sync(0xffffffffu, mine);
         }
 #pragma unroll
-        for (int j = 0; j < CW; ++j)
-          if ((mk[j >> 5] & (1u << (j & 31))) == 0u) sc[j] = -INFINITY;
+        for (int w = 0; w < NW; ++w) {
+          if (__all_sync(0xffffffffu, mk[w] == 0xFFFFFFFFu)) continue;   // all 32 keys visible to all 32 queries
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if ((mk[w] & (1u << j)) == 0u) sc[w * 32 + j] = -INFINITY;
+        }
+      }
+      if (k + 1 < n_own || hh + 1 < nh) {   // the next head walks the same list again
+        cmd_next = wcmd[k + 1 < n_own ? k + 1 : 0];
+        prefetch_kd(cmd_next);
       }
       // four independent chains for the row maximum and for the row sum: a single chain of
       // dependent operations would be latency-bound
       float mx4[4] = {sc[0], sc[1], sc[2], sc[3]};
 #pragma unroll
-      for (int j = 4; j < CW; j += 4) {
-        mx4[0] = fmaxf(mx4[0], sc[j + 0]);
-        mx4[1] = fmaxf(mx4[1], sc[j + 1]);
-        mx4[2] = fmaxf(mx4[2], sc[j + 2]);
-        mx4[3] = fmaxf(mx4[3], sc[j + 3]);
+      for (int j = 4; j + 8 <= CW; j += 8) {   // three-input maximum: two new scores per instruction
+        mx4[0] = fmax3(mx4[0], sc[j + 0], sc[j + 4]);
+        mx4[1] = fmax3(mx4[1], sc[j + 1], sc[j + 5]);
+        mx4[2] = fmax3(mx4[2], sc[j + 2], sc[j + 6]);
+        mx4[3] = fmax3(mx4[3], sc[j + 3], sc[j + 7]);
       }
+#pragma unroll
+      for (int k4 = 0; k4 < 4; ++k4) mx4[k4] = fmaxf(mx4[k4], sc[CW - 4 + k4]);
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // The running maximum is refreshed only when it would grow by more than 2^8 in the
       // exponent; until then the stale value is used consistently for P, l and O, which leaves
