@@ -43,7 +43,7 @@ struct BwdCfg {
   static constexpr int CPT = 2 / NSUB;                // 32-column chunks per compute thread and unit
   static constexpr int THREADS = 128 + 256 * NSUB;    // four light warps + 2 * NSUB compute warpgroups
   static constexpr int REGS_COMPUTE = KD_REGS_COMPUTE_BWD;
-  static constexpr int STAGE_WORDS = 3 * 32 * CPT;                 // per warp: 32*CPT x {lse, delta, descriptor}
+  static constexpr int STAGE_WORDS = 2 * 32 * CPT;                 // per warp (dK/dV kernel): 32*CPT x {lse, delta}
   static constexpr int SMEM_ACT = SMEM_STAGE + 8 * NSUB * STAGE_WORDS * 4;  // compacted entry list
   static constexpr int SMEM_TOTAL = SMEM_ACT + 128 * 2;
   static constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;
@@ -322,7 +322,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int qi = qt * KD_TILE + row;
     const bool q_valid = qi < a.T;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
-    uint32_t* kd_buf = sStage + (size_t)(warp - 4) * C::STAGE_WORDS;
     const float c = a.scale_log2;
     const uint32_t qd = a.desc[(size_t)b * a.Tpad + qi];
     const int tbw = 2 * i + c0;      // first word of this thread's chunks in the 128-bit class masks of a key tile
@@ -372,22 +371,23 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int cc = 0; cc < CPT; ++cc) mk[cc] = 0xFFFFFFFFu;
         if (cls == KD_TILE_PARTIAL) {
           const int j0 = (ent & 0xFF) * KD_TILE + i * 64 + c0 * 32;  // first key handled here
-          __syncwarp();
-#pragma unroll
-          for (int cc = 0; cc < CPT; ++cc) kd_buf[cc * 32 + lane] = kd_pre[cc];
-          __syncwarp();
           query_row_mask<CPT>(qd, qi, j0, tb_pre[0], tb_pre[1], tb_pre[2], mk);
           uint32_t any_ins = 0u;
 #pragma unroll
           for (int cc = 0; cc < CPT; ++cc) any_ins |= tb_pre[2][cc];
-          if (any_ins != 0u && __any_sync(0xffffffffu, (qd & TD_SIDPOS) != 0u)) {
-            const uint32_t key = span_key_of_query(qd);
+          // "same span": one round per distinct span among the warp's 32 queries; a ballot over the lanes' key descriptors
+          // (lane L holds keys L, 32 + L, ... of the chunks) gives the keys of that span, 32 at a time
+          const uint32_t my_key = span_key_of_query(qd);
+          uint32_t todo = (any_ins != 0u) ? __ballot_sync(0xffffffffu, (qd & TD_SIDPOS) != 0u) : 0u;
+          while (todo != 0u) {
+            const uint32_t kq = __shfl_sync(0xffffffffu, my_key, __ffs(todo) - 1);
+            const bool mine = (my_key == kq);
 #pragma unroll
-            for (int j = 0; j < 32 * CPT; j += 4) {
-              const uint4 k4 = *reinterpret_cast<const uint4*>(kd_buf + j);
-              mk[j >> 5] |= (span_match_key(key, k4.x) << ((j + 0) & 31)) | (span_match_key(key, k4.y) << ((j + 1) & 31)) |
-                            (span_match_key(key, k4.z) << ((j + 2) & 31)) | (span_match_key(key, k4.w) << ((j + 3) & 31));
+            for (int cc = 0; cc < CPT; ++cc) {
+              const uint32_t hit = __ballot_sync(0xffffffffu, span_match_key(kq, kd_pre[cc]) != 0u);
+              if (mine) mk[cc] |= hit;
             }
+            todo &= ~__ballot_sync(0xffffffffu, mine);
           }
         }
         // the next entry: of this head or, at the end of the list, the first one again for the next head
@@ -692,7 +692,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const int kj = kt * KD_TILE + row;   // this thread's key
     const bool k_valid = kj < a.T;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
-    uint32_t* st_buf = sStage + (size_t)(warp - 4) * C::STAGE_WORDS;  // [QW lse][QW delta][QW desc]
+    uint32_t* st_buf = sStage + (size_t)(warp - 4) * C::STAGE_WORDS;  // [QW lse][QW delta]
     const float c = a.scale_log2;
     const uint32_t kdesc = a.desc[(size_t)b * a.Tpad + kj];
     const int tbw = 2 * i + c0;      // first word of this thread's chunks in the 128-bit class masks of a query tile
@@ -751,7 +751,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         for (int cc = 0; cc < CPT; ++cc) {
           st_buf[cc * 32 + lane] = __float_as_uint(pre_lse[cc]);
           st_buf[QW + cc * 32 + lane] = __float_as_uint(pre_delta[cc]);
-          st_buf[2 * QW + cc * 32 + lane] = pre_desc[cc];
         }
         __syncwarp();
         uint32_t mk[CPT];   // visibility of this key for the chunks' queries
@@ -763,14 +762,19 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           uint32_t any_armed = 0u;
 #pragma unroll
           for (int cc = 0; cc < CPT; ++cc) any_armed |= tb_pre[4][cc];
-          if (any_armed != 0u && __any_sync(0xffffffffu, (kdesc & TD_INS) != 0u)) {
-            const uint32_t key = span_key_of_key(kdesc);
+          // "same span": one round per distinct span among the warp's 32 keys; a ballot over the lanes' query descriptors
+          // (lane L holds queries L, 32 + L, ... of the chunks) gives the queries of that span, 32 at a time
+          const uint32_t my_key = span_key_of_key(kdesc);
+          uint32_t todo = (any_armed != 0u) ? __ballot_sync(0xffffffffu, (kdesc & TD_INS) != 0u) : 0u;
+          while (todo != 0u) {
+            const uint32_t kk = __shfl_sync(0xffffffffu, my_key, __ffs(todo) - 1);
+            const bool mine = (my_key == kk);
 #pragma unroll
-            for (int j = 0; j < QW; j += 4) {
-              const uint4 q4 = *reinterpret_cast<const uint4*>(st_buf + 2 * QW + j);
-              mk[j >> 5] |= (span_match_query(key, q4.x) << ((j + 0) & 31)) | (span_match_query(key, q4.y) << ((j + 1) & 31)) |
-                            (span_match_query(key, q4.z) << ((j + 2) & 31)) | (span_match_query(key, q4.w) << ((j + 3) & 31));
+            for (int cc = 0; cc < CPT; ++cc) {
+              const uint32_t hit = __ballot_sync(0xffffffffu, span_match_query(kk, pre_desc[cc]) != 0u);
+              if (mine) mk[cc] |= hit;
             }
+            todo &= ~__ballot_sync(0xffffffffu, mine);
           }
         }
         // the next entry: of this head or, at the end of the list, the first one again for the next head

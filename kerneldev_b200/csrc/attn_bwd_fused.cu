@@ -91,7 +91,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   uint16_t* sList = reinterpret_cast<uint16_t*>(smem + C::SMEM_LIST);
 
   __shared__ __align__(8) uint64_t bar_fix_full[C::NFIX], bar_fix_empty[C::NFIX], bar_ring_full[C::STAGES],
-      bar_ring_empty[C::STAGES], bar_s_full[2], bar_sp_free[2], bar_p_full, bar_pt_free, bar_acc_full, bar_acc_free,
+      bar_ring_empty[C::STAGES], bar_s_full[2], bar_sp_free[2], bar_p_full[2], bar_pt_free[2], bar_acc_full, bar_acc_free,
       bar_dq_full, bar_dq_empty, bar_ds_empty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ AbortFlag abortf;
@@ -117,10 +117,13 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     mbar_init(smem_u32(&bar_s_full[1]), 1);
     // the warps of a role arrive once each (lane 0, after a warp-wide sync): hundreds of single-thread arrivals on one
     // barrier would serialise in the shared-memory atomic unit
-    mbar_init(smem_u32(&bar_sp_free[0]), 16);  // every compute warp has loaded its S^T and dP^T columns of the half
-    mbar_init(smem_u32(&bar_sp_free[1]), 16);
-    mbar_init(smem_u32(&bar_p_full), 16);      // P^T is in TMEM and dS^T in shared memory
-    mbar_init(smem_u32(&bar_pt_free), 1);      // the dV product has read P^T
+    // every barrier of a half is used by the two compute warpgroups (8 warps) that own the half
+    mbar_init(smem_u32(&bar_sp_free[0]), 8);   // the warps have loaded their S^T and dP^T columns
+    mbar_init(smem_u32(&bar_sp_free[1]), 8);
+    mbar_init(smem_u32(&bar_p_full[0]), 8);    // P^T of the half is in TMEM and its dS^T block in shared memory
+    mbar_init(smem_u32(&bar_p_full[1]), 8);
+    mbar_init(smem_u32(&bar_pt_free[0]), 1);   // the dV products have read the half's P^T
+    mbar_init(smem_u32(&bar_pt_free[1]), 1);
     mbar_init(smem_u32(&bar_dq_full), 1);
     mbar_init(smem_u32(&bar_dq_empty), 4);     // the dQ warps have read the dQ tile out of TMEM
     mbar_init(smem_u32(&bar_ds_empty[0]), 1);  // a dS^T buffer is free: its products and the reduction staged in it are done
@@ -268,13 +271,17 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
         for (int e = 0; e < n && ok; ++e) {
           const uint32_t dob = loRingMN + stage * (2 * C::TILE_BYTES >> 4) + (C::TILE_BYTES >> 4);
-          ok = mbar_wait(smem_u32(&bar_p_full), t & 1, &abortf, a.status, W_U_PFULL);
-          if (!ok) break;
-          tc_fence_after_sync();
-          mma_ts_split(tDV, tPT, dob, hi, idesc_dv, e > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 1; kk < KD_TILE / 16; ++kk) mma_ts_split(tDV, tPT + kk * 8, dob + koff_mnmajor(kk), hi, idesc_dv, 1u);
-          mma_commit(smem_u32(&bar_pt_free));
+          for (int half = 0; half < 2; ++half) {   // 64 queries of the product's inner dimension at a time
+            ok = mbar_wait(smem_u32(&bar_p_full[half]), t & 1, &abortf, a.status, W_U_PFULL);
+            if (!ok) break;
+            tc_fence_after_sync();
+#pragma unroll
+            for (int kk = 4 * half; kk < 4 * half + 4; ++kk)
+              mma_ts_split(tDV, tPT + kk * 8, dob + koff_mnmajor(kk), hi, idesc_dv, (e > 0 || kk > 0) ? 1u : 0u);
+            mma_commit(smem_u32(&bar_pt_free[half]));
+          }
+          if (!ok) break;
           mma_commit(smem_u32(&bar_ring_empty[stage]));   // one of two: dO of the stage is no longer read
           ++t;
           if (++stage == C::STAGES) stage = 0;
@@ -302,12 +309,16 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           const uint32_t qb = loRingMN + stage * (2 * C::TILE_BYTES >> 4);
           const uint32_t dsK = desc_lo_kmajor(sDS + tb * (2 * C::TILE_BYTES));     // dS^T as [keys][queries]: K-major A of dK
           const uint32_t dsMN = desc_lo_mnmajor(sDS + tb * (2 * C::TILE_BYTES));   // the same bytes as MN-major A of dQ
-          ok = mbar_wait(smem_u32(&bar_p_full), t & 1, &abortf, a.status, W_U_PFULL);
-          if (!ok) break;
-          tc_fence_after_sync();
-          mma_ss_split(tDK, dsK, qb, hi, idesc_dk, e > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 1; kk < KD_TILE / 16; ++kk) mma_ss_split(tDK, dsK + koff_kmajor(kk), qb + koff_mnmajor(kk), hi, idesc_dk, 1u);
+          for (int half = 0; half < 2; ++half) {
+            ok = mbar_wait(smem_u32(&bar_p_full[half]), t & 1, &abortf, a.status, W_U_PFULL);
+            if (!ok) break;
+            tc_fence_after_sync();
+#pragma unroll
+            for (int kk = 4 * half; kk < 4 * half + 4; ++kk)
+              mma_ss_split(tDK, dsK + koff_kmajor(kk), qb + koff_mnmajor(kk), hi, idesc_dk, (e > 0 || kk > 0) ? 1u : 0u);
+          }
+          if (!ok) break;
           mma_commit(smem_u32(&bar_ring_empty[stage]));   // two of two: Q of the stage is no longer read
           if (t > 0) {   // the dQ warpgroup must have read the previous tile's dQ out of TMEM
             ok = mbar_wait(smem_u32(&bar_dq_empty), (t - 1) & 1, &abortf, a.status, W_U_DQEMPTY);
@@ -330,10 +341,11 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   } else if (warp < 20) {
     reg_alloc<C::REGS_COMPUTE>();
     // ------------------------------ compute warpgroups ------------------------------
-    // warpgroup g handles queries 16 g .. 16 g + 15 (first half of the tile's columns) and 64 + 16 g .. 64 + 16 g + 15 (second
-    // half): every warp is done with the first 64 columns of S^T and dP^T after its first pair of loads, so the next tile's
-    // products for those columns are issued while this tile's arithmetic is still running
+    // warpgroup g handles queries 32 g .. 32 g + 31 of every tile, a key row per thread. Warpgroups 0 and 1 own the first half of
+    // the tile's columns, 2 and 3 the second; the halves have their own barriers throughout, so the two pairs of warpgroups run
+    // as independent pipelines that drift apart in time: one does arithmetic while the other waits, loads or stores.
     const int g = (warp - 4) >> 2;
+    const int half = g >> 1;
     const int wq = warp & 3;
     const int row = wq * 32 + lane;
     const int kj = kt * KD_TILE + row;   // this thread's key
@@ -341,19 +353,18 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
     const float c = a.scale_log2;
     const uint32_t kdesc = a.desc[(size_t)b * a.Tpad + kj];
-    // this thread's bytes of its key's row in dS^T: 16-byte chunks 2 g, 2 g + 1 of block 0 and of block 1, swizzled with the row
-    const uint32_t ds_row = static_cast<uint32_t>(row) * 128u;
+    // this thread's 64 bytes of its key's row in dS^T block g / 2: 16-byte chunks 4 (g % 2) .. + 3, swizzled with the row
+    const uint32_t ds_row = static_cast<uint32_t>(half) * C::TILE_BYTES + static_cast<uint32_t>(row) * 128u;
     const uint32_t ds_sw = static_cast<uint32_t>(row & 7);
     bool ok = true;
 
-    const uint32_t tb_sel = (g & 1) ? 0x7632u : 0x5410u;   // bits 0-15: queries 16 g .. of the tile, bits 16-31: queries 64 + 16 g ..
     int stage = 0;
     uint32_t ring_parity = 0;
     int t = 0;   // tiles so far, over all heads
-    const uint32_t tS = tbase + lane_base + C::TM_S + g * 16, tP = tbase + lane_base + C::TM_DP + g * 16;   // + 64 for the second half
-    const uint32_t tPT = tbase + lane_base + C::TM_PT + g * 8;                                                // + 32 for the second half
-    const uint32_t b_sfull = smem_u32(&bar_s_full[0]), b_spfree = smem_u32(&bar_sp_free[0]), b_pfull = smem_u32(&bar_p_full),
-                   b_ptfree = smem_u32(&bar_pt_free);
+    const uint32_t tS = tbase + lane_base + C::TM_S + g * 32, tP = tbase + lane_base + C::TM_DP + g * 32;
+    const uint32_t tPT = tbase + lane_base + C::TM_PT + g * 16;
+    const uint32_t b_sfull = smem_u32(&bar_s_full[half]), b_spfree = smem_u32(&bar_sp_free[half]), b_pfull = smem_u32(&bar_p_full[half]),
+                   b_ptfree = smem_u32(&bar_pt_free[half]);
 
     for (int hh = 0; hh < nh && ok; ++hh) {
       const int h = h0 + hh;
@@ -364,20 +375,17 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         ok = mbar_wait(smem_u32(&bar_ring_full[stage]), ring_parity, &abortf, a.status, W_U_RINGFULL);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        const uint32_t* side = sSide + stage * C::SIDE_WORDS + g * 16;   // this warpgroup's first group of 16 queries; the second is 64 on
+        const uint32_t* side = sSide + stage * C::SIDE_WORDS + g * 32;   // this warpgroup's 32 queries
         if (++stage == C::STAGES) { stage = 0; ring_parity ^= 1; }
         uint32_t mk = 0xFFFFFFFFu;   // visibility of this key for the 32 queries
         if (cls == KD_TILE_PARTIAL) {
-          // query-side class masks: the two words that hold this warpgroup's groups of 16 queries, combined into one
-          const uint32_t* tbw = side - g * 16 + 3 * KD_TILE + (g >> 1);
-          auto two_groups = [&](int k) { return __byte_perm(tbw[4 * k], tbw[4 * k + 2], tb_sel); };
-          const int i0 = (ent & 0xFF) * KD_TILE + g * 16;  // first query of the first group; the second starts 64 later
-          const uint32_t causal = (~low_bits(kj - i0) & 0xFFFFu) | (~low_bits(kj - i0 - 64) << 16);   // queries i >= this key
-          mk = key_row_mask_word(kdesc, causal, two_groups(TB_SEES_PRE), two_groups(TB_SEES_CTX), two_groups(TB_SEES_INS), two_groups(TB_CTX));
-          if (two_groups(TB_SIDPOS) != 0u) {
+          const uint32_t* tbw = side - g * 32 + 3 * KD_TILE + g;   // word g of every query-side class mask
+          const int i0 = (ent & 0xFF) * KD_TILE + g * 32;          // first query handled here
+          key_row_mask<1>(kdesc, kj, i0, tbw + 4 * TB_SEES_PRE, tbw + 4 * TB_SEES_CTX, tbw + 4 * TB_SEES_INS, tbw + 4 * TB_CTX, &mk);
+          if (tbw[4 * TB_SIDPOS] != 0u) {
             // "same span": lane L holds the descriptor of query number L of this warpgroup; one round per distinct span among
             // the warp's 32 keys, each a ballot over the queries
-            const uint32_t qd_lane = side[2 * KD_TILE + (lane & 15) + (lane >> 4) * 64];
+            const uint32_t qd_lane = side[2 * KD_TILE + lane];
             const uint32_t my_key = span_key_of_key(kdesc);
             uint32_t todo = __ballot_sync(0xffffffffu, (kdesc & TD_INS) != 0u);
             while (todo != 0u) {
@@ -391,26 +399,27 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
         const int tb = t & 1;
         const uint32_t ds_base = sDS + tb * (2 * C::TILE_BYTES) + ds_row;
+        ok = mbar_wait(b_sfull, t & 1, &abortf, a.status, half ? W_U_SFULL1 : W_U_SFULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {   // 16 queries at a time: one group of each half of the tile's columns
+        for (int hf = 0; hf < 2; ++hf) {   // 16 queries at a time
           uint32_t pk_p[8], pk_ds[8];
           uint32_t rs[16], rp[16];
-          ok = mbar_wait(b_sfull + hf * 8, t & 1, &abortf, a.status, hf ? W_U_SFULL1 : W_U_SFULL);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after_sync();
-          tmem_ld16(tS + hf * 64, rs);
-          tmem_ld16(tP + hf * 64, rp);
+          tmem_ld16(tS + hf * 16, rs);
+          tmem_ld16(tP + hf * 16, rp);
           tmem_wait_ld();
-          // the values are in registers: the next tile's S^T and dP^T may overwrite this half's columns
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(b_spfree + hf * 8);
+          if (hf == 1) {   // all of this warp's values are in registers: the next tile's S^T and dP^T may overwrite the half's columns
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(b_spfree);
+          }
           const uint32_t mh = mk >> (hf * 16);
 #pragma unroll
           for (int j = 0; j < 16; j += 4) {
-            const float4 l4 = *reinterpret_cast<const float4*>(side + hf * 64 + j);             // LSE of 4 queries
-            const float4 d4 = *reinterpret_cast<const float4*>(side + KD_TILE + hf * 64 + j);   // delta of 4 queries
+            const float4 l4 = *reinterpret_cast<const float4*>(side + hf * 16 + j);             // LSE of 4 queries
+            const float4 d4 = *reinterpret_cast<const float4*>(side + KD_TILE + hf * 16 + j);   // delta of 4 queries
             const float lw[4] = {l4.x, l4.y, l4.z, l4.w}, dw[4] = {d4.x, d4.y, d4.z, d4.w};
             float pv[4], ds[4];
 #pragma unroll
@@ -436,10 +445,10 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             if (!ok) break;
             tc_fence_after_sync();
           }
-          tmem_st8(tPT + hf * 32, pk_p);
-          const uint32_t ch = static_cast<uint32_t>(2 * g);
-          st_shared_v4(ds_base + hf * C::TILE_BYTES + (((ch + 0u) ^ ds_sw) << 4), pk_ds[0], pk_ds[1], pk_ds[2], pk_ds[3]);
-          st_shared_v4(ds_base + hf * C::TILE_BYTES + (((ch + 1u) ^ ds_sw) << 4), pk_ds[4], pk_ds[5], pk_ds[6], pk_ds[7]);
+          tmem_st8(tPT + hf * 8, pk_p);
+          const uint32_t ch = static_cast<uint32_t>(4 * (g & 1) + 2 * hf);
+          st_shared_v4(ds_base + (((ch + 0u) ^ ds_sw) << 4), pk_ds[0], pk_ds[1], pk_ds[2], pk_ds[3]);
+          st_shared_v4(ds_base + (((ch + 1u) ^ ds_sw) << 4), pk_ds[4], pk_ds[5], pk_ds[6], pk_ds[7]);
         }
         if (!ok) break;
         fence_proxy_async_smem();   // the dK and dQ products read these shared-memory writes through the async proxy

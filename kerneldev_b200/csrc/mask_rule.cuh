@@ -103,15 +103,6 @@ __host__ __device__ __forceinline__ void key_row_mask(uint32_t kdesc, int j, int
   }
 }
 
-// The same for one word of 32 queries that are not consecutive: the caller supplies `causal`, the bits of the queries
-// i >= j, and the query-side mask bits in the same order.
-__host__ __device__ __forceinline__ uint32_t key_row_mask_word(uint32_t kdesc, uint32_t causal, uint32_t q_sees_pre,
-                                                               uint32_t q_sees_ctx, uint32_t q_sees_ins, uint32_t q_ctx) {
-  const uint32_t is_pre = (kdesc & TD_PRE) ? 0xFFFFFFFFu : 0u, is_ctx = (kdesc & TD_CTX) ? 0xFFFFFFFFu : 0u,
-                 is_ins = (kdesc & TD_INS) ? 0xFFFFFFFFu : 0u;
-  return (q_sees_pre & is_pre) | (is_ctx & (q_sees_ctx | (q_ctx & causal))) | (q_sees_ins & is_ins);
-}
-
 // "same span" term for one pair of descriptors
 __host__ __device__ __forceinline__ bool same_span(uint32_t qd, uint32_t kdesc) {
   return ((qd & TD_SIDPOS) != 0u) && ((kdesc & TD_INS) != 0u) && (((qd ^ kdesc) >> TD_SID_SHIFT) == 0u);
