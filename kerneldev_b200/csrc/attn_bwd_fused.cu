@@ -4,7 +4,7 @@
 // worker (original_kernel.py:1173-1336, :1339-1525) and so forms S = Q K^T, dP = dO V^T and the
 // exponentials twice per tile: 7 matrix products and two exponential passes. This kernel is key-tile
 // major like the dK/dV worker and forms them once: per (query tile, key tile)
-//     S^T = K Q^T, dP^T = V dO^T                           (smem x smem -> TMEM, N = 128 queries)
+//     S^T = K Q^T, dP^T = V dO^T                           (smem x smem -> TMEM, in two halves of 64 queries)
 //     P^T = exp2(S^T c - LSE), dS^T = P^T (dP^T - delta)   (compute warps; 16-bit results)
 //     dV += P^T dO                                         (P^T read from TMEM as the A operand)
 //     dK += dS^T Q,  dQ_tile = dS K                        (dS^T written to shared memory once and read by
@@ -18,15 +18,20 @@
 // which the products have finished reading by then.
 //
 // Pipeline. P^T has its own TMEM columns and dS^T goes to shared memory, so the S^T / dP^T columns are free
-// again as soon as the compute warps have LOADED them: the products of the next tile are issued then and run
-// while the compute warps do this tile's arithmetic, and the accumulating products of this tile run while
-// they work on the next one. Every TMEM region is therefore single-buffered (S^T 128 + dP^T 128 + P^T 64 +
-// dK 64 + dV 64 + dQ 64 = 512 columns); only dS^T in shared memory is double-buffered.
+// again as soon as the compute warps have LOADED them. The tile's 128 query columns are two halves with
+// their own barriers throughout: warpgroups 0-1 own the first half, 2-3 the second, the S^T / dP^T products
+// of a half (N = 64) are issued as soon as that half's columns have been loaded, and dV and dK take a half's
+// 64 queries of their inner dimension as soon as that half's P^T / dS^T are written. The two pairs of
+// warpgroups therefore run as two pipelines that drift apart in time, and the accumulating products of a
+// tile run while the compute warps work on the next one. Every TMEM region is single-buffered (S^T 128 +
+// dP^T 128 + P^T 64 + dK 64 + dV 64 + dQ 64 = 512 columns); only dS^T in shared memory is double-buffered.
 //
-// 768 threads: warp 0 TMA producer; warp 3 issues S^T and dP^T; warp 1 issues dV and warp 2 dK and dQ
-// (24 products per tile from one thread would make that thread the slowest stage); warps 4-19 are four
-// compute warpgroups (32 query columns each, a key row per thread); warps 20-23 move finished dQ tiles
-// from TMEM to the scratch.
+// 768 threads: warp 0 producer (lane 0 issues the TMA loads of Q and dO; all lanes copy LSE, delta, token
+// descriptors and mask words of the stage's 128 queries to shared memory, so that compute warps find them
+// there and issue no global loads); warp 3 issues S^T and dP^T; warp 1 issues dV and warp 2 dK and dQ (24
+// products per tile from one thread would make that thread the slowest stage); warps 4-19 are four compute
+// warpgroups (32 query columns each, a key row per thread); warps 20-23 move finished dQ tiles from TMEM to
+// the scratch.
 #include <algorithm>
 
 #include "attn_bwd.cuh"
