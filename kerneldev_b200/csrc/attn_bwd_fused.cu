@@ -43,9 +43,12 @@ struct FusedCfg {
   static constexpr int TILE_BYTES = KD_TILE * HD * 2;
   static constexpr int STAGES = 3;                   // ring of streamed (Q, dO) tile pairs: a stage is held from its TMA load until
                                                      // the tile's dV and dK products have completed, about two tile periods
-  static constexpr int NFIX = 1;                     // resident (K, V) pair
-  static constexpr int SMEM_FIX = 0;
-  static constexpr int SMEM_RING = SMEM_FIX + NFIX * 2 * TILE_BYTES;
+  // resident tiles of the CTA's key tile: K in two buffers (head hh in buffer hh % 2), V in one. V's last reader in a head
+  // is a dP^T product, issued about one tile before the head ends, so the next head's V lands in time without a second
+  // buffer; K's last reader is the head's last dQ product, so the next head's K has to be there already.
+  static constexpr int SMEM_K = 0;
+  static constexpr int SMEM_V = SMEM_K + 2 * TILE_BYTES;
+  static constexpr int SMEM_RING = SMEM_V + TILE_BYTES;
   static constexpr int SMEM_DS = SMEM_RING + STAGES * 2 * TILE_BYTES;   // 2 x dS^T of a query tile: two [128 keys][64 queries] blocks
   // per ring stage, beside the tiles: LSE, delta and token descriptor of the stage's 128 queries and the 32 mask words of
   // the query tile, copied there by the producer warp
@@ -68,7 +71,7 @@ struct FusedCfg {
 enum : uint32_t {
   W_U_FIXFULL = 0x401, W_U_RINGEMPTY = 0x402, W_U_RINGFULL = 0x403, W_U_PFULL = 0x404, W_U_SFULL = 0x405,
   W_U_ACCFULL = 0x406, W_U_SPFREE = 0x407, W_U_FIXEMPTY = 0x408, W_U_ACCFREE = 0x409, W_U_DQFULL = 0x40A,
-  W_U_DQEMPTY = 0x40B, W_U_DSEMPTY = 0x40C, W_U_PTFREE = 0x40D, W_U_SFULL1 = 0x40E, W_U_SPFREE1 = 0x40F,
+  W_U_DQEMPTY = 0x40B, W_U_DSEMPTY = 0x40C, W_U_PTFREE = 0x40D, W_U_SFULL1 = 0x40E, W_U_SPFREE1 = 0x40F, W_U_VFULL = 0x410,
 };
 
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
@@ -89,14 +92,15 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   constexpr int HD = C::HD;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const uint32_t sFix = smem_u32(smem + C::SMEM_FIX);    // buffer f: K at +0, V at +TILE_BYTES
+  const uint32_t sK = smem_u32(smem + C::SMEM_K);        // K of head hh at + (hh % 2) TILE_BYTES
+  const uint32_t sV = smem_u32(smem + C::SMEM_V);
   const uint32_t sRing = smem_u32(smem + C::SMEM_RING);  // stage s: Q at +0, dO at +TILE_BYTES
   const uint32_t sDS = smem_u32(smem + C::SMEM_DS);      // buffer t: block 0 (queries 0-63) at +0, block 1 at +TILE_BYTES
   uint32_t* sSide = reinterpret_cast<uint32_t*>(smem + C::SMEM_SIDE);
   uint16_t* sList = reinterpret_cast<uint16_t*>(smem + C::SMEM_LIST);
 
-  __shared__ __align__(8) uint64_t bar_fix_full[C::NFIX], bar_fix_empty[C::NFIX], bar_ring_full[C::STAGES],
-      bar_ring_empty[C::STAGES], bar_s_full[2], bar_sp_free[2], bar_p_full[2], bar_pt_free[2], bar_acc_full, bar_acc_free,
+  __shared__ __align__(8) uint64_t bar_k_full[2], bar_k_empty[2], bar_v_full, bar_v_empty, bar_ring_full[C::STAGES],
+      bar_ring_empty[C::STAGES], bar_s_full[2], bar_sp_free[2], bar_p_full[2][2], bar_pt_free[2], bar_acc_full, bar_acc_free[2],
       bar_dq_full, bar_dq_empty, bar_ds_empty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ AbortFlag abortf;
@@ -109,10 +113,13 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
   if (tid == 0) {
     abortf.v = 0;
-    for (int f = 0; f < C::NFIX; ++f) {
-      mbar_init(smem_u32(&bar_fix_full[f]), 1);
-      mbar_init(smem_u32(&bar_fix_empty[f]), 2);  // the M1 issuer and the dK / dQ issuer are done with the head's K and V
+    for (int f = 0; f < 2; ++f) {
+      mbar_init(smem_u32(&bar_k_full[f]), 1);
+      mbar_init(smem_u32(&bar_k_empty[f]), 1);   // the head's last dQ product has read K (its S^T products were issued, and so
+                                                 // completed, before it: the tensor pipe runs in issue order)
     }
+    mbar_init(smem_u32(&bar_v_full), 1);
+    mbar_init(smem_u32(&bar_v_empty), 1);        // the head's last dP^T product has read V
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(smem_u32(&bar_ring_full[s]), 2);    // the TMA loads (with their byte count) and the producer warp's own copies
       mbar_init(smem_u32(&bar_ring_empty[s]), 2);   // the dV issuer and the dK / dQ issuer are done with the stage
@@ -125,8 +132,10 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     // every barrier of a half is used by the two compute warpgroups (8 warps) that own the half
     mbar_init(smem_u32(&bar_sp_free[0]), 8);   // the warps have loaded their S^T and dP^T columns
     mbar_init(smem_u32(&bar_sp_free[1]), 8);
-    mbar_init(smem_u32(&bar_p_full[0]), 8);    // P^T of the half is in TMEM and its dS^T block in shared memory
-    mbar_init(smem_u32(&bar_p_full[1]), 8);
+    // P^T of the half is in TMEM and its dS^T block in shared memory. Two barriers per half, used by even and odd tiles: with
+    // two dS^T buffers the compute warps may finish two tiles before the dK / dQ issuer has looked at the first, and a parity
+    // wait on a single barrier cannot tell "two phases on" from "not yet"
+    for (int f = 0; f < 4; ++f) mbar_init(smem_u32(&bar_p_full[f >> 1][f & 1]), 8);
     mbar_init(smem_u32(&bar_pt_free[0]), 1);   // the dV products have read the half's P^T
     mbar_init(smem_u32(&bar_pt_free[1]), 1);
     mbar_init(smem_u32(&bar_dq_full), 1);
@@ -134,7 +143,8 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     mbar_init(smem_u32(&bar_ds_empty[0]), 1);  // a dS^T buffer is free: its products and the reduction staged in it are done
     mbar_init(smem_u32(&bar_ds_empty[1]), 1);
     mbar_init(smem_u32(&bar_acc_full), 2);       // both accumulating issuers have committed the head's last products
-    mbar_init(smem_u32(&bar_acc_free), 16);    // every compute warp has read its part of dK and dV
+    mbar_init(smem_u32(&bar_acc_free[0]), 4);  // the dQ warps have read dV out of TMEM
+    mbar_init(smem_u32(&bar_acc_free[1]), 4);  // ... and dK
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -163,21 +173,22 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         tma_prefetch_desc(&tmV);
         tma_prefetch_desc(&tmDO);
       }
-      int issued = 0, fix_issued = 0;   // ring entries / resident pairs requested so far, over all heads
+      int issued = 0;   // ring entries requested so far, over all heads
       bool ok = true;
-      for (int hh = 0; hh < nh && ok; ++hh) {
-        const int h = h0 + hh, fb = hh % C::NFIX;
-        if (lane == 0) {
-          if (hh >= C::NFIX) ok = mbar_wait(smem_u32(&bar_fix_empty[fb]), (hh / C::NFIX - 1) & 1, &abortf, a.status, W_U_FIXEMPTY);
-          if (ok) {
-            mbar_arrive_expect_tx(smem_u32(&bar_fix_full[fb]), 2 * C::TILE_BYTES);
-            tma_load_4d(sFix + fb * 2 * C::TILE_BYTES, &tmK, smem_u32(&bar_fix_full[fb]), 0, kt * KD_TILE, h, b);
-            tma_load_4d(sFix + fb * 2 * C::TILE_BYTES + C::TILE_BYTES, &tmV, smem_u32(&bar_fix_full[fb]), 0, kt * KD_TILE, h, b);
-            fix_issued = hh + 1;
-          }
+      if (lane == 0) {
+        // K and V of the first head and K of the second; later heads' tiles are requested by the issuing threads that see
+        // the buffers fall free (the dK / dQ issuer for K, the S^T / dP^T issuer for V)
+        mbar_arrive_expect_tx(smem_u32(&bar_k_full[0]), C::TILE_BYTES);
+        tma_load_4d(sK, &tmK, smem_u32(&bar_k_full[0]), 0, kt * KD_TILE, h0, b);
+        mbar_arrive_expect_tx(smem_u32(&bar_v_full), C::TILE_BYTES);
+        tma_load_4d(sV, &tmV, smem_u32(&bar_v_full), 0, kt * KD_TILE, h0, b);
+        if (nh > 1) {
+          mbar_arrive_expect_tx(smem_u32(&bar_k_full[1]), C::TILE_BYTES);
+          tma_load_4d(sK + C::TILE_BYTES, &tmK, smem_u32(&bar_k_full[1]), 0, kt * KD_TILE, h0 + 1, b);
         }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
+      }
+      for (int hh = 0; hh < nh && ok; ++hh) {
+        const int h = h0 + hh;
         const float* lse_row = a.lse + ((size_t)b * a.H + h) * a.T;
         const float* delta_row = a.delta + ((size_t)b * a.H + h) * a.T;
         for (int e = 0; e < n; ++e) {
@@ -193,8 +204,6 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           l4.z = lse_row[min(q + 2, a.T - 1)]; l4.w = lse_row[min(q + 3, a.T - 1)];
           d4.x = delta_row[min(q + 0, a.T - 1)]; d4.y = delta_row[min(q + 1, a.T - 1)];
           d4.z = delta_row[min(q + 2, a.T - 1)]; d4.w = delta_row[min(q + 3, a.T - 1)];
-          const uint4 c4 = *reinterpret_cast<const uint4*>(a.desc + (size_t)b * a.Tpad + q);   // the descriptor rows are padded to whole tiles
-          const uint32_t tbw = a.tilebits[((size_t)b * a.NT + qt) * 32 + lane];
           if (lane == 0) {
             ok = mbar_wait(smem_u32(&bar_ring_empty[s]), ph ^ 1, &abortf, a.status, W_U_RINGEMPTY);
             if (ok) {
@@ -206,6 +215,9 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           }
           ok = __shfl_sync(0xffffffffu, ok, 0);
           if (!ok) break;
+          // (descriptors and mask words are fetched after the wait: held across it they would not fit this warp's registers)
+          const uint4 c4 = *reinterpret_cast<const uint4*>(a.desc + (size_t)b * a.Tpad + q);   // the descriptor rows are padded to whole tiles
+          const uint32_t tbw = a.tilebits[((size_t)b * a.NT + qt) * 32 + lane];
           uint32_t* side = sSide + s * C::SIDE_WORDS;
           *reinterpret_cast<float4*>(side + 4 * lane) = l4;
           *reinterpret_cast<float4*>(side + KD_TILE + 4 * lane) = d4;
@@ -218,7 +230,9 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       }
       if (lane == 0 && abortf.v != 0) {   // let the copies in flight land before the CTA exits
         for (int e = max(0, issued - C::STAGES); e < issued; ++e) drain_wait(smem_u32(&bar_ring_full[e % C::STAGES]), (e / C::STAGES) & 1);
-        for (int f = max(0, fix_issued - C::NFIX); f < fix_issued; ++f) drain_wait(smem_u32(&bar_fix_full[f % C::NFIX]), (f / C::NFIX) & 1);
+        drain_wait(smem_u32(&bar_k_full[0]), 0);
+        drain_wait(smem_u32(&bar_v_full), 0);
+        if (nh > 1) drain_wait(smem_u32(&bar_k_full[1]), 0);
       }
     } else if (warp == 3 && lane == 0 && n > 0) {
       // ------- M1 issuer: per half of 64 queries, S^T = K Q^T and dP^T = V dO^T into columns 64 half .. 64 half + 63 -------
@@ -228,11 +242,12 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       bool ok = true;
       int t = 0, stage = 0;   // tiles so far and ring stage, running on across the heads
       uint32_t ring_parity = 0;
+      int v_loads = 1;        // V tiles requested so far (the first by the producer)
       for (int hh = 0; hh < nh && ok; ++hh) {
-        const int fb = hh % C::NFIX;
-        ok = mbar_wait(smem_u32(&bar_fix_full[fb]), (hh / C::NFIX) & 1, &abortf, a.status, W_U_FIXFULL);
+        ok = mbar_wait(smem_u32(&bar_k_full[hh & 1]), (hh >> 1) & 1, &abortf, a.status, W_U_FIXFULL);
         if (!ok) break;
-        const uint32_t loK = desc_lo_kmajor(sFix + fb * 2 * C::TILE_BYTES), loV = loK + (C::TILE_BYTES >> 4);
+        const uint32_t loK = desc_lo_kmajor(sK + (hh & 1) * C::TILE_BYTES), loV = desc_lo_kmajor(sV);
+        bool v_ready = false;
         for (int e = 0; e < n && ok; ++e) {
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
@@ -251,6 +266,11 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             mma_ss64<false>(tS, desc64(loK, hi), desc64(qlo, hi), idesc_m1);
 #pragma unroll
             for (int kk = 1; kk < HD / 16; ++kk) mma_ss64<true>(tS, desc64(loK + koff_kmajor(kk), hi), desc64(qlo + koff_kmajor(kk), hi), idesc_m1);
+            if (!v_ready) {   // the head's V is requested late (below), so it is waited for only where it is first needed
+              ok = mbar_wait(smem_u32(&bar_v_full), hh & 1, &abortf, a.status, W_U_VFULL);
+              if (!ok) break;
+              v_ready = true;
+            }
             mma_ss64<false>(tDP, desc64(loV, hi), desc64(dolo, hi), idesc_m1);
 #pragma unroll
             for (int kk = 1; kk < HD / 16; ++kk) mma_ss64<true>(tDP, desc64(loV + koff_kmajor(kk), hi), desc64(dolo + koff_kmajor(kk), hi), idesc_m1);
@@ -259,8 +279,20 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           ++t;
           if (++stage == C::STAGES) { stage = 0; ring_parity ^= 1; }
         }
-        if (ok) mma_commit(smem_u32(&bar_fix_empty[fb]));   // this issuer's products of the head no longer read K / V
+        if (!ok) break;
+        mma_commit(smem_u32(&bar_v_empty));           // the head's dP^T products no longer read V
+        if (hh + 1 < nh) {
+          // The next head's V goes into the same buffer: this thread waits for its own last products (a few hundred cycles,
+          // during which it has nothing else to issue: the next S^T needs columns the compute warps are still reading)
+          // and requests the tile.
+          ok = mbar_wait(smem_u32(&bar_v_empty), hh & 1, &abortf, a.status, W_U_FIXEMPTY);
+          if (!ok) break;
+          mbar_arrive_expect_tx(smem_u32(&bar_v_full), C::TILE_BYTES);
+          tma_load_4d(sV, &tmV, smem_u32(&bar_v_full), 0, kt * KD_TILE, h0 + hh + 1, b);
+          v_loads = hh + 2;
+        }
       }
+      if (abortf.v != 0 && v_loads > 1) drain_wait(smem_u32(&bar_v_full), (v_loads - 1) & 1);   // let a copy in flight land
     } else if (warp == 1 && lane == 0 && n > 0) {
       // ------- dV issuer: per tile dV += P^T dO (A from TMEM) -------
       const uint32_t idesc_dv = make_idesc_f16(kBf16, 0, 1, KD_TILE, HD);   // B = dO rows, MN-major
@@ -271,14 +303,14 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       int t = 0, stage = 0;
       for (int hh = 0; hh < nh && ok; ++hh) {
         if (hh > 0) {   // the previous head's dK and dV must have been read out of the accumulators
-          ok = mbar_wait(smem_u32(&bar_acc_free), (hh - 1) & 1, &abortf, a.status, W_U_ACCFREE);
+          ok = mbar_wait(smem_u32(&bar_acc_free[0]), (hh - 1) & 1, &abortf, a.status, W_U_ACCFREE);
           if (!ok) break;
         }
         for (int e = 0; e < n && ok; ++e) {
           const uint32_t dob = loRingMN + stage * (2 * C::TILE_BYTES >> 4) + (C::TILE_BYTES >> 4);
 #pragma unroll
           for (int half = 0; half < 2; ++half) {   // 64 queries of the product's inner dimension at a time
-            ok = mbar_wait(smem_u32(&bar_p_full[half]), t & 1, &abortf, a.status, W_U_PFULL);
+            ok = mbar_wait(smem_u32(&bar_p_full[half][t & 1]), (t >> 1) & 1, &abortf, a.status, W_U_PFULL);
             if (!ok) break;
             tc_fence_after_sync();
 #pragma unroll
@@ -302,11 +334,13 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       const uint32_t loRingMN = desc_lo_mnmajor(sRing);
       bool ok = true;
       int t = 0, stage = 0;
+      int k_loads = 2;   // K tiles requested so far (the first two by the producer)
       for (int hh = 0; hh < nh && ok; ++hh) {
-        const int fb = hh % C::NFIX;
-        const uint32_t loK = desc_lo_mnmajor(sFix + fb * 2 * C::TILE_BYTES);
+        const uint32_t loK = desc_lo_mnmajor(sK + (hh & 1) * C::TILE_BYTES);
+        ok = mbar_wait(smem_u32(&bar_k_full[hh & 1]), (hh >> 1) & 1, &abortf, a.status, W_U_FIXFULL);
+        if (!ok) break;
         if (hh > 0) {
-          ok = mbar_wait(smem_u32(&bar_acc_free), (hh - 1) & 1, &abortf, a.status, W_U_ACCFREE);
+          ok = mbar_wait(smem_u32(&bar_acc_free[1]), (hh - 1) & 1, &abortf, a.status, W_U_ACCFREE);
           if (!ok) break;
         }
         for (int e = 0; e < n && ok; ++e) {
@@ -316,7 +350,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           const uint32_t dsMN = desc_lo_mnmajor(sDS + tb * (2 * C::TILE_BYTES));   // the same bytes as MN-major A of dQ
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
-            ok = mbar_wait(smem_u32(&bar_p_full[half]), t & 1, &abortf, a.status, W_U_PFULL);
+            ok = mbar_wait(smem_u32(&bar_p_full[half][t & 1]), (t >> 1) & 1, &abortf, a.status, W_U_PFULL);
             if (!ok) break;
             tc_fence_after_sync();
 #pragma unroll
@@ -337,10 +371,22 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           ++t;
           if (++stage == C::STAGES) stage = 0;
         }
-        if (ok) {
-          mma_commit(smem_u32(&bar_acc_full));
-          mma_commit(smem_u32(&bar_fix_empty[fb]));   // the dQ products of the head no longer read K
+        if (!ok) break;
+        mma_commit(smem_u32(&bar_acc_full));
+        mma_commit(smem_u32(&bar_k_empty[hh & 1]));   // the head's dQ products no longer read K
+        if (hh + 2 < nh) {
+          // The K of the head after next goes into this head's buffer: this thread waits for its own last products (it has
+          // nothing to issue before the next tile's dS^T is written) and requests the tile, a whole head ahead of its use.
+          ok = mbar_wait(smem_u32(&bar_k_empty[hh & 1]), (hh >> 1) & 1, &abortf, a.status, W_U_FIXEMPTY);
+          if (!ok) break;
+          mbar_arrive_expect_tx(smem_u32(&bar_k_full[hh & 1]), C::TILE_BYTES);
+          tma_load_4d(sK + (hh & 1) * C::TILE_BYTES, &tmK, smem_u32(&bar_k_full[hh & 1]), 0, kt * KD_TILE, h0 + hh + 2, b);
+          k_loads = hh + 3;
         }
+      }
+      // let copies in flight land before the CTA exits: the last two requests of this thread
+      if (abortf.v != 0) {
+        for (int f = max(2, k_loads - 2); f < k_loads; ++f) drain_wait(smem_u32(&bar_k_full[f & 1]), (f >> 1) & 1);
       }
     }
   } else if (warp < 20) {
@@ -354,7 +400,6 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const int wq = warp & 3;
     const int row = wq * 32 + lane;
     const int kj = kt * KD_TILE + row;   // this thread's key
-    const bool k_valid = kj < a.T;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
     const float c = a.scale_log2;
     const uint32_t kdesc = a.desc[(size_t)b * a.Tpad + kj];
@@ -368,11 +413,10 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     int t = 0;   // tiles so far, over all heads
     const uint32_t tS = tbase + lane_base + C::TM_S + g * 32, tP = tbase + lane_base + C::TM_DP + g * 32;
     const uint32_t tPT = tbase + lane_base + C::TM_PT + g * 16;
-    const uint32_t b_sfull = smem_u32(&bar_s_full[half]), b_spfree = smem_u32(&bar_sp_free[half]), b_pfull = smem_u32(&bar_p_full[half]),
+    const uint32_t b_sfull = smem_u32(&bar_s_full[half]), b_spfree = smem_u32(&bar_sp_free[half]), b_pfull = smem_u32(&bar_p_full[half][0]),
                    b_ptfree = smem_u32(&bar_pt_free[half]);
 
     for (int hh = 0; hh < nh && ok; ++hh) {
-      const int h = h0 + hh;
       for (int e = 0; e < n; ++e) {
         const uint32_t ent = list[e];
         const uint32_t cls = ent >> 8;
@@ -460,35 +504,8 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         tmem_wait_st();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(b_pfull);
+        if (lane == 0) mbar_arrive(b_pfull + (t & 1) * 8);
         ++t;
-      }
-      if (!ok) break;
-
-      // epilogue of this head: warpgroup g stores 16 columns of dK and dV from column 16 g
-      if (n > 0) {
-        ok = mbar_wait(smem_u32(&bar_acc_full), hh & 1, &abortf, a.status, W_U_ACCFULL);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-      }
-      tc_fence_after_sync();
-      uint16_t* krow = reinterpret_cast<uint16_t*>(a.dk) + (size_t)b * a.dk_sb + (size_t)h * a.dk_sh + (size_t)kj * a.dk_st + g * 16;
-      uint16_t* vrow = reinterpret_cast<uint16_t*>(a.dv) + (size_t)b * a.dv_sb + (size_t)h * a.dv_sh + (size_t)kj * a.dv_st + g * 16;
-      uint32_t rk[16], rv[16];
-      if (n > 0) {
-        tmem_ld16(tbase + lane_base + C::TM_DK + g * 16, rk);
-        tmem_ld16(tbase + lane_base + C::TM_DV + g * 16, rv);
-        tmem_wait_ld();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bar_acc_free));   // the next head's first products may overwrite the accumulators
-      } else {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) { rk[j] = 0u; rv[j] = 0u; }
-      }
-      if (k_valid) {
-        store_row16_upto<kBf16>(krow, rk, a.sm_scale, g * 16, a.d_real);
-        store_row16_upto<kBf16>(vrow, rv, 1.0f, g * 16, a.d_real);
       }
     }
   } else {
@@ -503,8 +520,44 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const uint32_t tDQ = tbase + lane_base + C::TM_DQ;
     bool ok = true;
     int t = 0;
+    const int kj = kt * KD_TILE + row;   // this thread's key: it also writes that key's rows of dK and dV
+    // dK and dV of head number hd leave through these warps as well (a whole 128-byte row per thread): the compute warps
+    // go straight on to the next head's tiles, whose S^T / dP^T are already waiting, and the accumulating issuers wait for
+    // bar_acc_free before they overwrite the accumulators.
+    auto write_out = [&](int hd) -> bool {
+      if (n > 0) {
+        ok = mbar_wait(smem_u32(&bar_acc_full), hd & 1, &abortf, a.status, W_U_ACCFULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) return false;
+        tc_fence_after_sync();
+      }
+      const int h = h0 + hd;
+      uint16_t* krow = reinterpret_cast<uint16_t*>(a.dk) + (size_t)b * a.dk_sb + (size_t)h * a.dk_sh + (size_t)kj * a.dk_st;
+      uint16_t* vrow = reinterpret_cast<uint16_t*>(a.dv) + (size_t)b * a.dv_sb + (size_t)h * a.dv_sh + (size_t)kj * a.dv_st;
+#pragma unroll
+      for (int part = 0; part < 4; ++part) {   // dV columns 0-31, 32-63, then dK: the next head's first dV product is the
+                                               // one the compute warps wait for, so dV is released first
+        uint32_t r[32];
+        const bool is_k = part >= 2;
+        if (n > 0) {
+          tmem_ld32(tbase + lane_base + (is_k ? C::TM_DK : C::TM_DV) + (part & 1) * 32, r);
+          tmem_wait_ld();
+          if (part & 1) {   // the accumulator is in registers: the next head's first product may overwrite it
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_acc_free[is_k ? 1 : 0]));
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        if (kj < a.T) store_row32_upto<kBf16>((is_k ? krow : vrow) + (part & 1) * 32, r, is_k ? a.sm_scale : 1.0f, (part & 1) * 32, a.d_real);
+      }
+      return true;
+    };
     for (int hh = 0; hh < nh && ok; ++hh) {
       const int bh = b * a.H + h0 + hh;
+      if (n == 0) write_out(hh);
       for (int e = 0; e < n; ++e) {
         const int tb = t & 1;
         const int q0 = (list[e] & 0xFF) * KD_TILE;
@@ -537,6 +590,11 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           tma_reduce_add_3d(&tmAcc, stage, 0, q0, bh);
           tma_reduce_add_3d(&tmAcc, stage + C::TILE_BYTES, 32, q0, bh);
           bulk_commit_group();
+        }
+        // after the head's last tile its dK and dV are complete (their last products were issued before the dQ product
+        // this warpgroup has just consumed): they are written while the bulk reduction reads the staged tile
+        if (e == n - 1 && !write_out(hh)) break;
+        if (leader) {
           bulk_wait_group_read0();
           mbar_arrive(smem_u32(&bar_ds_empty[tb]));    // compute warps may write the tile after next's dS^T here
         }
