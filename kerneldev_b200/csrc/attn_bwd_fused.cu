@@ -26,12 +26,20 @@
 // tile run while the compute warps work on the next one. Every TMEM region is single-buffered (S^T 128 +
 // dP^T 128 + P^T 64 + dK 64 + dV 64 + dQ 64 = 512 columns); only dS^T in shared memory is double-buffered.
 //
+// Heads. A CTA handles several heads of its (batch, key tile) one after the other, and nothing drains between
+// them: the ring of Q / dO tiles runs on into the next head; K has two buffers (the next head's K is requested
+// a head ahead by the dK / dQ issuer, when the last dQ product of the head before has released the buffer) and
+// V one (requested by the S^T / dP^T issuer right after the head's last dP^T product, about a tile before the
+// head ends), so the next head's first products are issued while this head's last tile is still in the compute
+// warps; dK and dV of the finished head leave through the dQ warps, and only the next head's first
+// accumulating products wait for that.
+//
 // 768 threads: warp 0 producer (lane 0 issues the TMA loads of Q and dO; all lanes copy LSE, delta, token
 // descriptors and mask words of the stage's 128 queries to shared memory, so that compute warps find them
 // there and issue no global loads); warp 3 issues S^T and dP^T; warp 1 issues dV and warp 2 dK and dQ (24
 // products per tile from one thread would make that thread the slowest stage); warps 4-19 are four compute
 // warpgroups (32 query columns each, a key row per thread); warps 20-23 move finished dQ tiles from TMEM to
-// the scratch.
+// the scratch and write dK and dV at the end of each head.
 #include <algorithm>
 
 #include "attn_bwd.cuh"
