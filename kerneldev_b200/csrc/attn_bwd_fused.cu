@@ -324,6 +324,12 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
             for (int kk = 4 * half; kk < 4 * half + 4; ++kk)
               mma_ts_split(tDV, tPT + kk * 8, dob + koff_mnmajor(kk), hi, idesc_dv, (e > 0 || kk > 0) ? 1u : 0u);
+            if (half == 0 && t >= 1) {
+              // bar_pt_free of tile t also tells the compute warps that the dS^T buffer of tile t + 1 is free, i.e. that the
+              // dK / dQ products and the dQ reduction of tile t - 1 are done with it (normally long before this point)
+              ok = mbar_wait(smem_u32(&bar_ds_empty[(t + 1) & 1]), ((t - 1) >> 1) & 1, &abortf, a.status, W_U_DSEMPTY);
+              if (!ok) break;
+            }
             mma_commit(smem_u32(&bar_pt_free[half]));
           }
           if (!ok) break;
@@ -417,7 +423,6 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     bool ok = true;
 
     int stage = 0;
-    uint32_t ring_parity = 0;
     int t = 0;   // tiles so far, over all heads
     const uint32_t tS = tbase + lane_base + C::TM_S + g * 32, tP = tbase + lane_base + C::TM_DP + g * 32;
     const uint32_t tPT = tbase + lane_base + C::TM_PT + g * 16;
@@ -428,12 +433,15 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       for (int e = 0; e < n; ++e) {
         const uint32_t ent = list[e];
         const uint32_t cls = ent >> 8;
-        // the stage's scalars and mask words were written by the producer warp before its arrival on this barrier
-        ok = mbar_wait(smem_u32(&bar_ring_full[stage]), ring_parity, &abortf, a.status, W_U_RINGFULL);
+        // The stage's scalars and mask words were written by the producer warp before its arrival on the stage's barrier;
+        // the issuer of S^T waited for that barrier before the products whose completion is awaited here, so no separate
+        // wait for the stage is taken.
+        ok = mbar_wait(b_sfull, t & 1, &abortf, a.status, half ? W_U_SFULL1 : W_U_SFULL);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        tc_fence_after_sync();
         const uint32_t* side = sSide + stage * C::SIDE_WORDS + g * 32;   // this warpgroup's 32 queries
-        if (++stage == C::STAGES) { stage = 0; ring_parity ^= 1; }
+        if (++stage == C::STAGES) stage = 0;
         uint32_t mk = 0xFFFFFFFFu;   // visibility of this key for the 32 queries
         if (cls == KD_TILE_PARTIAL) {
           const uint32_t* tbw = side - g * 32 + 3 * KD_TILE + g;   // word g of every query-side class mask
@@ -456,10 +464,6 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
         const int tb = t & 1;
         const uint32_t ds_base = sDS + tb * (2 * C::TILE_BYTES) + ds_row;
-        ok = mbar_wait(b_sfull, t & 1, &abortf, a.status, half ? W_U_SFULL1 : W_U_SFULL);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after_sync();
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {   // 16 queries at a time
           uint32_t pk_p[8], pk_ds[8];
@@ -493,11 +497,11 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             pk_ds[j / 2] = pack2<kBf16>(ds[0], ds[1]);
             pk_ds[j / 2 + 1] = pack2<kBf16>(ds[2], ds[3]);
           }
-          if (hf == 0) {
-            // P^T and dS^T may leave the registers once the products that read their previous contents are done:
-            // the previous tile's dV, and the dK / dQ / reduction of the tile before that
-            if (t > 0) ok = mbar_wait(b_ptfree, (t - 1) & 1, &abortf, a.status, W_U_PTFREE);
-            if (ok && t >= 2) ok = mbar_wait(smem_u32(&bar_ds_empty[tb]), ((t >> 1) - 1) & 1, &abortf, a.status, W_U_DSEMPTY);
+          if (hf == 0 && t > 0) {
+            // P^T and dS^T may leave the registers once the products that read their previous contents are done: the
+            // previous tile's dV, and the dK / dQ / reduction of the tile before that. The dV issuer waits for the latter
+            // itself before it signals the former, so one barrier stands for both.
+            ok = mbar_wait(b_ptfree, (t - 1) & 1, &abortf, a.status, W_U_PTFREE);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
