@@ -442,13 +442,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     auto prefetch_kd = [&](uint32_t cmd) {
       if (wcmd_class(cmd) == KD_TILE_PARTIAL) {
         const uint32_t* src = a.desc + (size_t)b * a.Tpad + (size_t)wcmd_kt(cmd) * KD_TILE;
-        const uint32_t* tbp = a.tilebits + ((size_t)b * a.NT + wcmd_kt(cmd)) * 32;
+        const uint4* tbp = reinterpret_cast<const uint4*>(a.tilebits + ((size_t)b * a.NT + wcmd_kt(cmd)) * 32);
 #pragma unroll
-        for (int w = 0; w < NW; ++w) {
-          kd_pre[w] = src[w * 32 + lane];
-          tb_pre[0][w] = tbp[4 * TB_PRE + w];
-          tb_pre[1][w] = tbp[4 * TB_CTX + w];
-          tb_pre[2][w] = tbp[4 * TB_INS + w];
+        for (int w = 0; w < NW; ++w) kd_pre[w] = src[w * 32 + lane];
+        static_assert(NW == 4, "a class mask of a tile is four words: one 16-byte load each");
+        constexpr int cls3[3] = {TB_PRE, TB_CTX, TB_INS};
+#pragma unroll
+        for (int k3 = 0; k3 < 3; ++k3) {
+          const uint4 m4 = tbp[cls3[k3]];
+          tb_pre[k3][0] = m4.x; tb_pre[k3][1] = m4.y; tb_pre[k3][2] = m4.z; tb_pre[k3][3] = m4.w;
         }
       }
     };
