@@ -38,6 +38,23 @@ def _tensor_key(t):
     return (t.data_ptr(), t._version, tuple(t.shape), tuple(t.stride()), str(t.dtype))
 
 
+_PINNED_WORDS = None
+_PINNED_NEXT = 0
+
+
+def _pinned_status_word() -> torch.Tensor:
+    """One int32 of pinned host memory for a plan's status mirror. Pinning memory is a slow, device-wide
+    call, so the words come from one pinned block handed out in rotation (1024 slots: a collision would
+    need more than 1024 live plans, and could only make a reported failure show up on two of them)."""
+    global _PINNED_WORDS, _PINNED_NEXT
+    if _PINNED_WORDS is None:
+        _PINNED_WORDS = torch.zeros(1024, dtype=torch.int32).pin_memory()
+    w = _PINNED_WORDS[_PINNED_NEXT:_PINNED_NEXT + 1]
+    _PINNED_NEXT = (_PINNED_NEXT + 1) % 1024
+    w.zero_()
+    return w
+
+
 class AttentionPlan:
     """Device-resident plan for B sequences of T tokens (layout: kd_plan_layout in kd_attention.h)."""
 
@@ -84,7 +101,7 @@ class AttentionPlan:
         self._keep = keep + [x for x in (in_span, span_id, is_prefix, lens) if x is not None]
         off = self.layout.off_status
         self._status_dev = self.buf[off:off + 4].view(torch.int32)
-        self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._status_host = _pinned_status_word()
         cur = torch.cuda.current_stream(device)
         with torch.cuda.device(device):
             _capi.check(_capi.load().kd_classify(ctypes.byref(meta), self.buf.data_ptr(), cur.cuda_stream))
